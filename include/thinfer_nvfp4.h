@@ -1,0 +1,228 @@
+/*
+ * thinfer_nvfp4.h — C ABI of the B200 (sm_100a) NVFP4 linear path.
+ *
+ * This is the boundary a thinfer maintainer binds from Rust (`extern "C"`): plain
+ * pointers and sizes, no C++ or torch types. Each entry point names the reference
+ * interface it stands in for (paths are relative to the reference's `projects/`).
+ *
+ * Conventions kept from the reference: activations A are [M,K] row-major bf16, weights
+ * are [N,K] ("N-major", blocks contiguous along K; thinfer-core/src/residency.rs:1026-1030),
+ * outputs are [M,N] row-major bf16; buffers are opaque ids in a backend-owned table
+ * (GpuBufferId, thinfer-core/src/tensor.rs:52-53) and `tnf_buf` is the non-owning
+ * {id, offset, len} view (BufRef, thinfer-core/src/backend/mod.rs:12-33).
+ *
+ * Every function returns a status: 0 on success, a negative tnf_status otherwise;
+ * tnf_last_error() gives the text of the calling thread's most recent failure.
+ * Kernel launches are asynchronous on the context's compute stream; uploads issued with
+ * tnf_stream_upload run on its copy stream. There is no CPU fallback anywhere: without a
+ * CUDA device every call that needs one fails with TNF_ERR_LAUNCH.
+ */
+#ifndef THINFER_NVFP4_H_
+#define THINFER_NVFP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error classes; mirror WgpuError (thinfer-core/src/backend/wgpu.rs:115-159). */
+typedef enum tnf_status {
+  TNF_OK = 0,
+  TNF_ERR_UNKNOWN_BUFFER = -1,  /* WgpuError::UnknownBuffer */
+  TNF_ERR_ALLOCATE_OOM = -2,    /* WgpuError::AllocateOom: the device refused */
+  TNF_ERR_BUDGET_EXCEEDED = -3, /* WgpuError::BudgetExceeded: refused on the host, device untouched */
+  TNF_ERR_INVALID_ARGUMENT = -4,/* shape / alignment / range */
+  TNF_ERR_LAUNCH = -5,          /* WgpuError::SubmitFailed: CUDA reported an error */
+  TNF_ERR_TIMEOUT = -6,         /* a bounded device-side or host-side wait gave up */
+  TNF_ERR_NCCL = -7
+} tnf_status;
+
+/* VramCategory (thinfer-core/src/mem.rs:14-26). */
+enum { TNF_CAT_WEIGHTS = 0, TNF_CAT_WORKSPACE = 1, TNF_CAT_STAGING = 2 };
+
+/* Source dtypes accepted by the weight quantiser. */
+enum { TNF_DTYPE_F32 = 0, TNF_DTYPE_BF16 = 1 };
+
+/* Scale layouts. CANONICAL is row-major [rows, K/16]; DEVICE is the 128x4 tiled layout
+ * the block-scaled MMA reads (512-byte atoms [rows/128][K/64 rounded up to 4]; inside an
+ * atom byte (r%32)*16 + ((r%128)/32)*4 + (b%4) holds row r, block b). */
+enum { TNF_SCALES_CANONICAL = 0, TNF_SCALES_DEVICE = 1 };
+
+/* Epilogue activation. GELU is the tanh form of thinfer-core/src/ops/gelu.rs:21-31. */
+enum { TNF_ACT_NONE = 0, TNF_ACT_GELU_TANH = 1 };
+
+typedef struct tnf_ctx tnf_ctx; /* one per device; Arc<WgpuBackend> in the reference */
+
+typedef struct tnf_buf {
+  uint64_t id, offset, len;
+} tnf_buf;
+
+/* ---- context and buffers ------------------------------------------------------------ */
+
+/* WgpuBackend::new + MemArbiter budget (thinfer-core/src/backend/wgpu.rs:741-760,
+ * thinfer-core/src/arbiter.rs:58-127). vram_budget_bytes == 0 means "no budget". */
+int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out);
+int32_t tnf_destroy(tnf_ctx* ctx);
+const char* tnf_last_error(void);
+/* Bytes of the built library's ABI version; bumps on any signature change. */
+uint32_t tnf_abi_version(void);
+
+/* Backend::allocate_in (thinfer-core/src/backend/mod.rs:104-113): charged to `category`;
+ * a request that would pass the budget fails with TNF_ERR_BUDGET_EXCEEDED before the
+ * device is touched (budget_oom_error, :101-107). */
+int32_t tnf_alloc(tnf_ctx* ctx, uint64_t bytes, int32_t category, uint64_t* id);
+/* Backend::free (thinfer-core/src/backend/wgpu.rs:764-780). */
+int32_t tnf_free(tnf_ctx* ctx, uint64_t id);
+/* Backend::write_buffer (thinfer-core/src/backend/mod.rs:123-132): ordered before later
+ * launches on the compute stream; the host memory may be reused on return. */
+int32_t tnf_write(tnf_ctx* ctx, uint64_t id, uint64_t dst_off, const void* src, uint64_t n);
+/* Backend::read_buffer (thinfer-core/src/backend/mod.rs:188-196): blocking. */
+int32_t tnf_read(tnf_ctx* ctx, uint64_t id, uint64_t off, void* dst, uint64_t n);
+/* Backend::copy_buffer_to_buffer (thinfer-core/src/backend/mod.rs:150-160). */
+int32_t tnf_copy(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uint64_t dst_id, uint64_t dst_off, uint64_t n);
+/* Raw device address of a buffer, for callers that interoperate with other CUDA code
+ * (no reference counterpart: wgpu hides addresses). */
+int32_t tnf_buf_ptr(tnf_ctx* ctx, uint64_t id, void** device_ptr, uint64_t* bytes);
+/* Awaited Backend::submit (thinfer-core/src/backend/wgpu.rs:941-1071): waits for the
+ * compute and copy streams, then reports a device-side wait that gave up as
+ * TNF_ERR_TIMEOUT. timeout_ms == 0 waits without a host limit. */
+int32_t tnf_sync(tnf_ctx* ctx, uint32_t timeout_ms);
+/* MemAccount snapshot (thinfer-core/src/mem.rs:105-196): out = {live weights, live
+ * workspace, live staging, peak weights, peak workspace, peak staging, true concurrent
+ * peak, bytes streamed host->device since creation}. */
+int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]);
+/* The context's CUDA streams (cudaStream_t as void*), for event timing by the caller. */
+int32_t tnf_streams(tnf_ctx* ctx, void** compute_stream, void** copy_stream);
+
+/* ---- quantisers (canonical layouts are bit-exact with the CPU oracle) ---------------- */
+
+/* Load-time transcode of a dense weight to NVFP4; stands where the reference's upload-time
+ * weight prep does (WeightPrep::Q8_0FromBf16, thinfer-core/src/backend/mod.rs:65-90,
+ * thinfer-core/src/ops/weight_prep.rs:86-163). w_src is f32 or bf16 [n,k]; codes is
+ * [n,k/2], scales [n,k/16] canonical. *global_scale receives amax/(6*448). Blocking. */
+int32_t tnf_quantize_weight(tnf_ctx* ctx, tnf_buf w_src, int32_t src_dtype, uint32_t n, uint32_t k,
+                            tnf_buf codes, tnf_buf scales, float* global_scale);
+/* Bytes of the DEVICE scale layout for a [rows,k] operand. */
+uint64_t tnf_device_scales_bytes(uint32_t rows, uint32_t k);
+/* Canonical scales -> DEVICE layout (weights: once at load; PreparedWeight idea,
+ * thinfer-models/src/common/block.rs:217-227). */
+int32_t tnf_prepare_scales(tnf_ctx* ctx, tnf_buf scales_canonical, uint32_t rows, uint32_t k, tnf_buf scales_device);
+/* Per-row, per-16 activation quantiser; stands where act_quant does
+ * (thinfer-core/src/ops/act_quant.rs:58-191, BatchScope::act_quant
+ * thinfer-core/src/workspace.rs:774-800). a_bf16 is [m,k]; global_scale > 0 is the
+ * per-tensor scale to use, 0 computes amax/(6*448) on the device first.
+ * *global_scale_used may be NULL; when not NULL the call blocks to report it. */
+int32_t tnf_quantize_act(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32_t k, float global_scale,
+                         int32_t scales_layout, tnf_buf codes, tnf_buf scales, float* global_scale_used);
+
+/* ---- the linear ---------------------------------------------------------------------- */
+
+/* out = epilogue(alpha * (Aq . Wq^T)): the dispatch arm Block::dispatch_matmul_site_diag
+ * selects (thinfer-models/src/common/block.rs:2656-2882) plus the bias / GELU / gated
+ * residual dispatches that follow it at the call sites
+ * (thinfer-models/src/qwen_image/dit.rs:324-340,745-754; thinfer-core/src/ops/bcast_add.rs,
+ * gelu.rs, bcast_fma.rs), fused. */
+typedef struct tnf_linear_args {
+  uint32_t m, n, k;
+  float a_global;       /* per-tensor activation scale; > 0 */
+  float w_global;       /* per-tensor weight scale from tnf_quantize_weight */
+  tnf_buf a_bf16;       /* [m,k] bf16; quantised on the fly */
+  tnf_buf w_codes;      /* [n,k/2] */
+  tnf_buf w_scales;     /* DEVICE layout (tnf_prepare_scales) */
+  tnf_buf bias_bf16;    /* [n] or len 0 */
+  tnf_buf gate_bf16;    /* [n] or len 0: out = residual + gate*y (BcastFma) */
+  tnf_buf residual_bf16;/* [m,n] (leading dim n) when gate is given */
+  tnf_buf out_bf16;     /* [m, ldo] */
+  uint32_t act;         /* TNF_ACT_* */
+  uint32_t parity_mode; /* 0 fused (one rounding), 1 chain (reference's intermediate bf16 roundings) */
+  uint32_t n_offset;    /* column offset into out (N-split) */
+  uint32_t ldo;         /* leading dimension of out in elements; 0 = n */
+  uint32_t flags;       /* TNF_LINEAR_* */
+  uint32_t reserved;
+} tnf_linear_args;
+
+enum {
+  TNF_LINEAR_A_PREQUANTIZED = 1u, /* a_bf16 unused; a_codes/a_scales of the ctx scratch come from tnf_quantize_act_shared */
+  TNF_LINEAR_SCATTER_PEERS = 2u   /* epilogue also stores to every peer registered with tnf_peer_outputs */
+};
+
+int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);
+
+/* Quantise A once into context scratch so that several linears can share it (q, k and v
+ * read one A: thinfer-models/src/qwen_image/dit.rs:511-560). Follow with
+ * tnf_linear_nvfp4(flags = TNF_LINEAR_A_PREQUANTIZED). */
+int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32_t k, float global_scale);
+
+/* Pre-quantised operands on both sides (codes + DEVICE scales): the GEMM alone. */
+int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args, tnf_buf a_codes, tnf_buf a_scales_device);
+
+/* ---- streaming residency (WeightResidency, thinfer-core/src/residency.rs) ------------ */
+
+/* Pinned host arena. host_ptr == NULL allocates `bytes` of pinned memory owned by the
+ * context; otherwise the caller's range is page-locked in place. The reference has no
+ * pinned memory (queue.write_buffer staging, thinfer-core/src/backend/wgpu.rs:782-803). */
+int32_t tnf_host_register(tnf_ctx* ctx, void* host_ptr, uint64_t bytes, uint64_t* host_id);
+int32_t tnf_host_ptr(tnf_ctx* ctx, uint64_t host_id, void** ptr, uint64_t* bytes);
+int32_t tnf_host_release(tnf_ctx* ctx, uint64_t host_id);
+/* stream_source_to_gpu (thinfer-core/src/residency.rs:1197-1341): asynchronous copy on
+ * the copy stream; *event identifies its completion. */
+int32_t tnf_stream_upload(tnf_ctx* ctx, uint64_t host_id, uint64_t host_off, uint64_t dst_id,
+                          uint64_t dst_off, uint64_t n, uint64_t* event);
+/* Compute stream waits for an upload event; the host does not block. */
+int32_t tnf_wait_event(tnf_ctx* ctx, uint64_t event);
+/* Copy stream waits until everything launched so far on the compute stream is done
+ * (a ring slot may be overwritten only after its last reader). */
+int32_t tnf_copy_after_compute(tnf_ctx* ctx);
+
+/* Layer-stack driver: the block loop that joins {compute block i, acquire i+1, prefetch
+ * i+2} (thinfer-models/src/qwen_image/dit.rs:1052-1180, thinfer-models/src/wan/dit.rs:520-640)
+ * over weights registered in rings / a pin plan (register_in_ring :382-423, set_pin_plan
+ * :440-457). See tnf_stack_* below. */
+typedef struct tnf_stack tnf_stack;
+
+typedef struct tnf_stack_linear {
+  uint32_t n, k;
+  uint32_t act;        /* TNF_ACT_* */
+  uint32_t has_bias;
+  uint32_t input;      /* 0: the layer input X; 1: the previous linear's output */
+  uint32_t stream_id;  /* which activation stream (0 img, 1 txt, 2 mod ...) */
+} tnf_stack_linear;
+
+/* Describe a stack of `layers` identical layers, each `n_linears` linears applied to
+ * `n_streams` activation streams of m_rows[s] rows. Weights live in the pinned arena
+ * `host_id` as consecutive per-linear records {codes, device scales, bias, f32 global};
+ * tnf_stack_record_bytes gives the record size. `vram_budget` bounds resident + ring
+ * weight bytes; ring_slots per linear kind defaults to 4 when 0 (residency.rs:50). */
+uint64_t tnf_stack_record_bytes(uint32_t n, uint32_t k);
+int32_t tnf_stack_create(tnf_ctx* ctx, uint32_t layers, uint32_t n_linears, const tnf_stack_linear* linears,
+                         uint32_t n_streams, const uint32_t* m_rows, uint32_t hidden, uint64_t host_id,
+                         uint64_t weight_budget_bytes, uint32_t ring_slots, tnf_stack** out);
+/* One pass over all layers (one "DiT step" of the GEMM stack). x_ids[s] are [m_rows[s],
+ * hidden] bf16 inputs; outputs are written to out_ids[s] ([m_rows[s], n_last]). */
+int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* out_ids, float a_global);
+/* out = {pinned layers' bytes, ring bytes, bytes uploaded in the last step, uploads in
+ * the last step, resident linears, streamed linears}. */
+int32_t tnf_stack_stats(tnf_stack* st, uint64_t out[6]);
+int32_t tnf_stack_destroy(tnf_stack* st);
+
+/* ---- multi-GPU (no reference counterpart: the reference is single-device) ------------ */
+
+/* Join an NCCL communicator of `world` ranks. unique_id is the 128-byte ncclUniqueId
+ * made by rank 0 with tnf_comm_unique_id and passed around by the caller. */
+int32_t tnf_comm_unique_id(void* unique_id_128);
+int32_t tnf_comm_init(tnf_ctx* ctx, int32_t world, int32_t rank, const void* unique_id_128);
+/* All-gather the column slices of an N-split output: every rank holds out[m, n_total]
+ * with its own n_local columns at rank*n_local filled; on return all columns are filled. */
+int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t n_total, uint32_t n_local);
+/* Peer output windows for the fused epilogue scatter: 64-byte CUDA IPC handles. */
+int32_t tnf_ipc_export(tnf_ctx* ctx, uint64_t id, void* handle_64);
+int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t n_peers, const void* handles_64xn);
+/* Stream-ordered barrier across the communicator (after a scatter epilogue). */
+int32_t tnf_comm_barrier(tnf_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THINFER_NVFP4_H_ */

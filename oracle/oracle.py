@@ -1,0 +1,292 @@
+"""ctypes/numpy front end of the CPU oracle (TEST INFRASTRUCTURE, not a product path)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "build", "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside this file (needs g++)."""
+    srcs = [os.path.join(_HERE, f) for f in ("nvfp4_oracle.cpp", "ref_restate.cpp", "Makefile")]
+    stale = not os.path.exists(_SO) or any(os.path.getmtime(s) > os.path.getmtime(_SO) for s in srcs)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
+    return _SO
+
+
+def _load():
+    if not os.path.exists(_SO):
+        build()
+    lib = C.CDLL(_SO)
+    f32p, u16p, u8p, i8p = (C.POINTER(t) for t in (C.c_float, C.c_uint16, C.c_uint8, C.c_int8))
+    i64, f32, vp = C.c_int64, C.c_float, C.c_void_p
+    sig = {
+        "orc_num_threads": (C.c_int, []),
+        "orc_bf16_rne": (C.c_uint16, [f32]),
+        "orc_e4m3_encode": (C.c_uint8, [f32]),
+        "orc_e4m3_decode": (f32, [C.c_uint8]),
+        "orc_e2m1_encode": (C.c_uint8, [f32]),
+        "orc_e2m1_decode": (f32, [C.c_uint8]),
+        "orc_f32_to_bf16": (None, [vp, vp, i64]),
+        "orc_gaussian": (None, [vp, i64, C.c_uint64]),
+        "orc_amax_f32": (f32, [vp, i64]),
+        "orc_amax_bf16": (f32, [vp, i64]),
+        "orc_global_scale": (f32, [f32]),
+        "orc_quantize_weight": (f32, [vp, i64, i64, vp, vp]),
+        "orc_quantize_weight_bf16": (f32, [vp, i64, i64, vp, vp]),
+        "orc_quantize_act": (None, [vp, i64, i64, f32, vp, vp]),
+        "orc_dequant": (None, [vp, vp, f32, i64, i64, vp]),
+        "orc_scales_to_device_layout": (i64, [vp, i64, i64, vp]),
+        "orc_gemm_f32": (None, [vp, vp, i64, i64, i64, vp]),
+        "orc_gemm_f64": (None, [vp, vp, i64, i64, i64, vp]),
+        "orc_epilogue": (None, [vp, i64, i64, f32, vp, C.c_int, vp, vp, C.c_int, vp]),
+        "orc_linear": (None, [vp, i64, i64, f32, C.c_int, vp, vp, f32, i64, vp, C.c_int, vp, vp, C.c_int, vp, vp]),
+        "ref_f16_from_f32": (C.c_uint16, [f32]),
+        "ref_f16_to_f32": (f32, [C.c_uint16]),
+        "ref_lcg_fill": (None, [vp, i64, C.POINTER(C.c_uint64), f32]),
+        "ref_quantize_row_q8_0": (None, [vp, i64, vp]),
+        "ref_encode_q8_0_from_bf16": (None, [vp, i64, vp]),
+        "ref_dequantize_row_q8_0": (None, [vp, i64, vp]),
+        "ref_quantize_row_q4_0": (None, [vp, i64, vp]),
+        "ref_dequantize_row_q4_0": (None, [vp, i64, vp]),
+        "ref_act_quant_i8": (None, [vp, i64, i64, vp, vp]),
+        "ref_matmul_i8": (None, [vp, vp, vp, vp, vp, i64, i64, i64, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+_lib = _load()
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def num_threads() -> int:
+    return int(_lib.orc_num_threads())
+
+
+# ---- scalar conversions -------------------------------------------------------------
+def bf16_rne(x: float) -> int:
+    return int(_lib.orc_bf16_rne(x))
+
+
+def e4m3_encode(x: float) -> int:
+    return int(_lib.orc_e4m3_encode(x))
+
+
+def e4m3_decode(c: int) -> float:
+    return float(_lib.orc_e4m3_decode(c))
+
+
+def e2m1_encode(x: float) -> int:
+    return int(_lib.orc_e2m1_encode(x))
+
+
+def e2m1_decode(c: int) -> float:
+    return float(_lib.orc_e2m1_decode(c))
+
+
+# ---- arrays -------------------------------------------------------------------------
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    _lib.orc_f32_to_bf16(_p(x), _p(out), x.size)
+    return out
+
+
+def bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    return (_c(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def gaussian(n: int, seed: int) -> np.ndarray:
+    out = np.empty(n, np.float32)
+    _lib.orc_gaussian(_p(out), n, C.c_uint64(seed & (2**64 - 1)))
+    return out
+
+
+def global_scale(amax: float) -> float:
+    return float(_lib.orc_global_scale(amax))
+
+
+def amax_bf16(a: np.ndarray) -> float:
+    a = _c(a, np.uint16)
+    return float(_lib.orc_amax_bf16(_p(a), a.size))
+
+
+def quantize_weight(w: np.ndarray):
+    """f32 or bf16-bits (uint16) [rows, k] -> (codes [rows,k/2] u8, scales [rows,k/16] u8, g)."""
+    rows, k = w.shape
+    assert k % 16 == 0
+    codes = np.empty((rows, k // 2), np.uint8)
+    scales = np.empty((rows, k // 16), np.uint8)
+    if w.dtype == np.uint16:
+        w = _c(w, np.uint16)
+        g = _lib.orc_quantize_weight_bf16(_p(w), rows, k, _p(codes), _p(scales))
+    else:
+        w = _c(w, np.float32)
+        g = _lib.orc_quantize_weight(_p(w), rows, k, _p(codes), _p(scales))
+    return codes, scales, float(g)
+
+
+def quantize_act(a_bf16: np.ndarray, g: float):
+    a = _c(a_bf16, np.uint16)
+    m, k = a.shape
+    assert k % 16 == 0
+    codes = np.empty((m, k // 2), np.uint8)
+    scales = np.empty((m, k // 16), np.uint8)
+    _lib.orc_quantize_act(_p(a), m, k, g, _p(codes), _p(scales))
+    return codes, scales
+
+
+def dequant(codes: np.ndarray, scales: np.ndarray, g: float) -> np.ndarray:
+    codes, scales = _c(codes, np.uint8), _c(scales, np.uint8)
+    rows, k = codes.shape[0], codes.shape[1] * 2
+    out = np.empty((rows, k), np.float32)
+    _lib.orc_dequant(_p(codes), _p(scales), g, rows, k, _p(out))
+    return out
+
+
+def scales_to_device_layout(scales: np.ndarray) -> np.ndarray:
+    scales = _c(scales, np.uint8)
+    rows, nb = scales.shape
+    out = np.empty(((rows + 127) // 128) * ((((nb + 3) // 4) + 3) // 4 * 4) * 512, np.uint8)
+    _lib.orc_scales_to_device_layout(_p(scales), rows, nb, _p(out))
+    return out
+
+
+def gemm_f32(a: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """out[m,n] = sum_k a[m,k]*w[n,k], f32, K ascending."""
+    a, w = _c(a, np.float32), _c(w, np.float32)
+    m, k = a.shape
+    n = w.shape[0]
+    out = np.empty((m, n), np.float32)
+    _lib.orc_gemm_f32(_p(a), _p(w), m, n, k, _p(out))
+    return out
+
+
+def gemm_f64(a: np.ndarray, w: np.ndarray) -> np.ndarray:
+    a, w = _c(a, np.float32), _c(w, np.float32)
+    m, k = a.shape
+    n = w.shape[0]
+    out = np.empty((m, n), np.float64)
+    _lib.orc_gemm_f64(_p(a), _p(w), m, n, k, _p(out))
+    return out
+
+
+def epilogue(acc, scale=1.0, bias=None, act=0, gate=None, residual=None, chain=False) -> np.ndarray:
+    acc = _c(acc, np.float32)
+    m, n = acc.shape
+    out = np.empty((m, n), np.uint16)
+    bias = None if bias is None else _c(bias, np.uint16)
+    gate = None if gate is None else _c(gate, np.uint16)
+    residual = None if residual is None else _c(residual, np.uint16)
+    _lib.orc_epilogue(_p(acc), m, n, scale, _p(bias), act, _p(gate), _p(residual), int(chain), _p(out))
+    return out
+
+
+def linear(a_bf16, g_a, w_codes, w_scales, g_w, bias=None, act=0, gate=None, residual=None,
+           chain=False, quantize_a=True, return_acc=False):
+    """The NVFP4 linear as the device computes it; returns bf16 bits [m, n]."""
+    a = _c(a_bf16, np.uint16)
+    w_codes, w_scales = _c(w_codes, np.uint8), _c(w_scales, np.uint8)
+    m, k = a.shape
+    n = w_codes.shape[0]
+    out = np.empty((m, n), np.uint16)
+    acc = np.empty((m, n), np.float32) if return_acc else None
+    bias = None if bias is None else _c(bias, np.uint16)
+    gate = None if gate is None else _c(gate, np.uint16)
+    residual = None if residual is None else _c(residual, np.uint16)
+    _lib.orc_linear(_p(a), m, k, g_a, int(quantize_a), _p(w_codes), _p(w_scales), g_w, n, _p(bias),
+                    act, _p(gate), _p(residual), int(chain), _p(out), _p(acc))
+    return (out, acc) if return_acc else out
+
+
+# ---- restated reference routines (pinned by the reference's own unit tests) ----------
+def ref_f16_from_f32(x: float) -> int:
+    return int(_lib.ref_f16_from_f32(x))
+
+
+def ref_f16_to_f32(h: int) -> float:
+    return float(_lib.ref_f16_to_f32(h))
+
+
+class RefLcg:
+    """The LCG the reference's conformance tests draw inputs from."""
+
+    def __init__(self, seed: int):
+        self.state = C.c_uint64(seed)
+
+    def fill(self, n: int, amp: float = 1.0) -> np.ndarray:
+        out = np.empty(n, np.float32)
+        _lib.ref_lcg_fill(_p(out), n, C.byref(self.state), amp)
+        return out
+
+
+def ref_quantize_row_q8_0(x):
+    x = _c(x, np.float32)
+    out = np.empty(x.size // 32 * 34, np.uint8)
+    _lib.ref_quantize_row_q8_0(_p(x), x.size, _p(out))
+    return out
+
+
+def ref_encode_q8_0_from_bf16(h):
+    h = _c(h, np.uint16)
+    out = np.empty(h.size // 32 * 34, np.uint8)
+    _lib.ref_encode_q8_0_from_bf16(_p(h), h.size, _p(out))
+    return out
+
+
+def ref_dequantize_row_q8_0(q):
+    q = _c(q, np.uint8)
+    n = q.size // 34 * 32
+    out = np.empty(n, np.float32)
+    _lib.ref_dequantize_row_q8_0(_p(q), n, _p(out))
+    return out
+
+
+def ref_quantize_row_q4_0(x):
+    x = _c(x, np.float32)
+    out = np.empty(x.size // 32 * 18, np.uint8)
+    _lib.ref_quantize_row_q4_0(_p(x), x.size, _p(out))
+    return out
+
+
+def ref_dequantize_row_q4_0(q):
+    q = _c(q, np.uint8)
+    n = q.size // 18 * 32
+    out = np.empty(n, np.float32)
+    _lib.ref_dequantize_row_q4_0(_p(q), n, _p(out))
+    return out
+
+
+def ref_act_quant_i8(a):
+    a = _c(a, np.float32)
+    rows, k = a.shape
+    q = np.empty((rows, k), np.int8)
+    params = np.empty((rows, k // 32, 2), np.float32)
+    _lib.ref_act_quant_i8(_p(a), rows, k, _p(q), _p(params))
+    return q, params
+
+
+def ref_matmul_i8(a, a_scale, a_zero, b, b_scale):
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    m, k = a.shape
+    n = b.shape[0]
+    out = np.empty((m, n), np.float32)
+    _lib.ref_matmul_i8(_p(a), _p(_c(a_scale, np.float32)), _p(_c(a_zero, np.float32)), _p(b),
+                       _p(_c(b_scale, np.float32)), m, n, k, _p(out))
+    return out

@@ -1,0 +1,190 @@
+// TEST INFRASTRUCTURE — CPU restatement of the pieces of cretz/thinfer's quantised-linear
+// path that the reference itself pins with unit tests. Not a product path.
+//
+// The NVFP4 oracle (nvfp4_oracle.cpp) borrows its conventions from these routines; they
+// are restated here so that the borrowing can be checked against the reference's own
+// known-answer tests (see tests/test_oracle_pins.py). Each function cites the reference
+// lines it follows. f16 narrowing follows the `half` crate 2.7.1 behaviour (IEEE RNE with
+// subnormals) that thinfer-core/src/weight.rs:269-336 and
+// thinfer-core/src/ops/weight_prep.rs:52-80 pin.
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+namespace {
+inline uint32_t f32_bits(float x) { uint32_t b; std::memcpy(&b, &x, 4); return b; }
+inline float bits_f32(uint32_t b) { float x; std::memcpy(&x, &b, 4); return x; }
+
+// IEEE binary16 <- binary32, round-to-nearest-even, subnormals kept.
+inline uint16_t f16_from_f32(float x) {
+    uint32_t b = f32_bits(x);
+    uint32_t sign = (b >> 16) & 0x8000u;
+    uint32_t abs = b & 0x7FFFFFFFu;
+    if (abs > 0x7F800000u) return uint16_t(sign | 0x7E00u | ((abs >> 13) & 0x3FFu));  // NaN
+    if (abs >= 0x47800000u) return uint16_t(sign | 0x7C00u);                          // >= 65536 -> inf
+    if (abs < 0x33000000u) return uint16_t(sign);                                     // < 2^-25 -> 0
+    int e = int(abs >> 23) - 127;
+    uint32_t mant = (abs & 0x7FFFFFu) | 0x800000u;
+    int shift = (e < -14) ? (13 + (-14 - e)) : 13;
+    uint32_t q = mant >> shift;
+    uint32_t rem = mant & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1u))) q += 1;
+    uint32_t out = (e < -14) ? q : ((uint32_t(e + 15) << 10) + (q - 0x400u));
+    return uint16_t(sign | out);  // mantissa carry propagates into the exponent, inf at 0x7C00
+}
+inline float f16_to_f32(uint16_t h) {
+    uint32_t sign = uint32_t(h & 0x8000u) << 16;
+    int e = (h >> 10) & 0x1F;
+    uint32_t m = h & 0x3FFu;
+    if (e == 0) return bits_f32(sign) + (sign ? -1.0f : 1.0f) * std::ldexp(float(m), -24);
+    if (e == 31) return bits_f32(sign | 0x7F800000u | (m << 13));
+    return bits_f32(sign | (uint32_t(e + 112) << 23) | (m << 13));
+}
+// Rust f32::round: half away from zero.
+inline float round_half_away(float v) { return std::round(v); }
+}  // namespace
+
+extern "C" {
+
+uint16_t ref_f16_from_f32(float x) { return f16_from_f32(x); }
+float ref_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
+// LCG of the reference's conformance tests (thinfer-conformance/tests/q4_0_matmul.rs:56-61):
+// s = s*6364136223846793005 + 1 ; r = (s>>33) as u32 as f32 / u32::MAX as f32 ; r*2-1.
+void ref_lcg_fill(float* out, int64_t n, uint64_t* state, float amp) {
+    uint64_t s = *state;
+    for (int64_t i = 0; i < n; ++i) {
+        s = s * 6364136223846793005ull + 1ull;
+        float r = float(uint32_t(s >> 33)) / float(0xFFFFFFFFu);
+        out[i] = (r * 2.0f - 1.0f) * amp;
+    }
+    *state = s;
+}
+
+// thinfer-core/src/quant.rs:735-755 (quantize_row_q8_0): 34-byte blocks, f16 d + 32 i8.
+void ref_quantize_row_q8_0(const float* src, int64_t n, uint8_t* dst) {
+    for (int64_t b = 0; b < n / 32; ++b) {
+        const float* x = src + b * 32;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) amax = std::fmax(amax, std::fabs(x[i]));
+        float scale = amax / 127.0f;
+        float inv = scale > 0.0f ? 1.0f / scale : 0.0f;
+        uint16_t h = f16_from_f32(scale);
+        dst[b * 34] = uint8_t(h & 0xFF);
+        dst[b * 34 + 1] = uint8_t(h >> 8);
+        for (int i = 0; i < 32; ++i) {
+            float q = round_half_away(x[i] * inv);
+            q = q < -127.0f ? -127.0f : (q > 127.0f ? 127.0f : q);
+            dst[b * 34 + 2 + i] = uint8_t(int8_t(q));
+        }
+    }
+}
+
+// thinfer-core/src/quant.rs:169-194 (encode_q8_0_from_bf16): source is bf16 bits.
+void ref_encode_q8_0_from_bf16(const uint16_t* src, int64_t n, uint8_t* dst) {
+    for (int64_t b = 0; b < n / 32; ++b) {
+        float x[32];
+        float amax = 0.0f;
+        for (int i = 0; i < 32; ++i) {
+            x[i] = bits_f32(uint32_t(src[b * 32 + i]) << 16);
+            amax = std::fmax(amax, std::fabs(x[i]));
+        }
+        float d = amax / 127.0f;
+        float id = d == 0.0f ? 0.0f : 1.0f / d;
+        uint16_t h = f16_from_f32(d);
+        dst[b * 34] = uint8_t(h & 0xFF);
+        dst[b * 34 + 1] = uint8_t(h >> 8);
+        for (int i = 0; i < 32; ++i) dst[b * 34 + 2 + i] = uint8_t(int8_t(round_half_away(x[i] * id)));
+    }
+}
+
+// thinfer-core/src/quant.rs:709-733 (dequantize_row_q8_0).
+void ref_dequantize_row_q8_0(const uint8_t* src, int64_t n, float* dst) {
+    for (int64_t b = 0; b < n / 32; ++b) {
+        float scale = f16_to_f32(uint16_t(src[b * 34] | (src[b * 34 + 1] << 8)));
+        for (int i = 0; i < 32; ++i) dst[b * 32 + i] = float(int8_t(src[b * 34 + 2 + i])) * scale;
+    }
+}
+
+// thinfer-core/src/quant.rs:784-811 (quantize_row_q4_0): 18-byte blocks; byte j packs
+// element j (low nibble) and j+16 (high nibble).
+void ref_quantize_row_q4_0(const float* src, int64_t n, uint8_t* dst) {
+    for (int64_t b = 0; b < n / 32; ++b) {
+        const float* x = src + b * 32;
+        float amax = 0.0f, smax = 0.0f;
+        for (int i = 0; i < 32; ++i)
+            if (std::fabs(x[i]) > amax) { amax = std::fabs(x[i]); smax = x[i]; }
+        float d = smax / -8.0f;
+        float id = d != 0.0f ? 1.0f / d : 0.0f;
+        uint16_t h = f16_from_f32(d);
+        dst[b * 18] = uint8_t(h & 0xFF);
+        dst[b * 18 + 1] = uint8_t(h >> 8);
+        for (int j = 0; j < 16; ++j) {
+            int a0 = int(std::floor(x[j] * id + 8.5f)), a1 = int(std::floor(x[j + 16] * id + 8.5f));
+            a0 = a0 < 0 ? 0 : (a0 > 15 ? 15 : a0);
+            a1 = a1 < 0 ? 0 : (a1 > 15 ? 15 : a1);
+            dst[b * 18 + 2 + j] = uint8_t(a0 | (a1 << 4));
+        }
+    }
+}
+
+// thinfer-core/src/quant.rs:757-782 (dequantize_row_q4_0).
+void ref_dequantize_row_q4_0(const uint8_t* src, int64_t n, float* dst) {
+    for (int64_t b = 0; b < n / 32; ++b) {
+        float scale = f16_to_f32(uint16_t(src[b * 18] | (src[b * 18 + 1] << 8)));
+        for (int j = 0; j < 16; ++j) {
+            uint8_t by = src[b * 18 + 2 + j];
+            dst[b * 32 + j] = float(int(by & 0xF) - 8) * scale;
+            dst[b * 32 + j + 16] = float(int(by >> 4) - 8) * scale;
+        }
+    }
+}
+
+// thinfer-core/src/ops/act_quant.rs:121-151 and
+// thinfer-conformance/tests/i8_common/mod.rs:245-272 (quant_block_to_i8): asymmetric
+// int8 per 32-block; the parameters are narrowed to f16 BEFORE the codes are computed.
+void ref_act_quant_i8(const float* a, int64_t rows, int64_t k, int8_t* q, float* params /*[rows*k/32*2]*/) {
+    int64_t nb = k / 32;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t b = 0; b < nb; ++b) {
+            const float* x = a + r * k + b * 32;
+            float mn = INFINITY, mx = -INFINITY;
+            for (int i = 0; i < 32; ++i) { if (x[i] < mn) mn = x[i]; if (x[i] > mx) mx = x[i]; }
+            float range = mx - mn;
+            float s_raw = range <= 0.0f ? 1.0e-30f : range / 254.0f;
+            float z_raw = mn + 127.0f * s_raw;
+            float s = f16_to_f32(f16_from_f32(s_raw)), z = f16_to_f32(f16_from_f32(z_raw));
+            float inv = 1.0f / s;
+            for (int i = 0; i < 32; ++i) {
+                float v = round_half_away((x[i] - z) * inv);
+                v = v < -127.0f ? -127.0f : (v > 127.0f ? 127.0f : v);
+                q[r * k + b * 32 + i] = int8_t(int(v));
+            }
+            params[2 * (r * nb + b)] = s;
+            params[2 * (r * nb + b) + 1] = z;
+        }
+}
+
+// thinfer-conformance/tests/matmul_i8.rs:76-116 (cpu_matmul_i8_ref).
+void ref_matmul_i8(const int8_t* a, const float* a_scale, const float* a_zero, const int8_t* b,
+                   const float* b_scale, int64_t m, int64_t n, int64_t k, float* out) {
+    int64_t nb = k / 32;
+    for (int64_t i = 0; i < m; ++i)
+        for (int64_t j = 0; j < n; ++j) {
+            float acc = 0.0f;
+            for (int64_t t = 0; t < nb; ++t) {
+                int32_t dot = 0, qsum = 0;
+                for (int kk = 0; kk < 32; ++kk) {
+                    int32_t av = a[i * k + t * 32 + kk], bv = b[j * k + t * 32 + kk];
+                    dot += av * bv;
+                    qsum += bv;
+                }
+                float sa = a_scale[i * nb + t], za = a_zero[i * nb + t], sb = b_scale[j * nb + t];
+                acc += float(dot) * sa * sb + za * sb * float(qsum);
+            }
+            out[i * n + j] = acc < -65504.0f ? -65504.0f : (acc > 65504.0f ? 65504.0f : acc);
+        }
+}
+
+}  // extern "C"

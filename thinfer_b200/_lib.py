@@ -1,0 +1,102 @@
+"""ctypes binding of libthinfer_nvfp4.so. There is no fallback: a missing library raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libthinfer_nvfp4.so")
+
+OK = 0
+ERR_UNKNOWN_BUFFER, ERR_ALLOCATE_OOM, ERR_BUDGET_EXCEEDED = -1, -2, -3
+ERR_INVALID_ARGUMENT, ERR_LAUNCH, ERR_TIMEOUT, ERR_NCCL = -4, -5, -6, -7
+CAT_WEIGHTS, CAT_WORKSPACE, CAT_STAGING = 0, 1, 2
+DTYPE_F32, DTYPE_BF16 = 0, 1
+SCALES_CANONICAL, SCALES_DEVICE = 0, 1
+ACT_NONE, ACT_GELU_TANH = 0, 1
+LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS = 1, 2
+
+
+class Buf(C.Structure):
+    """tnf_buf: the non-owning {id, offset, len} view (BufRef in the reference)."""
+    _fields_ = [("id", C.c_uint64), ("offset", C.c_uint64), ("len", C.c_uint64)]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+        ("a_global", C.c_float), ("w_global", C.c_float),
+        ("a_bf16", Buf), ("w_codes", Buf), ("w_scales", Buf), ("bias_bf16", Buf),
+        ("gate_bf16", Buf), ("residual_bf16", Buf), ("out_bf16", Buf),
+        ("act", C.c_uint32), ("parity_mode", C.c_uint32), ("n_offset", C.c_uint32),
+        ("ldo", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+class StackLinear(C.Structure):
+    _fields_ = [("n", C.c_uint32), ("k", C.c_uint32), ("act", C.c_uint32), ("has_bias", C.c_uint32),
+                ("input", C.c_uint32), ("stream_id", C.c_uint32)]
+
+
+_u64p, _u32p, _vpp = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_void_p)
+_ctx = C.c_void_p
+
+# name -> (restype, argtypes); must list every symbol include/thinfer_nvfp4.h declares
+SIGNATURES = {
+    "tnf_create": (C.c_int32, [C.c_int32, C.c_uint64, C.POINTER(_ctx)]),
+    "tnf_destroy": (C.c_int32, [_ctx]),
+    "tnf_last_error": (C.c_char_p, []),
+    "tnf_abi_version": (C.c_uint32, []),
+    "tnf_alloc": (C.c_int32, [_ctx, C.c_uint64, C.c_int32, _u64p]),
+    "tnf_free": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_write": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "tnf_read": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_void_p, C.c_uint64]),
+    "tnf_copy": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "tnf_buf_ptr": (C.c_int32, [_ctx, C.c_uint64, _vpp, _u64p]),
+    "tnf_sync": (C.c_int32, [_ctx, C.c_uint32]),
+    "tnf_mem_snapshot": (C.c_int32, [_ctx, _u64p]),
+    "tnf_streams": (C.c_int32, [_ctx, _vpp, _vpp]),
+    "tnf_quantize_weight": (C.c_int32, [_ctx, Buf, C.c_int32, C.c_uint32, C.c_uint32, Buf, Buf, C.POINTER(C.c_float)]),
+    "tnf_device_scales_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
+    "tnf_prepare_scales": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, Buf]),
+    "tnf_quantize_act": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float, C.c_int32, Buf, Buf, C.POINTER(C.c_float)]),
+    "tnf_linear_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_quantize_act_shared": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float]),
+    "tnf_gemm_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs), Buf, Buf]),
+    "tnf_host_register": (C.c_int32, [_ctx, C.c_void_p, C.c_uint64, _u64p]),
+    "tnf_host_ptr": (C.c_int32, [_ctx, C.c_uint64, _vpp, _u64p]),
+    "tnf_host_release": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_stream_upload": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _u64p]),
+    "tnf_wait_event": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_copy_after_compute": (C.c_int32, [_ctx]),
+    "tnf_stack_record_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
+    "tnf_stack_create": (C.c_int32, [_ctx, C.c_uint32, C.c_uint32, C.POINTER(StackLinear), C.c_uint32, _u32p,
+                                     C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "tnf_stack_step": (C.c_int32, [C.c_void_p, _u64p, _u64p, C.c_float]),
+    "tnf_stack_stats": (C.c_int32, [C.c_void_p, _u64p]),
+    "tnf_stack_destroy": (C.c_int32, [C.c_void_p]),
+    "tnf_comm_unique_id": (C.c_int32, [C.c_void_p]),
+    "tnf_comm_init": (C.c_int32, [_ctx, C.c_int32, C.c_int32, C.c_void_p]),
+    "tnf_all_gather_cols": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "tnf_ipc_export": (C.c_int32, [_ctx, C.c_uint64, C.c_void_p]),
+    "tnf_peer_outputs": (C.c_int32, [_ctx, C.c_int32, C.c_void_p]),
+    "tnf_comm_barrier": (C.c_int32, [_ctx]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the CUDA library. Raises if it has not been built; nothing stands in for it."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m thinfer_b200.build` "
+                "(nvcc, sm_100a). thinfer_b200 has no CPU or PyTorch fallback.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

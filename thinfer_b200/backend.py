@@ -1,0 +1,285 @@
+"""Host-side mirror of the reference's backend and op surface for the NVFP4 linear path.
+
+Names follow the reference so that tests read like its own:
+
+* :class:`Backend` — ``trait Backend`` (thinfer-core/src/backend/mod.rs:94-206):
+  ``allocate_in`` / ``free`` / ``write_buffer`` / ``read_buffer`` /
+  ``copy_buffer_to_buffer`` / ``submit`` / ``supports_weight_prep`` / ``weight_prep``.
+* :class:`BatchScope` — the op-forwarding methods of ``BatchScope``
+  (thinfer-core/src/workspace.rs:774-996): ``act_quant``, ``matmul`` and the fused
+  ``linear`` that covers the ``biased`` call site (thinfer-models/src/qwen_image/dit.rs:324-340).
+* :class:`Nvfp4Weight` — the ``PreparedWeight`` a site keeps resident
+  (thinfer-models/src/common/block.rs:217-227), here codes + device-layout scales + bias.
+
+Everything runs on the GPU through the C ABI (``include/thinfer_nvfp4.h``); host arrays are
+numpy, bf16 carried as ``uint16`` bit patterns.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import _lib as L
+from ._lib import Buf, LinearArgs
+
+
+class TnfError(RuntimeError):
+    """WgpuError (thinfer-core/src/backend/wgpu.rs:115-159)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+
+
+class UnknownBuffer(TnfError):
+    pass
+
+
+class AllocateOom(TnfError):
+    pass
+
+
+class BudgetExceeded(TnfError):
+    pass
+
+
+class InvalidArgument(TnfError):
+    pass
+
+
+class LaunchFailed(TnfError):
+    pass
+
+
+class DeviceTimeout(TnfError):
+    pass
+
+
+class NcclError(TnfError):
+    pass
+
+
+_ERRORS = {
+    L.ERR_UNKNOWN_BUFFER: UnknownBuffer, L.ERR_ALLOCATE_OOM: AllocateOom,
+    L.ERR_BUDGET_EXCEEDED: BudgetExceeded, L.ERR_INVALID_ARGUMENT: InvalidArgument,
+    L.ERR_LAUNCH: LaunchFailed, L.ERR_TIMEOUT: DeviceTimeout, L.ERR_NCCL: NcclError,
+}
+
+
+def _check(code: int) -> None:
+    if code != L.OK:
+        msg = L.load().tnf_last_error().decode("utf-8", "replace")
+        raise _ERRORS.get(code, TnfError)(code, msg)
+
+
+_NONE = Buf(0, 0, 0)
+
+
+def _host(a: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(a)
+
+
+class Backend:
+    """One CUDA device behind the C ABI. ``vram_budget`` (bytes, 0 = none) is the arbiter's budget."""
+
+    def __init__(self, device: int = 0, vram_budget: int = 0):
+        self.lib = L.load()
+        self._ctx = C.c_void_p()
+        _check(self.lib.tnf_create(device, vram_budget, C.byref(self._ctx)))
+        self.device = device
+
+    # -- lifetime ---------------------------------------------------------------------
+    def close(self) -> None:
+        if self._ctx:
+            self.lib.tnf_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- trait Backend ------------------------------------------------------------------
+    def allocate_in(self, nbytes: int, category: int = L.CAT_WORKSPACE) -> Buf:
+        bid = C.c_uint64()
+        _check(self.lib.tnf_alloc(self._ctx, nbytes, category, C.byref(bid)))
+        return Buf(bid.value, 0, nbytes)
+
+    def allocate(self, nbytes: int) -> Buf:
+        return self.allocate_in(nbytes, L.CAT_WORKSPACE)
+
+    def free(self, buf) -> None:
+        _check(self.lib.tnf_free(self._ctx, buf.id if isinstance(buf, Buf) else int(buf)))
+
+    def write_buffer(self, buf: Buf, data: np.ndarray, offset: int = 0) -> None:
+        data = _host(data)
+        _check(self.lib.tnf_write(self._ctx, buf.id, buf.offset + offset, data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def read_buffer(self, buf: Buf, dtype=np.uint8, count: Optional[int] = None, offset: int = 0) -> np.ndarray:
+        dt = np.dtype(dtype)
+        nbytes = (buf.len - offset) if count is None else count * dt.itemsize
+        out = np.empty(nbytes // dt.itemsize, dt)
+        _check(self.lib.tnf_read(self._ctx, buf.id, buf.offset + offset, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def copy_buffer_to_buffer(self, src: Buf, dst: Buf, nbytes: int) -> None:
+        _check(self.lib.tnf_copy(self._ctx, src.id, src.offset, dst.id, dst.offset, nbytes))
+
+    def submit(self, timeout_ms: int = 0) -> None:
+        """Awaited submit: waits for the device and surfaces device-side wait failures."""
+        _check(self.lib.tnf_sync(self._ctx, timeout_ms))
+
+    def supports_weight_prep(self) -> bool:
+        return True
+
+    def weight_prep(self, w: np.ndarray) -> "Nvfp4Weight":
+        return Nvfp4Weight.from_dense(self, w)
+
+    # -- helpers ------------------------------------------------------------------------
+    def upload(self, data: np.ndarray, category: int = L.CAT_WORKSPACE) -> Buf:
+        data = _host(data)
+        buf = self.allocate_in(max(data.nbytes, 16), category)
+        self.write_buffer(buf, data)
+        return Buf(buf.id, 0, data.nbytes)
+
+    def mem_snapshot(self) -> dict:
+        out = (C.c_uint64 * 8)()
+        _check(self.lib.tnf_mem_snapshot(self._ctx, out))
+        keys = ["live_weights", "live_workspace", "live_staging", "peak_weights", "peak_workspace",
+                "peak_staging", "true_peak", "streamed_bytes"]
+        return dict(zip(keys, [int(v) for v in out]))
+
+    def device_ptr(self, buf: Buf) -> int:
+        p = C.c_void_p()
+        _check(self.lib.tnf_buf_ptr(self._ctx, buf.id, C.byref(p), None))
+        return int(p.value) + buf.offset
+
+    def streams(self):
+        a, b = C.c_void_p(), C.c_void_p()
+        _check(self.lib.tnf_streams(self._ctx, C.byref(a), C.byref(b)))
+        return int(a.value), int(b.value)
+
+    def scope(self) -> "BatchScope":
+        return BatchScope(self)
+
+
+def device_scales_bytes(rows: int, k: int) -> int:
+    return int(L.load().tnf_device_scales_bytes(rows, k))
+
+
+@dataclass
+class Nvfp4Weight:
+    """A linear's resident weight: E2M1 codes [n,k/2], device-layout E4M3 scales, f32 scale, bias."""
+    n: int
+    k: int
+    codes: Buf
+    scales_device: Buf
+    global_scale: float
+    bias: Optional[Buf] = None
+    scales_canonical: Optional[Buf] = None
+
+    @staticmethod
+    def from_dense(be: Backend, w: np.ndarray, bias_bf16: Optional[np.ndarray] = None,
+                   keep_canonical: bool = False) -> "Nvfp4Weight":
+        """Quantise a dense [n,k] weight (float32, or bf16 bits as uint16) on the device."""
+        n, k = w.shape
+        dtype = L.DTYPE_BF16 if w.dtype == np.uint16 else L.DTYPE_F32
+        if dtype == L.DTYPE_F32:
+            w = w.astype(np.float32, copy=False)
+        src = be.upload(w, L.CAT_STAGING)
+        codes = be.allocate_in(n * k // 2, L.CAT_WEIGHTS)
+        canon = be.allocate_in(max(n * k // 16, 16), L.CAT_WEIGHTS if keep_canonical else L.CAT_STAGING)
+        g = C.c_float()
+        _check(be.lib.tnf_quantize_weight(be._ctx, src, dtype, n, k, codes, canon, C.byref(g)))
+        dev = be.allocate_in(device_scales_bytes(n, k), L.CAT_WEIGHTS)
+        _check(be.lib.tnf_prepare_scales(be._ctx, canon, n, k, dev))
+        be.submit()
+        be.free(src)
+        if not keep_canonical:
+            be.free(canon)
+            canon = None
+        bias = be.upload(bias_bf16.astype(np.uint16, copy=False), L.CAT_WEIGHTS) if bias_bf16 is not None else None
+        return Nvfp4Weight(n, k, codes, dev, float(g.value), bias, canon)
+
+    @staticmethod
+    def from_packed(be: Backend, codes: np.ndarray, scales_canonical: np.ndarray, global_scale: float,
+                    bias_bf16: Optional[np.ndarray] = None) -> "Nvfp4Weight":
+        """Upload an already quantised weight (canonical layouts)."""
+        n, k = codes.shape[0], codes.shape[1] * 2
+        cb = be.upload(codes.astype(np.uint8, copy=False), L.CAT_WEIGHTS)
+        canon = be.upload(scales_canonical.astype(np.uint8, copy=False), L.CAT_STAGING)
+        dev = be.allocate_in(device_scales_bytes(n, k), L.CAT_WEIGHTS)
+        _check(be.lib.tnf_prepare_scales(be._ctx, canon, n, k, dev))
+        be.submit()
+        be.free(canon)
+        bias = be.upload(bias_bf16.astype(np.uint16, copy=False), L.CAT_WEIGHTS) if bias_bf16 is not None else None
+        return Nvfp4Weight(n, k, cb, dev, float(global_scale), bias, None)
+
+    def free(self, be: Backend) -> None:
+        for b in (self.codes, self.scales_device, self.bias, self.scales_canonical):
+            if b is not None:
+                be.free(b)
+
+
+class BatchScope:
+    """Op surface used by the linear call sites; launches are asynchronous until ``submit``."""
+
+    def __init__(self, backend: Backend):
+        self.be = backend
+
+    def act_quant(self, a_bf16: Buf, m: int, k: int, global_scale: float = 0.0, device_layout: bool = False):
+        """Per-row per-16 NVFP4 activation quantiser. Returns (codes, scales, global_scale_used)."""
+        be = self.be
+        codes = be.allocate(m * k // 2)
+        nscale = device_scales_bytes(m, k) if device_layout else max(m * k // 16, 16)
+        scales = be.allocate(nscale)
+        g = C.c_float()
+        _check(be.lib.tnf_quantize_act(be._ctx, a_bf16, m, k, global_scale,
+                                       L.SCALES_DEVICE if device_layout else L.SCALES_CANONICAL, codes, scales,
+                                       C.byref(g)))
+        return codes, scales, float(g.value)
+
+    def act_quant_shared(self, a_bf16: Buf, m: int, k: int, global_scale: float) -> None:
+        _check(self.be.lib.tnf_quantize_act_shared(self.be._ctx, a_bf16, m, k, global_scale))
+
+    def _args(self, m, w: Nvfp4Weight, a, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias):
+        args = LinearArgs()
+        args.m, args.n, args.k = m, w.n, w.k
+        args.a_global, args.w_global = a_global, w.global_scale
+        args.a_bf16 = a if a is not None else _NONE
+        args.w_codes, args.w_scales = w.codes, w.scales_device
+        use_bias = w.bias if bias is None else (None if bias is False else bias)
+        args.bias_bf16 = use_bias if use_bias is not None else _NONE
+        args.gate_bf16 = gate if gate is not None else _NONE
+        args.residual_bf16 = residual if residual is not None else _NONE
+        args.out_bf16 = out
+        args.act, args.parity_mode = act, int(chain)
+        args.n_offset, args.ldo, args.flags = n_offset, ldo, flags
+        return args
+
+    def linear(self, a_bf16: Optional[Buf], m: int, w: Nvfp4Weight, a_global: float, out: Buf, act: int = L.ACT_NONE,
+               gate: Optional[Buf] = None, residual: Optional[Buf] = None, chain: bool = False, n_offset: int = 0,
+               ldo: int = 0, flags: int = 0, bias=None) -> None:
+        """out = epilogue(a_global*w_global * (quant(A) . Wq^T)): the ``biased`` call site, fused."""
+        args = self._args(m, w, a_bf16, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias)
+        _check(self.be.lib.tnf_linear_nvfp4(self.be._ctx, C.byref(args)))
+
+    def matmul(self, a_codes: Buf, a_scales_device: Buf, m: int, w: Nvfp4Weight, a_global: float, out: Buf,
+               act: int = L.ACT_NONE, gate=None, residual=None, chain: bool = False, n_offset: int = 0, ldo: int = 0,
+               flags: int = 0, bias=None) -> None:
+        """The GEMM alone on pre-quantised operands."""
+        args = self._args(m, w, None, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias)
+        _check(self.be.lib.tnf_gemm_nvfp4(self.be._ctx, C.byref(args), a_codes, a_scales_device))
+
+    def submit(self, timeout_ms: int = 0) -> None:
+        self.be.submit(timeout_ms)

@@ -1,0 +1,747 @@
+// C ABI of the NVFP4 linear path: context, buffers, quantisers, the linear, uploads.
+// See include/thinfer_nvfp4.h for the reference interface each entry point replaces.
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <thread>
+
+#include "context.h"
+
+namespace tnf {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+  set_error("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return e == cudaErrorMemoryAllocation ? TNF_ERR_ALLOCATE_OOM : TNF_ERR_LAUNCH;
+}
+
+#define TNF_CUDA(call, what)                               \
+  do {                                                     \
+    cudaError_t _e = (call);                               \
+    if (_e != cudaSuccess) return tnf::cuda_fail(_e, what); \
+  } while (0)
+
+#define TNF_CHECK_CTX(ctx)                          \
+  do {                                              \
+    if (!(ctx)) {                                   \
+      tnf::set_error("null context");               \
+      return TNF_ERR_INVALID_ARGUMENT;              \
+    }                                               \
+    cudaError_t _e = cudaSetDevice((ctx)->device);  \
+    if (_e != cudaSuccess) return tnf::cuda_fail(_e, "cudaSetDevice"); \
+  } while (0)
+
+uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need, const char* name, int32_t* status) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->bufs.find(b.id);
+  if (it == ctx->bufs.end()) {
+    set_error("%s: unknown buffer id %llu", name, (unsigned long long)b.id);
+    *status = TNF_ERR_UNKNOWN_BUFFER;
+    return nullptr;
+  }
+  if (b.offset > it->second.bytes || b.len > it->second.bytes - b.offset || need > b.len) {
+    set_error("%s: view {off %llu, len %llu} needs %llu bytes, buffer has %llu", name, (unsigned long long)b.offset,
+              (unsigned long long)b.len, (unsigned long long)need, (unsigned long long)it->second.bytes);
+    *status = TNF_ERR_INVALID_ARGUMENT;
+    return nullptr;
+  }
+  if (b.offset % 16 != 0) {
+    set_error("%s: view offset %llu is not 16-byte aligned", name, (unsigned long long)b.offset);
+    *status = TNF_ERR_INVALID_ARGUMENT;
+    return nullptr;
+  }
+  return static_cast<uint8_t*>(it->second.ptr) + b.offset;
+}
+
+int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id) {
+  if (category < 0 || category > 2 || bytes == 0) {
+    set_error("tnf_alloc: bad category %d or zero size", category);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  uint64_t total = ctx->live[0] + ctx->live[1] + ctx->live[2];
+  if (ctx->budget && total + bytes > ctx->budget) {
+    // refused on the host; the device is not touched
+    set_error("budget exceeded: live %llu + request %llu > budget %llu", (unsigned long long)total,
+              (unsigned long long)bytes, (unsigned long long)ctx->budget);
+    return TNF_ERR_BUDGET_EXCEEDED;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return cuda_fail(e, "cudaMalloc");
+  }
+  uint64_t nid = ctx->next_id++;
+  ctx->bufs[nid] = tnf_buffer_rec{p, bytes, category};
+  ctx->live[category] += bytes;
+  ctx->peak[category] = std::max(ctx->peak[category], ctx->live[category]);
+  ctx->true_peak = std::max(ctx->true_peak, total + bytes);
+  *id = nid;
+  return TNF_OK;
+}
+
+int32_t free_locked(tnf_ctx* ctx, uint64_t id) {
+  auto it = ctx->bufs.find(id);
+  if (it == ctx->bufs.end()) {
+    set_error("tnf_free: unknown buffer id %llu", (unsigned long long)id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  // cudaFree waits for work that may still use the memory
+  cudaError_t e = cudaFree(it->second.ptr);
+  ctx->live[it->second.category] -= it->second.bytes;
+  // tensor maps over the freed range are dropped (a later buffer may reuse the address)
+  for (auto m = ctx->maps.begin(); m != ctx->maps.end();) {
+    const uint8_t* b = static_cast<const uint8_t*>(m->first.base);
+    const uint8_t* lo = static_cast<const uint8_t*>(it->second.ptr);
+    if (b >= lo && b < lo + it->second.bytes) m = ctx->maps.erase(m);
+    else ++m;
+  }
+  ctx->bufs.erase(it);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFree");
+  return TNF_OK;
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_fn get_encode_fn() {
+  static encode_tiled_fn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_tiled_fn>(p);
+  }
+  return fn;
+}
+
+int make_codes_tensor_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+  encode_tiled_fn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver");
+    return TNF_ERR_LAUNCH;
+  }
+  cuuint64_t gdim[2] = {k / 2, rows};
+  cuuint64_t gstride[1] = {k / 2};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p rows %u k %u box %u)", int(r), base, rows, k,
+              box_rows);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  return TNF_OK;
+}
+
+const CUtensorMap* get_map(tnf_ctx* ctx, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  tnf_map_key key{base, rows, k, box_rows};
+  auto it = ctx->maps.find(key);
+  if (it != ctx->maps.end()) return &it->second;
+  CUtensorMap m;
+  if (make_codes_tensor_map(&m, base, rows, k, box_rows) != TNF_OK) return nullptr;
+  if (ctx->maps.size() > 4096) ctx->maps.clear();
+  return &(ctx->maps[key] = m);
+}
+
+static int32_t ensure_scratch(tnf_ctx* ctx, uint32_t m, uint32_t k) {
+  uint64_t need_codes = uint64_t(m) * (k / 2), need_scales = sf_device_bytes(m, k);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (need_codes > ctx->scratch_codes_bytes) {
+    if (ctx->scratch_codes_id) free_locked(ctx, ctx->scratch_codes_id);
+    ctx->scratch_codes_id = 0;
+    ctx->scratch_codes_bytes = 0;
+    int32_t st = alloc_locked(ctx, need_codes, TNF_CAT_WORKSPACE, &ctx->scratch_codes_id);
+    if (st != TNF_OK) return st;
+    ctx->scratch_codes_bytes = need_codes;
+  }
+  if (need_scales > ctx->scratch_scales_bytes) {
+    if (ctx->scratch_scales_id) free_locked(ctx, ctx->scratch_scales_id);
+    ctx->scratch_scales_id = 0;
+    ctx->scratch_scales_bytes = 0;
+    int32_t st = alloc_locked(ctx, need_scales, TNF_CAT_WORKSPACE, &ctx->scratch_scales_id);
+    if (st != TNF_OK) return st;
+    ctx->scratch_scales_bytes = need_scales;
+  }
+  return TNF_OK;
+}
+
+static int32_t check_dims(uint32_t m, uint32_t n, uint32_t k) {
+  if (m == 0 || n == 0 || k == 0) {
+    set_error("empty problem m=%u n=%u k=%u", m, n, k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (k % 32 != 0) {
+    set_error("k=%u must be a multiple of 32 (16-byte rows of packed codes)", k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (n % 8 != 0) {
+    set_error("n=%u must be a multiple of 8 (16-byte output vectors)", n);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  return TNF_OK;
+}
+
+// shared tail of tnf_linear_nvfp4 / tnf_gemm_nvfp4
+static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales) {
+  int32_t st = TNF_OK;
+  const uint32_t ldo = a->ldo ? a->ldo : a->n;
+  if (ldo % 8 != 0 || a->n_offset % 8 != 0 || a->n_offset + a->n > ldo) {
+    set_error("bad output window: n_offset %u + n %u within ldo %u, all multiples of 8", a->n_offset, a->n, ldo);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  uint8_t* w_codes = resolve(ctx, a->w_codes, uint64_t(a->n) * (a->k / 2), "w_codes", &st);
+  if (!w_codes) return st;
+  uint8_t* w_scales = resolve(ctx, a->w_scales, sf_device_bytes(a->n, a->k), "w_scales", &st);
+  if (!w_scales) return st;
+  uint8_t* out = resolve(ctx, a->out_bf16, (uint64_t(a->m - 1) * ldo + a->n_offset + a->n) * 2, "out_bf16", &st);
+  if (!out) return st;
+  GemmParams p{};
+  p.m = a->m; p.n = a->n; p.k = a->k;
+  p.k_atoms = sf_k_atoms(a->k);
+  p.alpha = a->a_global * a->w_global;
+  p.sfa = a_scales;
+  p.sfb = w_scales;
+  if (a->bias_bf16.len) {
+    p.bias = reinterpret_cast<const uint16_t*>(resolve(ctx, a->bias_bf16, uint64_t(a->n) * 2, "bias_bf16", &st));
+    if (!p.bias) return st;
+  }
+  if (a->gate_bf16.len) {
+    p.gate = reinterpret_cast<const uint16_t*>(resolve(ctx, a->gate_bf16, uint64_t(a->n) * 2, "gate_bf16", &st));
+    if (!p.gate) return st;
+    p.residual = reinterpret_cast<const uint16_t*>(
+        resolve(ctx, a->residual_bf16, uint64_t(a->m) * a->n * 2, "residual_bf16", &st));
+    if (!p.residual) return st;
+  }
+  p.out[0] = reinterpret_cast<uint16_t*>(out);
+  p.n_out = 1;
+  if (a->flags & TNF_LINEAR_SCATTER_PEERS) {
+    if (ctx->n_peers <= 0) {
+      set_error("TNF_LINEAR_SCATTER_PEERS without tnf_peer_outputs");
+      return TNF_ERR_INVALID_ARGUMENT;
+    }
+    for (int i = 0; i < ctx->n_peers; ++i) p.out[p.n_out++] = reinterpret_cast<uint16_t*>(ctx->peer_out[i]);
+  }
+  p.ldo = ldo;
+  p.n_offset = a->n_offset;
+  p.act = a->act;
+  p.chain = a->parity_mode;
+  p.status = ctx->dwords;
+  const CUtensorMap* ma = get_map(ctx, a_codes, a->m, a->k, 128);
+  const CUtensorMap* mw = get_map(ctx, w_codes, a->n, a->k, gemm_tile_n(a->n));
+  if (!ma || !mw) return TNF_ERR_INVALID_ARGUMENT;
+  TNF_CUDA(launch_gemm_nvfp4(*ma, *mw, p, ctx->sm_count, ctx->compute), "nvfp4 gemm launch");
+  return TNF_OK;
+}
+
+}  // namespace tnf
+
+using namespace tnf;
+
+extern "C" {
+
+uint32_t tnf_abi_version(void) { return 1; }
+const char* tnf_last_error(void) { return g_err; }
+
+int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out) {
+  if (!out) {
+    set_error("tnf_create: null out");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    set_error("no CUDA device is visible (%s); this library has no CPU path", cudaGetErrorString(e));
+    return TNF_ERR_LAUNCH;
+  }
+  if (device < 0 || device >= count) {
+    set_error("device %d out of range (0..%d)", device, count - 1);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  TNF_CUDA(cudaSetDevice(device), "cudaSetDevice");
+  cudaDeviceProp prop;
+  TNF_CUDA(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+  if (prop.major != 10) {
+    set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    return TNF_ERR_LAUNCH;
+  }
+  tnf_ctx* ctx = new tnf_ctx();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->budget = vram_budget_bytes;
+  TNF_CUDA(cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking), "cudaStreamCreate");
+  TNF_CUDA(cudaStreamCreateWithFlags(&ctx->copy, cudaStreamNonBlocking), "cudaStreamCreate");
+  TNF_CUDA(cudaMalloc(&ctx->dwords, 64), "cudaMalloc(status words)");
+  TNF_CUDA(cudaMemset(ctx->dwords, 0, 64), "cudaMemset(status words)");
+  *out = ctx;
+  return TNF_OK;
+}
+
+int32_t tnf_destroy(tnf_ctx* ctx) {
+  if (!ctx) return TNF_OK;
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  extern void tnf_comm_teardown(tnf_ctx*);
+  tnf_comm_teardown(ctx);
+  for (auto& kv : ctx->bufs) cudaFree(kv.second.ptr);
+  for (auto& kv : ctx->hosts) {
+    if (kv.second.owned) cudaFreeHost(kv.second.ptr);
+    else cudaHostUnregister(kv.second.ptr);
+  }
+  for (auto& kv : ctx->events) cudaEventDestroy(kv.second);
+  for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
+  cudaFree(ctx->dwords);
+  cudaStreamDestroy(ctx->compute);
+  cudaStreamDestroy(ctx->copy);
+  cudaGetLastError();
+  delete ctx;
+  return TNF_OK;
+}
+
+int32_t tnf_alloc(tnf_ctx* ctx, uint64_t bytes, int32_t category, uint64_t* id) {
+  TNF_CHECK_CTX(ctx);
+  if (!id) {
+    set_error("tnf_alloc: null id");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  return alloc_locked(ctx, bytes, category, id);
+}
+
+int32_t tnf_free(tnf_ctx* ctx, uint64_t id) {
+  TNF_CHECK_CTX(ctx);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  return free_locked(ctx, id);
+}
+
+static int32_t raw_range(tnf_ctx* ctx, uint64_t id, uint64_t off, uint64_t n, const char* what, uint8_t** p) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->bufs.find(id);
+  if (it == ctx->bufs.end()) {
+    set_error("%s: unknown buffer id %llu", what, (unsigned long long)id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  if (off > it->second.bytes || n > it->second.bytes - off) {
+    set_error("%s: range [%llu, +%llu) outside buffer of %llu bytes", what, (unsigned long long)off,
+              (unsigned long long)n, (unsigned long long)it->second.bytes);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  *p = static_cast<uint8_t*>(it->second.ptr) + off;
+  return TNF_OK;
+}
+
+int32_t tnf_write(tnf_ctx* ctx, uint64_t id, uint64_t dst_off, const void* src, uint64_t n) {
+  TNF_CHECK_CTX(ctx);
+  if (dst_off % 4 || n % 4) {  // same rule as Backend::write_buffer
+    set_error("tnf_write: offset %llu and length %llu must be multiples of 4", (unsigned long long)dst_off,
+              (unsigned long long)n);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (n == 0) return TNF_OK;
+  uint8_t* p = nullptr;
+  int32_t st = raw_range(ctx, id, dst_off, n, "tnf_write", &p);
+  if (st != TNF_OK) return st;
+  TNF_CUDA(cudaMemcpyAsync(p, src, n, cudaMemcpyHostToDevice, ctx->compute), "tnf_write copy");
+  // pageable sources are staged before the call returns; pinned ones are not, so wait
+  TNF_CUDA(cudaStreamSynchronize(ctx->compute), "tnf_write sync");
+  return TNF_OK;
+}
+
+int32_t tnf_read(tnf_ctx* ctx, uint64_t id, uint64_t off, void* dst, uint64_t n) {
+  TNF_CHECK_CTX(ctx);
+  if (n == 0) return TNF_OK;
+  uint8_t* p = nullptr;
+  int32_t st = raw_range(ctx, id, off, n, "tnf_read", &p);
+  if (st != TNF_OK) return st;
+  TNF_CUDA(cudaMemcpyAsync(dst, p, n, cudaMemcpyDeviceToHost, ctx->compute), "tnf_read copy");
+  TNF_CUDA(cudaStreamSynchronize(ctx->compute), "tnf_read sync");
+  return TNF_OK;
+}
+
+int32_t tnf_copy(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uint64_t dst_id, uint64_t dst_off, uint64_t n) {
+  TNF_CHECK_CTX(ctx);
+  if (n == 0) return TNF_OK;
+  uint8_t *s = nullptr, *d = nullptr;
+  int32_t st = raw_range(ctx, src_id, src_off, n, "tnf_copy src", &s);
+  if (st != TNF_OK) return st;
+  st = raw_range(ctx, dst_id, dst_off, n, "tnf_copy dst", &d);
+  if (st != TNF_OK) return st;
+  TNF_CUDA(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, ctx->compute), "tnf_copy");
+  return TNF_OK;
+}
+
+int32_t tnf_buf_ptr(tnf_ctx* ctx, uint64_t id, void** device_ptr, uint64_t* bytes) {
+  TNF_CHECK_CTX(ctx);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->bufs.find(id);
+  if (it == ctx->bufs.end()) {
+    set_error("tnf_buf_ptr: unknown buffer id %llu", (unsigned long long)id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  if (device_ptr) *device_ptr = it->second.ptr;
+  if (bytes) *bytes = it->second.bytes;
+  return TNF_OK;
+}
+
+int32_t tnf_streams(tnf_ctx* ctx, void** compute_stream, void** copy_stream) {
+  TNF_CHECK_CTX(ctx);
+  if (compute_stream) *compute_stream = ctx->compute;
+  if (copy_stream) *copy_stream = ctx->copy;
+  return TNF_OK;
+}
+
+int32_t tnf_sync(tnf_ctx* ctx, uint32_t timeout_ms) {
+  TNF_CHECK_CTX(ctx);
+  cudaStream_t streams[2] = {ctx->compute, ctx->copy};
+  auto t0 = std::chrono::steady_clock::now();
+  for (cudaStream_t s : streams) {
+    if (timeout_ms == 0) {
+      TNF_CUDA(cudaStreamSynchronize(s), "tnf_sync");
+    } else {
+      while (true) {
+        cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) break;
+        if (e != cudaErrorNotReady) return cuda_fail(e, "tnf_sync");
+        auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > timeout_ms) {
+          set_error("tnf_sync: work still running after %u ms", timeout_ms);
+          return TNF_ERR_TIMEOUT;
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+      }
+    }
+  }
+  uint32_t status = 0;
+  TNF_CUDA(cudaMemcpy(&status, ctx->dwords, 4, cudaMemcpyDeviceToHost), "tnf_sync status read");
+  if (status != 0) {
+    cudaMemset(ctx->dwords, 0, 4);
+    static const char* names[] = {"ok", "producer wait on a free stage", "MMA wait on a loaded stage",
+                                  "epilogue wait on the accumulator", "MMA wait on a drained accumulator"};
+    set_error("a device-side wait gave up: %s (code %u)", status < 5 ? names[status] : "unknown", status);
+    return TNF_ERR_TIMEOUT;
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]) {
+  if (!ctx || !out) {
+    set_error("tnf_mem_snapshot: null argument");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  for (int i = 0; i < 3; ++i) {
+    out[i] = ctx->live[i];
+    out[3 + i] = ctx->peak[i];
+  }
+  out[6] = ctx->true_peak;
+  out[7] = ctx->streamed;
+  return TNF_OK;
+}
+
+// ---- quantisers ----------------------------------------------------------------------------------
+
+uint64_t tnf_device_scales_bytes(uint32_t rows, uint32_t k) { return sf_device_bytes(rows, k); }
+
+int32_t tnf_quantize_weight(tnf_ctx* ctx, tnf_buf w_src, int32_t src_dtype, uint32_t n, uint32_t k, tnf_buf codes,
+                            tnf_buf scales, float* global_scale) {
+  TNF_CHECK_CTX(ctx);
+  if (n == 0 || k == 0 || k % 32 != 0 || (src_dtype != TNF_DTYPE_F32 && src_dtype != TNF_DTYPE_BF16)) {
+    set_error("tnf_quantize_weight: n=%u k=%u (k %% 32 == 0) dtype=%d", n, k, src_dtype);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  const uint64_t esz = src_dtype == TNF_DTYPE_BF16 ? 2 : 4;
+  uint8_t* src = resolve(ctx, w_src, uint64_t(n) * k * esz, "w_src", &st);
+  if (!src) return st;
+  uint8_t* c = resolve(ctx, codes, uint64_t(n) * (k / 2), "codes", &st);
+  if (!c) return st;
+  uint8_t* s = resolve(ctx, scales, uint64_t(n) * (k / 16), "scales", &st);
+  if (!s) return st;
+  float* g = reinterpret_cast<float*>(ctx->dwords + 2);
+  TNF_CUDA(launch_amax(src, src_dtype, uint64_t(n) * k, ctx->dwords + 1, ctx->compute), "amax launch");
+  TNF_CUDA(launch_global_scale(ctx->dwords + 1, g, ctx->compute), "global scale launch");
+  TNF_CUDA(launch_quantize(src, src_dtype, n, k, g, 0.0f, c, s, false, ctx->compute), "weight quantise launch");
+  if (global_scale) {
+    TNF_CUDA(cudaMemcpyAsync(global_scale, g, 4, cudaMemcpyDeviceToHost, ctx->compute), "global scale read");
+    TNF_CUDA(cudaStreamSynchronize(ctx->compute), "tnf_quantize_weight sync");
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_prepare_scales(tnf_ctx* ctx, tnf_buf scales_canonical, uint32_t rows, uint32_t k, tnf_buf scales_device) {
+  TNF_CHECK_CTX(ctx);
+  if (rows == 0 || k == 0 || k % 16 != 0) {
+    set_error("tnf_prepare_scales: rows=%u k=%u", rows, k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  uint8_t* in = resolve(ctx, scales_canonical, uint64_t(rows) * (k / 16), "scales_canonical", &st);
+  if (!in) return st;
+  uint8_t* out = resolve(ctx, scales_device, sf_device_bytes(rows, k), "scales_device", &st);
+  if (!out) return st;
+  TNF_CUDA(launch_scales_to_device(in, rows, k, out, ctx->compute), "scale layout launch");
+  return TNF_OK;
+}
+
+static int32_t quantize_act_impl(tnf_ctx* ctx, const uint8_t* a, uint32_t m, uint32_t k, float g, bool device_layout,
+                                 uint8_t* codes, uint8_t* scales, float* g_used) {
+  const float* g_ptr = nullptr;
+  if (!(g > 0.0f)) {
+    float* gd = reinterpret_cast<float*>(ctx->dwords + 2);
+    TNF_CUDA(launch_amax(a, TNF_DTYPE_BF16, uint64_t(m) * k, ctx->dwords + 1, ctx->compute), "amax launch");
+    TNF_CUDA(launch_global_scale(ctx->dwords + 1, gd, ctx->compute), "global scale launch");
+    g_ptr = gd;
+  }
+  TNF_CUDA(launch_quantize(a, TNF_DTYPE_BF16, m, k, g_ptr, g, codes, scales, device_layout, ctx->compute),
+           "activation quantise launch");
+  if (g_used) {
+    if (g_ptr) {
+      TNF_CUDA(cudaMemcpyAsync(g_used, g_ptr, 4, cudaMemcpyDeviceToHost, ctx->compute), "global scale read");
+      TNF_CUDA(cudaStreamSynchronize(ctx->compute), "tnf_quantize_act sync");
+    } else {
+      *g_used = g;
+    }
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_quantize_act(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32_t k, float global_scale,
+                         int32_t scales_layout, tnf_buf codes, tnf_buf scales, float* global_scale_used) {
+  TNF_CHECK_CTX(ctx);
+  if (m == 0 || k == 0 || k % 32 != 0) {
+    set_error("tnf_quantize_act: m=%u k=%u (k %% 32 == 0)", m, k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  const bool dev = scales_layout == TNF_SCALES_DEVICE;
+  uint8_t* a = resolve(ctx, a_bf16, uint64_t(m) * k * 2, "a_bf16", &st);
+  if (!a) return st;
+  uint8_t* c = resolve(ctx, codes, uint64_t(m) * (k / 2), "codes", &st);
+  if (!c) return st;
+  uint8_t* s = resolve(ctx, scales, dev ? sf_device_bytes(m, k) : uint64_t(m) * (k / 16), "scales", &st);
+  if (!s) return st;
+  return quantize_act_impl(ctx, a, m, k, global_scale, dev, c, s, global_scale_used);
+}
+
+int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32_t k, float global_scale) {
+  TNF_CHECK_CTX(ctx);
+  if (m == 0 || k == 0 || k % 32 != 0 || !(global_scale > 0.0f)) {
+    set_error("tnf_quantize_act_shared: m=%u k=%u (k %% 32 == 0), global_scale must be > 0", m, k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  uint8_t* a = resolve(ctx, a_bf16, uint64_t(m) * k * 2, "a_bf16", &st);
+  if (!a) return st;
+  st = ensure_scratch(ctx, m, k);
+  if (st != TNF_OK) return st;
+  return quantize_act_impl(ctx, a, m, k, global_scale, true, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
+                           static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr);
+}
+
+// ---- the linear ------------------------------------------------------------------------------------
+
+int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
+  TNF_CHECK_CTX(ctx);
+  if (!a) {
+    set_error("tnf_linear_nvfp4: null args");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = check_dims(a->m, a->n, a->k);
+  if (st != TNF_OK) return st;
+  if (!(a->a_global > 0.0f) || !(a->w_global > 0.0f) || a->act > 1 || a->parity_mode > 1) {
+    set_error("tnf_linear_nvfp4: scales must be > 0 (a %g, w %g), act %u, parity_mode %u", a->a_global, a->w_global,
+              a->act, a->parity_mode);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (!(a->flags & TNF_LINEAR_A_PREQUANTIZED)) {
+    uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
+    if (!src) return st;
+    st = ensure_scratch(ctx, a->m, a->k);
+    if (st != TNF_OK) return st;
+    st = quantize_act_impl(ctx, src, a->m, a->k, a->a_global, true,
+                           static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
+                           static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr);
+    if (st != TNF_OK) return st;
+  } else if (uint64_t(a->m) * (a->k / 2) > ctx->scratch_codes_bytes) {
+    set_error("TNF_LINEAR_A_PREQUANTIZED: tnf_quantize_act_shared has not been called for m=%u k=%u", a->m, a->k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  return run_gemm(ctx, a, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
+                  static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr));
+}
+
+int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a, tnf_buf a_codes, tnf_buf a_scales_device) {
+  TNF_CHECK_CTX(ctx);
+  if (!a) {
+    set_error("tnf_gemm_nvfp4: null args");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = check_dims(a->m, a->n, a->k);
+  if (st != TNF_OK) return st;
+  if (!(a->a_global > 0.0f) || !(a->w_global > 0.0f) || a->act > 1 || a->parity_mode > 1) {
+    set_error("tnf_gemm_nvfp4: scales must be > 0, act <= 1, parity_mode <= 1");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  uint8_t* c = resolve(ctx, a_codes, uint64_t(a->m) * (a->k / 2), "a_codes", &st);
+  if (!c) return st;
+  uint8_t* s = resolve(ctx, a_scales_device, sf_device_bytes(a->m, a->k), "a_scales_device", &st);
+  if (!s) return st;
+  return run_gemm(ctx, a, c, s);
+}
+
+// ---- pinned host arenas and uploads -------------------------------------------------------------------
+
+int32_t tnf_host_register(tnf_ctx* ctx, void* host_ptr, uint64_t bytes, uint64_t* host_id) {
+  TNF_CHECK_CTX(ctx);
+  if (!host_id || bytes == 0) {
+    set_error("tnf_host_register: null id or zero size");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  tnf_host_rec rec;
+  rec.bytes = bytes;
+  if (host_ptr) {
+    TNF_CUDA(cudaHostRegister(host_ptr, bytes, cudaHostRegisterDefault), "cudaHostRegister");
+    rec.ptr = host_ptr;
+    rec.owned = false;
+  } else {
+    TNF_CUDA(cudaHostAlloc(&rec.ptr, bytes, cudaHostAllocDefault), "cudaHostAlloc");
+    rec.owned = true;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  uint64_t id = ctx->next_id++;
+  ctx->hosts[id] = rec;
+  *host_id = id;
+  return TNF_OK;
+}
+
+int32_t tnf_host_ptr(tnf_ctx* ctx, uint64_t host_id, void** ptr, uint64_t* bytes) {
+  if (!ctx) {
+    set_error("null context");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->hosts.find(host_id);
+  if (it == ctx->hosts.end()) {
+    set_error("tnf_host_ptr: unknown host arena %llu", (unsigned long long)host_id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  if (ptr) *ptr = it->second.ptr;
+  if (bytes) *bytes = it->second.bytes;
+  return TNF_OK;
+}
+
+int32_t tnf_host_release(tnf_ctx* ctx, uint64_t host_id) {
+  TNF_CHECK_CTX(ctx);
+  TNF_CUDA(cudaStreamSynchronize(ctx->copy), "tnf_host_release sync");
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->hosts.find(host_id);
+  if (it == ctx->hosts.end()) {
+    set_error("tnf_host_release: unknown host arena %llu", (unsigned long long)host_id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  cudaError_t e = it->second.owned ? cudaFreeHost(it->second.ptr) : cudaHostUnregister(it->second.ptr);
+  ctx->hosts.erase(it);
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_host_release");
+  return TNF_OK;
+}
+
+int32_t tnf_stream_upload(tnf_ctx* ctx, uint64_t host_id, uint64_t host_off, uint64_t dst_id, uint64_t dst_off,
+                          uint64_t n, uint64_t* event) {
+  TNF_CHECK_CTX(ctx);
+  uint8_t* d = nullptr;
+  int32_t st = raw_range(ctx, dst_id, dst_off, n, "tnf_stream_upload dst", &d);
+  if (st != TNF_OK) return st;
+  const uint8_t* h = nullptr;
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->hosts.find(host_id);
+    if (it == ctx->hosts.end()) {
+      set_error("tnf_stream_upload: unknown host arena %llu", (unsigned long long)host_id);
+      return TNF_ERR_UNKNOWN_BUFFER;
+    }
+    if (host_off > it->second.bytes || n > it->second.bytes - host_off) {
+      set_error("tnf_stream_upload: host range [%llu, +%llu) outside arena of %llu bytes",
+                (unsigned long long)host_off, (unsigned long long)n, (unsigned long long)it->second.bytes);
+      return TNF_ERR_INVALID_ARGUMENT;
+    }
+    h = static_cast<const uint8_t*>(it->second.ptr) + host_off;
+    if (event) {
+      if (!ctx->event_pool.empty()) {
+        ev = ctx->event_pool.back();
+        ctx->event_pool.pop_back();
+      }
+    }
+    ctx->streamed += n;
+  }
+  if (n) TNF_CUDA(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, ctx->copy), "tnf_stream_upload copy");
+  if (event) {
+    if (!ev) TNF_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    TNF_CUDA(cudaEventRecord(ev, ctx->copy), "cudaEventRecord");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    uint64_t id = ctx->next_id++;
+    ctx->events[id] = ev;
+    *event = id;
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_wait_event(tnf_ctx* ctx, uint64_t event) {
+  TNF_CHECK_CTX(ctx);
+  cudaEvent_t ev;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->events.find(event);
+    if (it == ctx->events.end()) {
+      set_error("tnf_wait_event: unknown event %llu", (unsigned long long)event);
+      return TNF_ERR_UNKNOWN_BUFFER;
+    }
+    ev = it->second;
+    ctx->events.erase(it);
+  }
+  cudaError_t e = cudaStreamWaitEvent(ctx->compute, ev, 0);
+  {
+    // the wait has captured the event's current record; the object can be recycled
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->event_pool.push_back(ev);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+  return TNF_OK;
+}
+
+int32_t tnf_copy_after_compute(tnf_ctx* ctx) {
+  TNF_CHECK_CTX(ctx);
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->event_pool.empty()) {
+      ev = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    }
+  }
+  if (!ev) TNF_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+  TNF_CUDA(cudaEventRecord(ev, ctx->compute), "cudaEventRecord");
+  TNF_CUDA(cudaStreamWaitEvent(ctx->copy, ev, 0), "cudaStreamWaitEvent");
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  ctx->event_pool.push_back(ev);
+  return TNF_OK;
+}
+
+}  // extern "C"

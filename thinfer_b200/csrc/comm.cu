@@ -1,0 +1,236 @@
+// Multi-GPU side of the ABI: NCCL communicator (loaded at run time), the all-gather of an
+// N-split output, CUDA IPC windows for the fused epilogue scatter, a stream-ordered barrier.
+// The reference is single-device; the N-split with an all-gather of the output is what the
+// benchmark configuration adds. One process per GPU; NCCL is found with dlopen so that a
+// process that already loaded a libnccl (torch) shares it.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+
+#include "context.h"
+
+namespace tnf {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static NcclApi* nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api.handle ? &api : nullptr;
+  tried = true;
+  void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) {
+    set_error("libnccl.so.2 could not be loaded: %s", dlerror());
+    return nullptr;
+  }
+  api.handle = h;
+#define TNF_SYM(name)                                                           \
+  api.name = reinterpret_cast<decltype(api.name)>(dlsym(h, "nccl" #name));      \
+  if (!api.name) {                                                              \
+    set_error("libnccl.so.2 lacks nccl" #name);                                 \
+    api.handle = nullptr;                                                       \
+    return nullptr;                                                             \
+  }
+  TNF_SYM(GetUniqueId)
+  TNF_SYM(CommInitRank)
+  TNF_SYM(CommDestroy)
+  TNF_SYM(AllGather)
+  TNF_SYM(AllReduce)
+  TNF_SYM(GetErrorString)
+#undef TNF_SYM
+  return &api;
+}
+
+static int32_t nccl_fail(NcclApi* api, ncclResult_t r, const char* what) {
+  set_error("%s: %s", what, api->GetErrorString(r));
+  return TNF_ERR_NCCL;
+}
+
+// own column slice of out[m, n_total] -> contiguous [m, n_local]
+__global__ void pack_cols_kernel(const uint4* __restrict__ out, uint4* __restrict__ packed, uint32_t m,
+                                 uint32_t n_total8, uint32_t n_local8, uint32_t col0_8) {
+  uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= uint64_t(m) * n_local8) return;
+  uint32_t r = uint32_t(t / n_local8), c = uint32_t(t % n_local8);
+  packed[t] = out[uint64_t(r) * n_total8 + col0_8 + c];
+}
+// gathered [world, m, n_local] -> out[m, n_total], skipping this rank's own slice
+__global__ void unpack_cols_kernel(const uint4* __restrict__ gathered, uint4* __restrict__ out, uint32_t m,
+                                   uint32_t n_total8, uint32_t n_local8, uint32_t world, uint32_t self) {
+  uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= uint64_t(world) * m * n_local8) return;
+  uint32_t c = uint32_t(t % n_local8);
+  uint64_t q = t / n_local8;
+  uint32_t r = uint32_t(q % m), w = uint32_t(q / m);
+  if (w == self) return;
+  out[uint64_t(r) * n_total8 + uint64_t(w) * n_local8 + c] = gathered[t];
+}
+
+}  // namespace tnf
+
+using namespace tnf;
+
+void tnf_comm_teardown(tnf_ctx* ctx) {
+  if (ctx->nccl_comm) {
+    NcclApi* api = nccl_api();
+    if (api) api->CommDestroy(static_cast<ncclComm_t>(ctx->nccl_comm));
+    ctx->nccl_comm = nullptr;
+  }
+  for (int i = 0; i < ctx->n_peers; ++i)
+    if (ctx->peer_out[i]) cudaIpcCloseMemHandle(ctx->peer_out[i]);
+  ctx->n_peers = 0;
+  if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
+  ctx->gather_tmp = nullptr;
+}
+
+extern "C" {
+
+int32_t tnf_comm_unique_id(void* unique_id_128) {
+  NcclApi* api = nccl_api();
+  if (!api) return TNF_ERR_NCCL;
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  ncclUniqueId id;
+  ncclResult_t r = api->GetUniqueId(&id);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclGetUniqueId");
+  std::memcpy(unique_id_128, &id, 128);
+  return TNF_OK;
+}
+
+int32_t tnf_comm_init(tnf_ctx* ctx, int32_t world, int32_t rank, const void* unique_id_128) {
+  if (!ctx || !unique_id_128 || world < 1 || rank < 0 || rank >= world || world > kMaxPeers) {
+    set_error("tnf_comm_init: bad arguments (world %d, rank %d, at most %d ranks)", world, rank, kMaxPeers);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  NcclApi* api = nccl_api();
+  if (!api) return TNF_ERR_NCCL;
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  ncclUniqueId id;
+  std::memcpy(&id, unique_id_128, 128);
+  ncclComm_t comm;
+  ncclResult_t r = api->CommInitRank(&comm, world, id, rank);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclCommInitRank");
+  ctx->nccl_comm = comm;
+  ctx->world = world;
+  ctx->rank = rank;
+  return TNF_OK;
+}
+
+int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t n_total, uint32_t n_local) {
+  if (!ctx || !ctx->nccl_comm) {
+    set_error("tnf_all_gather_cols: no communicator (call tnf_comm_init)");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  if (n_local % 8 || n_total != n_local * uint32_t(ctx->world) || m == 0) {
+    set_error("tnf_all_gather_cols: n_total %u must be world %d x n_local %u, n_local a multiple of 8", n_total,
+              ctx->world, n_local);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  uint8_t* out = resolve(ctx, out_bf16, uint64_t(m) * n_total * 2, "out_bf16", &st);
+  if (!out) return st;
+  NcclApi* api = nccl_api();
+  const uint64_t slice = uint64_t(m) * n_local * 2;
+  const uint64_t need = slice * (uint64_t(ctx->world) + 1);
+  if (need > ctx->gather_tmp_bytes) {
+    if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
+    ctx->gather_tmp = nullptr;
+    ctx->gather_tmp_bytes = 0;
+    e = cudaMalloc(&ctx->gather_tmp, need);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
+    ctx->gather_tmp_bytes = need;
+  }
+  uint8_t* send = static_cast<uint8_t*>(ctx->gather_tmp);
+  uint8_t* recv = send + slice;
+  const uint32_t nl8 = n_local / 8, nt8 = n_total / 8;
+  uint64_t threads = uint64_t(m) * nl8;
+  pack_cols_kernel<<<unsigned((threads + 255) / 256), 256, 0, ctx->compute>>>(
+      reinterpret_cast<const uint4*>(out), reinterpret_cast<uint4*>(send), m, nt8, nl8, uint32_t(ctx->rank) * nl8);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pack launch");
+  ncclResult_t r = api->AllGather(send, recv, slice / 2, ncclBfloat16, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->compute);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllGather");
+  threads *= uint64_t(ctx->world);
+  unpack_cols_kernel<<<unsigned((threads + 255) / 256), 256, 0, ctx->compute>>>(
+      reinterpret_cast<const uint4*>(recv), reinterpret_cast<uint4*>(out), m, nt8, nl8, uint32_t(ctx->world),
+      uint32_t(ctx->rank));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
+  return TNF_OK;
+}
+
+int32_t tnf_ipc_export(tnf_ctx* ctx, uint64_t id, void* handle_64) {
+  if (!ctx || !handle_64) {
+    set_error("tnf_ipc_export: null argument");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  void* p = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->bufs.find(id);
+    if (it == ctx->bufs.end()) {
+      set_error("tnf_ipc_export: unknown buffer id %llu", (unsigned long long)id);
+      return TNF_ERR_UNKNOWN_BUFFER;
+    }
+    p = it->second.ptr;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is 64 bytes");
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaIpcGetMemHandle");
+  std::memcpy(handle_64, &h, 64);
+  return TNF_OK;
+}
+
+int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t n_peers, const void* handles_64xn) {
+  if (!ctx || n_peers < 0 || n_peers > kMaxPeers - 1 || (n_peers > 0 && !handles_64xn)) {
+    set_error("tnf_peer_outputs: bad arguments (n_peers %d, at most %d)", n_peers, kMaxPeers - 1);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  e = cudaStreamSynchronize(ctx->compute);
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_peer_outputs sync");
+  for (int i = 0; i < ctx->n_peers; ++i)
+    if (ctx->peer_out[i]) cudaIpcCloseMemHandle(ctx->peer_out[i]);
+  ctx->n_peers = 0;
+  for (int i = 0; i < n_peers; ++i) {
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const uint8_t*>(handles_64xn) + 64 * i, 64);
+    void* p = nullptr;
+    e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle");
+    ctx->peer_out[ctx->n_peers++] = p;
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_comm_barrier(tnf_ctx* ctx) {
+  if (!ctx || !ctx->nccl_comm) {
+    set_error("tnf_comm_barrier: no communicator (call tnf_comm_init)");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  NcclApi* api = nccl_api();
+  float* word = reinterpret_cast<float*>(ctx->dwords + 8);
+  ncclResult_t r = api->AllReduce(word, word, 1, ncclFloat, ncclSum, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->compute);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce (barrier)");
+  return TNF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,77 @@
+// The per-device context behind the C ABI: buffer table with category accounting, streams,
+// scratch, tensor-map cache, pinned host arenas, upload events. Internal to the library.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/thinfer_nvfp4.h"
+#include "internal.h"
+
+struct tnf_buffer_rec {
+  void* ptr = nullptr;
+  uint64_t bytes = 0;
+  int category = 0;
+};
+
+struct tnf_host_rec {
+  void* ptr = nullptr;
+  uint64_t bytes = 0;
+  bool owned = false;  // cudaHostAlloc'ed by us (else cudaHostRegister'ed in place)
+};
+
+struct tnf_map_key {
+  const void* base;
+  uint32_t rows, k, box_rows;
+  bool operator<(const tnf_map_key& o) const {
+    if (base != o.base) return base < o.base;
+    if (rows != o.rows) return rows < o.rows;
+    if (k != o.k) return k < o.k;
+    return box_rows < o.box_rows;
+  }
+};
+
+struct tnf_ctx {
+  int device = 0;
+  int sm_count = 148;
+  uint64_t budget = 0;
+  cudaStream_t compute = nullptr, copy = nullptr;
+  std::mutex mu;
+  uint64_t next_id = 1;
+  std::unordered_map<uint64_t, tnf_buffer_rec> bufs;
+  std::unordered_map<uint64_t, tnf_host_rec> hosts;
+  std::unordered_map<uint64_t, cudaEvent_t> events;
+  std::vector<cudaEvent_t> event_pool;
+  // MemAccount: live and peak per category, true concurrent peak, streamed bytes
+  uint64_t live[3] = {0, 0, 0}, peak[3] = {0, 0, 0}, true_peak = 0, streamed = 0;
+  // scratch for on-the-fly activation quantisation (workspace category)
+  uint64_t scratch_codes_id = 0, scratch_scales_id = 0;
+  uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;
+  // small device words: [0] kernel status, [1] amax bits, [2] global scale (f32)
+  uint32_t* dwords = nullptr;
+  std::map<tnf_map_key, CUtensorMap> maps;
+  // fused-scatter peer windows (opened CUDA IPC mappings), index 0 unused
+  void* peer_out[tnf::kMaxPeers] = {nullptr};
+  int n_peers = 0;
+  // NCCL
+  void* nccl_comm = nullptr;
+  int world = 1, rank = 0;
+  void* gather_tmp = nullptr;
+  uint64_t gather_tmp_bytes = 0;
+};
+
+namespace tnf {
+void set_error(const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what);
+// Looks a view up and checks its range; returns the device address or null (error set).
+uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need_bytes, const char* name, int32_t* status);
+int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id);
+int32_t free_locked(tnf_ctx* ctx, uint64_t id);
+const CUtensorMap* get_map(tnf_ctx* ctx, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows);
+}  // namespace tnf

@@ -1,0 +1,308 @@
+// NVFP4 GEMM for sm_100a: out[m,n] = epilogue(alpha * sum_k A[m,k] * W[n,k]) with E2M1
+// operands and one UE4M3 scale per 16 K-elements on both sides.
+//
+// Replaces the reference's dequant + matmul / matmul_i8 dispatches and the bias / GELU /
+// gated-residual dispatches after them (thinfer-core/src/ops/matmul.rs:150-749,
+// matmul_i8.rs:196-393, bcast_add.rs, gelu.rs:21-31, bcast_fma.rs) with one kernel.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0     TMA producer: per 256-element K tile, one 2-D tensor-map load each for the A
+//              and W code tiles (128-byte rows, 128-byte swizzle) and untiled bulk copies of
+//              the matching 512-byte scale atoms, all completing on the stage's mbarrier.
+//   warp 1     owns TMEM; one lane copies the scale atoms shared->TMEM (tcgen05.cp) and issues
+//              tcgen05.mma kind::mxf4nvf4 block16, four K=64 steps per stage; tcgen05.commit
+//              frees the stage and, after the last K tile, publishes the accumulator.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32-lane quarter),
+//              alpha, bias, tanh-GELU, gated residual, bf16 RNE, 16-byte stores to the local
+//              output and to any peer windows.
+// Every mbarrier wait is bounded; a wait that gives up raises a CTA-wide abort flag, records
+// a status code for the host and every role falls through to the common tear-down, which
+// frees TMEM.
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace tnf {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;  // 256 E2M1 elements
+constexpr int kBlockK = 256;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kSfbAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 96 + 127) / 128;  // 128-row scale blocks touched
+  static constexpr int kAccStages = (2 * BN + 16 + 4 * kSfbAtoms * 4 <= 512) ? 2 : 1;
+  static constexpr int kABytes = kBlockM * kBlockKBytes;
+  static constexpr int kBBytes = BN * kBlockKBytes;
+  static constexpr int kSfaBytes = 2048;
+  static constexpr int kSfbBytes = 2048 * kSfbAtoms;
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kStages = (BN >= 224) ? 4 : (BN >= 192 ? 5 : 6);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t kAccCol0 = 0;
+  static constexpr uint32_t kSfaCol = kAccStages * BN;
+  static constexpr uint32_t kSfbCol = kSfaCol + 16;
+  static_assert(kSfbCol + 4 * kSfbAtoms * 4 <= 512, "TMEM overflow");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
+};
+
+__device__ __forceinline__ float gelu_tanh_dev(float x) {
+  // 0.5*x*(1+tanh(u)) == x / (1 + exp(-2u)), u = sqrt(2/pi)*(x + 0.044715 x^3)
+  float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return x / (1.0f + __expf(-2.0f * u));
+}
+__device__ __forceinline__ float bf16_round_dev(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  constexpr int AS = Cfg::kAccStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the 128-byte swizzle atoms
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA = smem_base;
+  const uint32_t sB = sA + S * Cfg::kABytes;
+  const uint32_t sSfa = sB + S * Cfg::kBBytes;
+  const uint32_t sSfb = sSfa + S * Cfg::kSfaBytes;
+  const uint32_t sBar = sSfb + S * Cfg::kSfbBytes;  // 8-byte aligned (all sizes are multiples of 512)
+  const uint32_t bar_full = sBar;                   // S barriers
+  const uint32_t bar_empty = bar_full + 8 * S;      // S
+  const uint32_t bar_acc_full = bar_empty + 8 * S;  // AS
+  const uint32_t bar_acc_empty = bar_acc_full + 8 * AS;
+  const uint32_t tmem_holder = bar_acc_empty + 8 * AS;
+  volatile uint32_t* abort_flag =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8 - smem_base));
+  volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t num_k_tiles = (p.k + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < AS; ++i) {
+      mbar_init(bar_acc_full + 8 * i, 1);
+      mbar_init(bar_acc_empty + 8 * i, 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+        const uint32_t m0 = tm * kBlockM, n0 = tn * BN;
+        const uint8_t* sfa_src = p.sfa + uint64_t(tm) * p.k_atoms * 512u;
+        const uint8_t* sfb_src = p.sfb + uint64_t(n0 >> 7) * p.k_atoms * 512u;
+        for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(sA + stage * Cfg::kABytes, &map_a, full, int32_t(kt * kBlockKBytes), int32_t(m0));
+          tma_load_2d(sB + stage * Cfg::kBBytes, &map_w, full, int32_t(kt * kBlockKBytes), int32_t(n0));
+          bulk_load_1d(sSfa + stage * Cfg::kSfaBytes, sfa_src + uint64_t(kt) * 2048u, 2048u, full);
+#pragma unroll
+          for (int j = 0; j < Cfg::kSfbAtoms; ++j)
+            bulk_load_1d(sSfb + stage * Cfg::kSfbBytes + j * 2048, sfb_src + (uint64_t(j) * p.k_atoms + kt * 4u) * 512u,
+                         2048u, full);
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // drain: every stage this lane armed must have landed before the CTA may exit
+      if (!ok) {
+        for (int i = 0; i < S; ++i) mbar_wait_bounded(bar_full + 8 * i, 0, abort_flag, 0, 20000000ll);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvfp4(kBlockM, BN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const uint32_t n0 = (tile / p.tiles_m) * BN;
+        const uint32_t sfb_shift = (n0 & 127u) >> 5;  // TMEM column shift when the tile starts inside a 128-row scale block
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusAccEmptyTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + Cfg::kAccCol0 + acc * BN;
+        for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = sA + stage * Cfg::kABytes, b_addr = sB + stage * Cfg::kBBytes;
+          const uint32_t sfa_addr = sSfa + stage * Cfg::kSfaBytes, sfb_addr = sSfb + stage * Cfg::kSfbBytes;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfaCol + kb * 4, make_desc_sf(sfa_addr + kb * 512));
+#pragma unroll
+            for (int j = 0; j < Cfg::kSfbAtoms; ++j)
+              tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + j * 4,
+                                   make_desc_sf(sfb_addr + j * 2048 + kb * 512));
+          }
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tc_mma_nvfp4(d_tmem, make_desc_sw128(a_addr + kb * 32), make_desc_sw128(b_addr + kb * 32), idesc,
+                         tmem_base + Cfg::kSfaCol + kb * 4,
+                         tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + sfb_shift, (kt | kb) != 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(bar_acc_full + 8 * acc);
+        if (++acc == AS) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+      const uint32_t row = tm * kBlockM + quarter * 32 + lane;
+      const uint32_t n0 = tn * BN;
+      if (!mbar_wait_bounded(bar_acc_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + Cfg::kAccCol0 + acc * BN + ((quarter * 32u) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const uint32_t nc = n0 + c * 32;
+        if (nc >= p.n) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.m) {
+          const uint32_t ncols = min(32u, p.n - nc);  // multiple of 8
+          const uint64_t out_off = uint64_t(row) * p.ldo + p.n_offset + nc;
+          const uint16_t* res_row = p.residual ? p.residual + uint64_t(row) * p.n + nc : nullptr;
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            if (uint32_t(v8 * 8) >= ncols) break;
+            uint4 bias4 = make_uint4(0, 0, 0, 0), gate4 = make_uint4(0, 0, 0, 0), res4 = make_uint4(0, 0, 0, 0);
+            if (p.bias) bias4 = __ldg(reinterpret_cast<const uint4*>(p.bias + nc + v8 * 8));
+            if (p.gate) {
+              gate4 = __ldg(reinterpret_cast<const uint4*>(p.gate + nc + v8 * 8));
+              res4 = __ldg(reinterpret_cast<const uint4*>(res_row + v8 * 8));
+            }
+            const uint32_t bw[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+            const uint32_t gw[4] = {gate4.x, gate4.y, gate4.z, gate4.w};
+            const uint32_t rw[4] = {res4.x, res4.y, res4.z, res4.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              float v[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                float x = __uint_as_float(r[v8 * 8 + h * 2 + e]) * p.alpha;
+                if (p.chain) x = bf16_round_dev(x);
+                if (p.bias) {
+                  x += bf16_bits_to_f32(e ? (bw[h] >> 16) : (bw[h] & 0xFFFFu));
+                  if (p.chain) x = bf16_round_dev(x);
+                }
+                if (p.act == 1u) {
+                  x = gelu_tanh_dev(x);
+                  if (p.chain) x = bf16_round_dev(x);
+                }
+                if (p.gate) {
+                  float g = bf16_bits_to_f32(e ? (gw[h] >> 16) : (gw[h] & 0xFFFFu));
+                  float rs = bf16_bits_to_f32(e ? (rw[h] >> 16) : (rw[h] & 0xFFFFu));
+                  x = rs + g * x;
+                }
+                v[e] = x;
+              }
+              __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
+              ow[h] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            for (uint32_t d = 0; d < p.n_out; ++d)
+              *reinterpret_cast<uint4*>(p.out[d] + out_off + v8 * 8) = o4;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+      if (++acc == AS) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- tear-down ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0u) atomicCAS(p.status, 0u, *abort_flag);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+uint32_t gemm_tile_n(uint32_t n) {
+  (void)n;
+  return 256;
+}
+
+template <int BN>
+static cudaError_t launch_bn(const CUtensorMap& map_a, const CUtensorMap& map_w, GemmParams p, int sm_count,
+                             cudaStream_t s) {
+  using Cfg = TileCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  p.tiles_m = (p.m + kBlockM - 1) / kBlockM;
+  p.tiles_n = (p.n + BN - 1) / BN;
+  uint32_t tiles = p.tiles_m * p.tiles_n;
+  if (tiles == 0) return cudaSuccess;
+  uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count));
+  nvfp4_gemm_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(map_a, map_w, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmParams& p, int sm_count,
+                              cudaStream_t s) {
+  switch (gemm_tile_n(p.n)) {
+    case 128: return launch_bn<128>(map_a, map_w, p, sm_count, s);
+    default: return launch_bn<256>(map_a, map_w, p, sm_count, s);
+  }
+}
+
+}  // namespace tnf
