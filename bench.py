@@ -1,0 +1,394 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear path (see DESIGN.md for the workload definitions).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+N = 1: one step = the Qwen-Image-shaped GEMM stack — per layer the four block linears at
+M = 4352 (fused QKV 3072->9216, out-proj 3072->3072, MLP up 3072->12288 + bias + tanh-GELU,
+MLP down 12288->3072 + bias), 60 layers with distinct resident NVFP4 weights (3.8 GB, larger
+than L2). Each linear is the library's public call: activation quantiser + tcgen05 GEMM with
+the fused epilogue.
+N > 1 (torchrun, one rank per GPU): one step = the batched Wan-5B-shaped FFN pair at
+M = 26520 with the weights split by output columns over the ranks and every rank's slice
+delivered to all ranks (fused peer-store epilogue, or NCCL all-gather with --gather nccl).
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN = 3072
+QWEN_M = 4352
+QWEN_LINEARS = [  # (name, k, n, act)
+    ("qkv", 3072, 9216, 0),
+    ("out", 3072, 3072, 0),
+    ("up", 3072, 12288, 1),
+    ("down", 12288, 3072, 0),
+]
+WAN_M = 26520
+WAN_FFN = 14336
+NOMINAL_FP4_TFLOPS = 9000.0  # NVIDIA's dense FP4 figure for B200 (context only)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "200", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [l.split(", ") for l in open(self.f.name).read().strip().splitlines() if l.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for i, nm in enumerate(names):
+                if len(r) > 5 + i and r[5 + i].strip().lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = sorted(sm)[len(sm) // 2:]  # upper half = samples under load
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU legs (the only place this file runs the oracle)
+# --------------------------------------------------------------------------------------------
+def cpu_sample(steps: int = 1, warmup: int = 0, workload: str = "qwen"):
+    """Times the CPU restatement on a bounded sample: the layer's linears at 256 rows."""
+    import oracle as O
+
+    rows = 256
+    shapes = QWEN_LINEARS if workload == "qwen" else [("up", HIDDEN, WAN_FFN, 1), ("down", WAN_FFN, HIDDEN, 0)]
+    ops = []
+    for i, (name, k, n, act) in enumerate(shapes):
+        a = O.f32_to_bf16(O.gaussian(rows * k, 0xA000 + i).reshape(rows, k))
+        w = (O.gaussian(n * k, 0xB000 + i) * np.float32(0.02)).reshape(n, k)
+        b = O.f32_to_bf16(O.gaussian(n, 0xC000 + i) * np.float32(0.01))
+        wc, ws, gw = O.quantize_weight(w)
+        ops.append((a, O.global_scale(O.amax_bf16(a)), wc, ws, gw, b, act))
+    flops = sum(2.0 * rows * k * n for _, k, n, _ in shapes)
+
+    def one():
+        for a, ga, wc, ws, gw, b, act in ops:
+            O.linear(a, ga, wc, ws, gw, bias=b, act=act)
+
+    for _ in range(warmup):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{len(shapes)} linears of one layer at {rows} rows ({flops / 1e9:.1f} GFLOP per step), "
+                      f"activation quantiser + dequantise + f32 GEMM + epilogue, OpenMP over {O.num_threads()} threads",
+            "ms_per_sample_step": dt * 1e3}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = "qwen" if args.gpus == 1 else "wan"
+    r = cpu_sample(steps=max(1, args.steps), warmup=max(1, min(args.warmup, 2)), workload=workload)
+    line = {
+        "impl": "reference", "metric": "nvfp4_linear_tflops", "value": r["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_sample_step"],
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "nvfp4",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no NVFP4 path and its GPU path needs a graphics API; this arm times the CPU "
+                "restatement of its dequantise-then-f32-GEMM linear on a bounded sample of the workload",
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int) -> dict:
+    if n_gpus == 1:
+        return {"workload": "BASELINE configs[1] block linears (M=4352: qkv 3072->9216, out 3072->3072, up 3072->12288+GELU, "
+                            "down 12288->3072) over 60 distinct resident layers (= configs[3] stack, weights resident)",
+                "m": QWEN_M, "layers": 60, "l2": "weights 3.8 GB > L2; no flush needed"}
+    return {"workload": "BASELINE configs[4] Wan-5B FFN pair at M=26520 (3072->14336 + GELU, 14336->3072), "
+                        "weights split by output columns across ranks, outputs delivered to every rank",
+            "m": WAN_M, "parallelism": f"n-split x{n_gpus}", "l2": "activations 163 MB + 760 MB outputs > L2"}
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+class _DevView:
+    """Exposes a library buffer to torch through __cuda_array_interface__ (for seeding inputs only)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def as_torch(be, buf, dtype, shape):
+    import torch
+
+    t = torch.as_tensor(_DevView(be.device_ptr(buf), buf.len), device=f"cuda:{be.device}")
+    return t.view(dtype).view(*shape)
+
+
+def make_weight(be, T, L, gen, n, k, sigma=0.02, with_bias=True):
+    """Random-init N(0, sigma) weight generated on the device, quantised by the library."""
+    import torch
+
+    dev = f"cuda:{be.device}"
+    src = be.allocate_in(n * k * 2, L.CAT_STAGING)
+    as_torch(be, src, torch.bfloat16, (n, k)).copy_((torch.randn(n, k, device=dev, generator=gen) * sigma).to(torch.bfloat16))
+    torch.cuda.synchronize()
+    codes = be.allocate_in(n * k // 2, L.CAT_WEIGHTS)
+    canon = be.allocate_in(n * k // 16, L.CAT_STAGING)
+    g = C.c_float()
+    from thinfer_b200.backend import _check, device_scales_bytes
+    _check(be.lib.tnf_quantize_weight(be._ctx, src, L.DTYPE_BF16, n, k, codes, canon, C.byref(g)))
+    devs = be.allocate_in(device_scales_bytes(n, k), L.CAT_WEIGHTS)
+    _check(be.lib.tnf_prepare_scales(be._ctx, canon, n, k, devs))
+    be.submit()
+    be.free(src)
+    be.free(canon)
+    bias = None
+    if with_bias:
+        bias = be.allocate_in(n * 2, L.CAT_WEIGHTS)
+        as_torch(be, bias, torch.bfloat16, (n,)).copy_((torch.randn(n, device=dev, generator=gen) * 0.01).to(torch.bfloat16))
+        torch.cuda.synchronize()
+    return T.Nvfp4Weight(n, k, codes, devs, float(g.value), bias, None)
+
+
+def run_single_gpu(args):
+    import torch
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+
+    layers = args.layers
+    be = T.Backend(0)
+    sc = be.scope()
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0xB200)
+    compute = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    M = QWEN_M
+
+    weights = [[make_weight(be, T, L, gen, n, k) for (_, k, n, _) in QWEN_LINEARS] for _ in range(layers)]
+    # activations: x -> qkv ; attn (fixed stand-in for the attention output) -> out-proj -> h1 ;
+    # h1 -> up+GELU -> h2 ; h2 -> down -> next layer's x (two x buffers alternate)
+    xs = [be.allocate(M * HIDDEN * 2) for _ in range(2)]
+    qkv = be.allocate(M * 9216 * 2)
+    attn = be.allocate(M * HIDDEN * 2)
+    h1 = be.allocate(M * HIDDEN * 2)
+    h2 = be.allocate(M * 12288 * 2)
+    x0 = (torch.randn(M, HIDDEN, device=dev, generator=gen)).to(torch.bfloat16)
+    as_torch(be, attn, torch.bfloat16, (M, HIDDEN)).copy_(torch.randn(M, HIDDEN, device=dev, generator=gen).to(torch.bfloat16))
+    as_torch(be, xs[0], torch.bfloat16, (M, HIDDEN)).copy_(x0)
+    torch.cuda.synchronize()
+
+    def layer_io(li):
+        xin, xout = xs[li % 2], xs[(li + 1) % 2]
+        return [(xin, qkv), (attn, h1), (h1, h2), (h2, xout)]
+
+    # calibration pass: per-site static activation scales from the dynamic amax (standard practice
+    # for NVFP4 activations; the quantiser in the timed region uses the given scale)
+    scales = [[1.0] * 4 for _ in range(layers)]
+    for li in range(layers):
+        for j, ((src, dst), (_, k, n, act)) in enumerate(zip(layer_io(li), QWEN_LINEARS)):
+            _, _, g = _calibrate(be, sc, src, M, k)
+            scales[li][j] = g
+            sc.linear(src, M, weights[li][j], g, dst, act=act)
+    be.submit()
+
+    def step(instrument=None):
+        for li in range(layers):
+            for j, ((src, dst), (_, k, n, act)) in enumerate(zip(layer_io(li), QWEN_LINEARS)):
+                if instrument is None:
+                    sc.linear(src, M, weights[li][j], scales[li][j], dst, act=act)
+                else:
+                    sc.act_quant_shared(src, M, k, scales[li][j])
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(compute)
+                    sc.linear(None, M, weights[li][j], scales[li][j], dst, act=act, flags=L.LINEAR_A_PREQUANTIZED)
+                    e1.record(compute)
+                    instrument.append((j, e0, e1))
+
+    flops_layer = sum(2.0 * M * k * n for _, k, n, _ in QWEN_LINEARS)
+    flops_step = flops_layer * layers
+
+    for _ in range(max(args.warmup, 3)):
+        as_torch(be, xs[0], torch.bfloat16, (M, HIDDEN)).copy_(x0)
+        step()
+    be.submit()
+
+    # ---- timed region: inputs resident ----
+    sampler = ClockSampler(0)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record(compute)
+    for _ in range(args.steps):
+        step()
+    t1.record(compute)
+    be.submit()
+    torch.cuda.synchronize()
+    ms_step = t0.elapsed_time(t1) / args.steps
+    clocks = sampler.stop()
+
+    # ---- per-kernel timing of the GEMM launches (events on the launching stream) ----
+    inst = []
+    for _ in range(min(args.steps, 3)):
+        step(inst)
+    be.submit()
+    torch.cuda.synchronize()
+    per_shape = {}
+    for j, e0, e1 in inst:
+        per_shape.setdefault(j, []).append(e0.elapsed_time(e1))
+    gemm_ms = sum(sum(v) for v in per_shape.values())
+    gemm_launches = sum(len(v) for v in per_shape.values())
+    gemm_flops = sum(2.0 * M * QWEN_LINEARS[j][1] * QWEN_LINEARS[j][2] * len(v) for j, v in per_shape.items())
+    peaks = measured_peaks()
+    peak_fp4 = 4.0 * peaks["bf16_sustained"]
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": "nvfp4_gemm_kernel", "achieved": achieved, "peak": peak_fp4, "unit": "TFLOP/s",
+        "frac": achieved / peak_fp4,
+        "peak_note": f"4 x sustained bf16 cuBLAS ({peaks['source']}); MEASURED_PEAKS has no FP4 figure; "
+                     f"burst 4x = {4 * peaks['bf16']:.0f}; nominal dense FP4 = {NOMINAL_FP4_TFLOPS:.0f}",
+        "frac_of_nominal_fp4": achieved / NOMINAL_FP4_TFLOPS,
+        "avg_launch_ms": gemm_ms / gemm_launches,
+        "per_shape": {QWEN_LINEARS[j][0]: {"ms": float(np.mean(v)),
+                                            "tflops": 2.0 * M * QWEN_LINEARS[j][1] * QWEN_LINEARS[j][2] / (np.mean(v) * 1e-3) / 1e12}
+                      for j, v in sorted(per_shape.items())},
+        "traffic": None,
+    }
+
+    # ---- end to end through the public API with host buffers ----
+    host_in = _pinned(be, M * HIDDEN * 2)
+    host_out = _pinned(be, M * HIDDEN * 2)
+    host_in["np"][:] = x0.view(torch.int16).cpu().numpy().view(np.uint16).ravel()
+    final = xs[layers % 2]
+    for _ in range(2):
+        _e2e_step(be, step, xs[0], final, host_in, host_out)
+    w0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(compute)
+    for _ in range(args.steps):
+        _e2e_step(be, step, xs[0], final, host_in, host_out)
+    e1.record(compute)
+    torch.cuda.synchronize()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - w0) * 1e3) / args.steps
+    out_ok = bool(np.isfinite(_bf16_to_f32(host_out["np"])).all())
+
+    cpu = cpu_sample(steps=1, warmup=1) if not args.no_cpu else None
+    line = {
+        "metric": "nvfp4_linear_tflops", "value": flops_step / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scales, f32 accumulate, bf16 in/out)",
+        "data": "synthetic (seeded torch.randn on device: weights N(0,0.02) quantised by the library, activations N(0,1) bf16)",
+        "config": dict(workload_config(1), layers=layers),
+        "ms_per_dit_step": ms_step * 60.0 / layers,
+        "frac_of_nominal_fp4": flops_step / (ms_step * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": out_ok},
+        "gpu_launches": args.steps * layers * len(QWEN_LINEARS) * 2,
+        "mem": be.mem_snapshot(),
+    }
+    print(json.dumps(line))
+    be.close()
+
+
+def _calibrate(be, sc, src, m, k):
+    c, s, g = sc.act_quant(src, m, k, 0.0, device_layout=True)
+    be.free(c)
+    be.free(s)
+    return None, None, g
+
+
+def _pinned(be, nbytes):
+    from thinfer_b200.backend import _check
+
+    hid = C.c_uint64()
+    _check(be.lib.tnf_host_register(be._ctx, None, nbytes, C.byref(hid)))
+    p = C.c_void_p()
+    _check(be.lib.tnf_host_ptr(be._ctx, hid.value, C.byref(p), None))
+    arr = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), shape=(nbytes // 2,))
+    return {"id": hid.value, "ptr": p, "np": arr, "nbytes": nbytes}
+
+
+def _e2e_step(be, step, x_in, x_out, host_in, host_out):
+    from thinfer_b200.backend import _check
+
+    _check(be.lib.tnf_write(be._ctx, x_in.id, 0, host_in["ptr"], host_in["nbytes"]))
+    step()
+    _check(be.lib.tnf_read(be._ctx, x_out.id, 0, host_out["ptr"], host_out["nbytes"]))
+
+
+def _bf16_to_f32(h):
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=60, help="layers in the single-GPU stack (60 = the named workload)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"], help="N>1: how slices reach every rank")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        from bench_multi import run_multi_gpu
+        run_multi_gpu(args)
+    else:
+        run_single_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

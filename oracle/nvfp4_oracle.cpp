@@ -271,7 +271,7 @@ void orc_gemm_f32(const float* a, const float* w, int64_t m, int64_t n, int64_t 
 #pragma omp parallel for schedule(static)
     for (int64_t kk = 0; kk < k; ++kk)
         for (int64_t j = 0; j < n; ++j) wt[size_t(kk) * n + j] = w[size_t(j) * k + kk];
-    const int64_t NB = 256;
+    const int64_t NB = 64;  // 8 AVX2 accumulators stay in registers
 #pragma omp parallel for collapse(2) schedule(static)
     for (int64_t i = 0; i < m; ++i)
         for (int64_t j0 = 0; j0 < n; j0 += NB) {

@@ -1,0 +1,57 @@
+"""The C-ABI library loads and exports every symbol include/thinfer_nvfp4.h declares (CPU only;
+no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "thinfer_nvfp4.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tnf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported_and_bound():
+    from thinfer_b200 import _lib
+
+    names = declared_symbols()
+    assert len(names) >= 30
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes binding table and header disagree"
+
+
+def test_struct_layouts_match_header():
+    from thinfer_b200._lib import Buf, LinearArgs, StackLinear
+
+    assert ctypes.sizeof(Buf) == 24
+    assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4  # 5 scalars (+pad to 8), 7 views, 6 words
+    assert ctypes.sizeof(StackLinear) == 24
+
+
+def test_no_device_fails_loudly():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    import thinfer_b200 as T
+
+    with pytest.raises(T.TnfError) as e:
+        T.Backend(0)
+    assert "no CPU path" in str(e.value)
+
+
+def test_abi_version_and_sizes():
+    from thinfer_b200 import _lib
+
+    lib = _lib.load()
+    assert lib.tnf_abi_version() == 1
+    # 128-row x 4-block atoms of 512 bytes; K atoms rounded up to a multiple of 4
+    assert lib.tnf_device_scales_bytes(128, 256) == 4 * 512
+    assert lib.tnf_device_scales_bytes(129, 3072) == 2 * 48 * 512
+    assert lib.tnf_device_scales_bytes(1, 64) == 4 * 512

@@ -298,7 +298,6 @@ int32_t tnf_destroy(tnf_ctx* ctx) {
   if (!ctx) return TNF_OK;
   cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
-  extern void tnf_comm_teardown(tnf_ctx*);
   tnf_comm_teardown(ctx);
   for (auto& kv : ctx->bufs) cudaFree(kv.second.ptr);
   for (auto& kv : ctx->hosts) {

@@ -66,6 +66,8 @@ struct tnf_ctx {
   uint64_t gather_tmp_bytes = 0;
 };
 
+void tnf_comm_teardown(tnf_ctx* ctx);  // comm.cu
+
 namespace tnf {
 void set_error(const char* fmt, ...);
 int32_t cuda_fail(cudaError_t e, const char* what);
