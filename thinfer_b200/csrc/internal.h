@@ -40,6 +40,8 @@ struct GemmParams {
   uint32_t act, chain;
   uint32_t tiles_m, tiles_n;
   uint32_t* status;            // device status word
+  uint32_t diag;               // diagnostic bits from TNF_GEMM_DIAG (0 in normal use): 1 no output stores,
+                               // 2 scale copies only on the first K tile, 4 no MMA, 8 no operand loads
 };
 
 cudaError_t launch_amax(const void* x, int dtype, uint64_t n, uint32_t* amax_bits, cudaStream_t s);
