@@ -128,36 +128,50 @@ static encode_tiled_fn get_encode_fn() {
   return fn;
 }
 
-int make_codes_tensor_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+int make_tensor_map(CUtensorMap* out, const MapSpec& sp) {
   encode_tiled_fn fn = get_encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from this driver");
     return TNF_ERR_LAUNCH;
   }
-  cuuint64_t gdim[2] = {k / 2, rows};
-  cuuint64_t gstride[1] = {k / 2};
-  cuuint32_t box[2] = {128, box_rows};
+  cuuint64_t gdim[2] = {sp.dim0, sp.dim1};
+  cuuint64_t gstride[1] = {sp.stride1};
+  cuuint32_t box[2] = {sp.box0, sp.box1};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(out, sp.elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                  const_cast<void*>(sp.base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  sp.swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p rows %u k %u box %u)", int(r), base, rows, k,
-              box_rows);
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p dims %llu x %llu stride %llu box %u x %u)", int(r),
+              sp.base, (unsigned long long)sp.dim0, (unsigned long long)sp.dim1, (unsigned long long)sp.stride1, sp.box0,
+              sp.box1);
     return TNF_ERR_INVALID_ARGUMENT;
   }
   return TNF_OK;
 }
 
-const CUtensorMap* get_map(tnf_ctx* ctx, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+const CUtensorMap* get_map(tnf_ctx* ctx, const MapSpec& spec) {
   std::lock_guard<std::mutex> lk(ctx->mu);
-  tnf_map_key key{base, rows, k, box_rows};
-  auto it = ctx->maps.find(key);
+  auto it = ctx->maps.find(spec);
   if (it != ctx->maps.end()) return &it->second;
   CUtensorMap m;
-  if (make_codes_tensor_map(&m, base, rows, k, box_rows) != TNF_OK) return nullptr;
-  if (ctx->maps.size() > 4096) ctx->maps.clear();
-  return &(ctx->maps[key] = m);
+  if (make_tensor_map(&m, spec) != TNF_OK) return nullptr;
+  if (ctx->maps.size() > 8192) ctx->maps.clear();
+  return &(ctx->maps[spec] = m);
+}
+
+// packed E2M1 codes viewed as bytes [rows, k/2]: box {128 bytes, box_rows}, 128-byte swizzle
+static MapSpec codes_spec(const void* base, uint32_t rows, uint32_t k, uint32_t box_rows) {
+  return MapSpec{base, 1, k / 2, rows, k / 2, 128, box_rows, 1};
+}
+// device-layout scales viewed as rows of 128 bytes: box = 16 rows = four 512-byte atoms
+static MapSpec scales_spec(const void* base, uint32_t rows, uint32_t k) {
+  return MapSpec{base, 1, 128, sf_device_bytes(rows, k) / 128, 128, 128, 16, 0};
+}
+// bf16 output window [m, n] with leading dimension ldo: box {64 columns, 32 rows}, 128-byte swizzle
+static MapSpec out_spec(const void* base, uint32_t m, uint32_t n, uint32_t ldo) {
+  return MapSpec{base, 2, n, m, uint64_t(ldo) * 2, 64, 32, 1};
 }
 
 static int32_t ensure_scratch(tnf_ctx* ctx, uint32_t m, uint32_t k) {
@@ -243,8 +257,25 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.act = a->act;
   p.chain = a->parity_mode;
   p.status = ctx->dwords;
-  const CUtensorMap* ma = get_map(ctx, a_codes, a->m, a->k, 128);
-  const CUtensorMap* mw = get_map(ctx, w_codes, a->n, a->k, gemm_tile_n(a->n));
+  p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
+  if (gemm_use_pair(a->m, a->n, a->k)) {
+    const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
+    const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, 128));
+    const CUtensorMap* msa = get_map(ctx, scales_spec(a_scales, a->m, a->k));
+    const CUtensorMap* msb = get_map(ctx, scales_spec(w_scales, a->n, a->k));
+    if (!ma || !mw || !msa || !msb) return TNF_ERR_INVALID_ARGUMENT;
+    CUtensorMap outs[kMaxPeers];
+    for (uint32_t d = 0; d < p.n_out; ++d) {
+      const CUtensorMap* mo = get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo));
+      if (!mo) return TNF_ERR_INVALID_ARGUMENT;
+      outs[d] = *mo;
+    }
+    for (uint32_t d = p.n_out; d < kMaxPeers; ++d) outs[d] = outs[0];
+    TNF_CUDA(launch_gemm_nvfp4_pair(*ma, *mw, *msa, *msb, outs, p, ctx->sm_count, ctx->compute), "nvfp4 pair gemm launch");
+    return TNF_OK;
+  }
+  const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
+  const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, gemm_tile_n(a->n)));
   if (!ma || !mw) return TNF_ERR_INVALID_ARGUMENT;
   TNF_CUDA(launch_gemm_nvfp4(*ma, *mw, p, ctx->sm_count, ctx->compute), "nvfp4 gemm launch");
   return TNF_OK;
@@ -288,8 +319,8 @@ int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out) {
   ctx->budget = vram_budget_bytes;
   TNF_CUDA(cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking), "cudaStreamCreate");
   TNF_CUDA(cudaStreamCreateWithFlags(&ctx->copy, cudaStreamNonBlocking), "cudaStreamCreate");
-  TNF_CUDA(cudaMalloc(&ctx->dwords, 64), "cudaMalloc(status words)");
-  TNF_CUDA(cudaMemset(ctx->dwords, 0, 64), "cudaMemset(status words)");
+  TNF_CUDA(cudaMalloc(&ctx->dwords, 256 + 16384), "cudaMalloc(status words)");
+  TNF_CUDA(cudaMemset(ctx->dwords, 0, 256 + 16384), "cudaMemset(status words)");
   *out = ctx;
   return TNF_OK;
 }
@@ -451,6 +482,13 @@ int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]) {
   }
   out[6] = ctx->true_peak;
   out[7] = ctx->streamed;
+  return TNF_OK;
+}
+
+// Diagnostic (not part of the ABI header): copies the clock64 stamps recorded with TNF_GEMM_DIAG bit 16.
+int32_t tnf_debug_trace(tnf_ctx* ctx, unsigned long long* dst_2048) {
+  TNF_CHECK_CTX(ctx);
+  TNF_CUDA(cudaMemcpy(dst_2048, ctx->dwords + 64, 16384, cudaMemcpyDeviceToHost), "trace read");
   return TNF_OK;
 }
 

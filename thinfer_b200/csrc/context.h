@@ -26,17 +26,6 @@ struct tnf_host_rec {
   bool owned = false;  // cudaHostAlloc'ed by us (else cudaHostRegister'ed in place)
 };
 
-struct tnf_map_key {
-  const void* base;
-  uint32_t rows, k, box_rows;
-  bool operator<(const tnf_map_key& o) const {
-    if (base != o.base) return base < o.base;
-    if (rows != o.rows) return rows < o.rows;
-    if (k != o.k) return k < o.k;
-    return box_rows < o.box_rows;
-  }
-};
-
 struct tnf_ctx {
   int device = 0;
   int sm_count = 148;
@@ -55,7 +44,7 @@ struct tnf_ctx {
   uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;
   // small device words: [0] kernel status, [1] amax bits, [2] global scale (f32)
   uint32_t* dwords = nullptr;
-  std::map<tnf_map_key, CUtensorMap> maps;
+  std::map<tnf::MapSpec, CUtensorMap> maps;
   // fused-scatter peer windows (opened CUDA IPC mappings), index 0 unused
   void* peer_out[tnf::kMaxPeers] = {nullptr};
   int n_peers = 0;
@@ -75,5 +64,5 @@ int32_t cuda_fail(cudaError_t e, const char* what);
 uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need_bytes, const char* name, int32_t* status);
 int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id);
 int32_t free_locked(tnf_ctx* ctx, uint64_t id);
-const CUtensorMap* get_map(tnf_ctx* ctx, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows);
+const CUtensorMap* get_map(tnf_ctx* ctx, const MapSpec& spec);
 }  // namespace tnf

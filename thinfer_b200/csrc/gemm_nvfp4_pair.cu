@@ -1,0 +1,431 @@
+// NVFP4 GEMM for sm_100a on CTA pairs: out[m,n] = epilogue(alpha * sum_k A[m,k] * W[n,k]).
+//
+// Same contract as the 1-CTA kernel in gemm_nvfp4.cu; this is the large-M path. Two CTAs of a
+// (2,1,1) cluster compute one 256x256 output tile with tcgen05.mma.cta_group::2: each CTA
+// loads its own 128 rows of A and its own 128-row half of the W tile, the leader CTA issues
+// the MMAs, and each CTA ends up with its 128x256 slice of the accumulator in its own TMEM.
+// Against the 1-CTA tile this cuts the shared-memory fill per SM and K tile from 54 KB to
+// 38 KB, which is what lets five stages cover the load latency. No TMA multicast is used:
+// the only cluster-wide operations are tcgen05.commit arrivals and remote mbarrier arrivals.
+//
+// Per CTA, 320 threads:
+//   warp 0     TMA producer (tensor-map loads of A, W-half, the CTA's scale atoms of A and the
+//              scale atoms of the whole W tile; bytes are counted on the LEADER's stage barrier)
+//   warp 1     TMEM owner; in the leader one lane issues scale copies smem->TMEM and MMAs for
+//              both CTAs, frees stages in both CTAs with a multicast commit
+//   warps 2-9  epilogue: TMEM -> registers -> alpha/bias/GELU/gated residual -> bf16 -> swizzled
+//              shared staging -> TMA store (one store per destination: local output and peers)
+// TMEM (512 columns): two 256-column accumulators at columns 0 and 192 that overlap in
+// [192,256); the epilogue reads the overlapping 64 columns first and then releases the next
+// tile's MMA, so the drain of tile i runs under the main loop of tile i+1. Scale factors sit
+// in columns [448,496).
+// Every mbarrier wait is bounded (see ptx.cuh); a wait that gives up raises the CTA's abort
+// flag, every role falls through to the tear-down, and the host reads the status word.
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdlib>
+
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace tnf {
+
+namespace pair {
+constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+constexpr int kStages = 5;
+constexpr int kABytes = 128 * 128;        // 128 rows x 256 E2M1
+constexpr int kBBytes = 128 * 128;        // this CTA's half of the 256-row W tile
+constexpr int kSfaBytes = 2048;           // 4 atoms: 128 rows x 16 blocks
+constexpr int kSfbBytes = 4096;           // 2 x 4 atoms: 256 rows x 16 blocks
+constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;  // 38912
+constexpr int kStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccStride = 192;  // accumulator b starts at column b * 192
+constexpr uint32_t kSfaCol = 448, kSfbCol = 464;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
+}  // namespace pair
+
+struct PairOutMaps {
+  CUtensorMap m[kMaxPeers];
+};
+
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  // 0.5*x*(1+tanh(u)), u = sqrt(2/pi)*(x + 0.044715 x^3); tanh.approx (rel. error ~2^-11)
+  float u = x * (0.7978845608028654f + 0.035677408136300125f * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// 8 accumulator columns -> 8 bf16 (one 16-byte chunk of the staging row)
+template <bool kGelu, bool kChain, bool kGate>
+__device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool has_bias, uint4 b4, uint4 g4, uint4 s4) {
+  const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w}, sw[4] = {s4.x, s4.y, s4.z, s4.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    float v[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float x = __uint_as_float(r[2 * h + e]) * alpha;
+      if (kChain) x = bf16r(x);
+      if (has_bias) {
+        x += e ? bf16_hi(bw[h]) : bf16_lo(bw[h]);
+        if (kChain) x = bf16r(x);
+      }
+      if (kGelu) {
+        x = gelu_tanh_fast(x);
+        if (kChain) x = bf16r(x);
+      }
+      if (kGate) x = fmaf(e ? bf16_hi(gw[h]) : bf16_lo(gw[h]), x, e ? bf16_hi(sw[h]) : bf16_lo(sw[h]));
+      v[e] = x;
+    }
+    __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
+    o[h] = *reinterpret_cast<uint32_t*>(&pk);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// One warp's 32 rows x 64 columns: accumulator registers -> bf16 rows in the swizzled staging
+// buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
+template <bool kGelu, bool kChain, bool kGate>
+__device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
+                                                   uint8_t* buf_gen, int lane) {
+  const bool row_ok = row < p.m;
+#pragma unroll
+  for (int sub = 0; sub < 2; ++sub) {
+    uint4 b4[4], g4[4], s4[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {  // loads first so that their latencies overlap
+      const uint32_t nc = ncol0 + (sub * 4 + jj) * 8;
+      const bool col_ok = nc < p.n;
+      b4[jj] = g4[jj] = s4[jj] = make_uint4(0, 0, 0, 0);
+      if (p.bias && col_ok) b4[jj] = __ldg(reinterpret_cast<const uint4*>(p.bias + nc));
+      if (kGate && col_ok) {
+        g4[jj] = __ldg(reinterpret_cast<const uint4*>(p.gate + nc));
+        if (row_ok) s4[jj] = __ldg(reinterpret_cast<const uint4*>(p.residual + uint64_t(row) * p.n + nc));
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = sub * 4 + jj;
+      const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4[jj], g4[jj], s4[jj]);
+      *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+    }
+  }
+}
+
+__device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
+                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, int lane) {
+  switch (mode) {
+    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, lane); break;
+    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, lane); break;
+    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, lane); break;
+    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, lane); break;
+    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, lane); break;
+    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, lane); break;
+    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, lane); break;
+    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, lane); break;
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
+    nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                           const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                           const __grid_constant__ PairOutMaps out_maps, const GemmParams p) {
+  using namespace pair;
+  constexpr int S = kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA = smem_base;
+  const uint32_t sB = sA + S * kABytes;
+  const uint32_t sSfa = sB + S * kBBytes;
+  const uint32_t sSfb = sSfa + S * kSfaBytes;
+  const uint32_t sStaging = sSfb + S * kSfbBytes;  // 1024-aligned: every size above is a multiple of 1024
+  const uint32_t sBar = sStaging + kStagingBytes;
+  const uint32_t bar_full = sBar;               // S barriers, used in the leader only
+  const uint32_t bar_empty = bar_full + 8 * S;  // S
+  const uint32_t bar_acc_full = bar_empty + 8 * S;
+  const uint32_t bar_acc_free = bar_acc_full + 8;  // used in the leader only
+  const uint32_t tmem_holder = bar_acc_free + 8;
+  volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8 - smem_base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const uint32_t tiles_m2 = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
+  const uint32_t num_k_tiles = (p.k + 255u) / 256u;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_free, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_sfa);
+    prefetch_tensormap(&map_sfb);
+    prefetch_tensormap(&out_maps.m[0]);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs): the whole warp runs the loop, one lane issues ----------------
+    {
+      uint32_t stage = 0, phase = 0, titer = 0;
+      bool ok = true;
+      for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+        const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
+        const int32_t m0 = int32_t(tm2 * 256u + rank * 128u), n0 = int32_t(tn * 256u);
+        const int32_t sfa_row0 = int32_t((tm2 * 2u + rank) * p.k_atoms * 4u);
+        const int32_t sfb_row0 = int32_t((uint32_t(n0) >> 7) * p.k_atoms * 4u);
+        for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          const bool tr = (p.diag & 16u) && rank == 0 && pair_id == 0 && titer < 256u;
+          const bool skip_ab = (p.diag & 8u) != 0u;
+          const uint32_t full = mapa_cluster(bar_full + 8 * stage, 0);  // the leader's barrier counts both CTAs' bytes
+          if (elect_one()) {
+            if (tr) p.trace[titer * 4 + 0] = clock64();
+            if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * kStageBytes);
+            if (!skip_ab) {
+              tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * 128u), m0);
+              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * 128u), n0 + int32_t(rank * 128u));
+            }
+            tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * 16u));
+            tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * 16u));
+            tma_load_2d_pair(sSfb + stage * kSfbBytes + 2048, &map_sfb, full, 0,
+                             sfb_row0 + int32_t(p.k_atoms * 4u + kt * 16u));
+            if (tr) p.trace[titer * 4 + 1] = clock64();
+          }
+          __syncwarp();
+          ++titer;
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (rank == 0) {  // whole warp runs the loop; one elected lane issues the tcgen05 instructions
+      constexpr uint32_t idesc = make_idesc_nvfp4(256, 256);
+      uint32_t stage = 0, phase = 0, it = 0, titer = 0;
+      bool ok = true;
+      for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const bool ttr = (p.diag & 16u) && pair_id == 0 && it < 16u && lane == 0;
+        if (ttr) p.trace[1024 + it * 8 + 0] = clock64();
+        if (it > 0) {  // the previous tile's epilogues (both CTAs) have read the overlapping columns
+          if (!mbar_wait_warp(bar_acc_free, (it - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
+        if (ttr) p.trace[1024 + it * 8 + 1] = clock64();
+        const uint32_t d_tmem = tmem_base + (it & 1u) * kAccStride;
+        for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const bool tr = (p.diag & 16u) && pair_id == 0 && titer < 256u;
+          if (elect_one()) {
+          if (tr) p.trace[titer * 4 + 2] = clock64();
+          const uint32_t a_addr = sA + stage * kABytes, b_addr = sB + stage * kBBytes;
+          const uint32_t sfa_addr = sSfa + stage * kSfaBytes, sfb_addr = sSfb + stage * kSfbBytes;
+          if (!(p.diag & 2u) || kt == 0)
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tc_cp_32x128b_warpx4_pair(tmem_base + kSfaCol + kb * 4, make_desc_sf(sfa_addr + kb * 512));
+            tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + kb * 8, make_desc_sf(sfb_addr + kb * 512));
+            tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + kb * 8 + 4, make_desc_sf(sfb_addr + 2048 + kb * 512));
+          }
+          if (!(p.diag & 4u))
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            tc_mma_nvfp4_pair(d_tmem, make_desc_sw128(a_addr + kb * 32), make_desc_sw128(b_addr + kb * 32), idesc,
+                              tmem_base + kSfaCol + kb * 4, tmem_base + kSfbCol + kb * 8, (kt | kb) != 0u);
+          tc_commit_pair_mc(bar_empty + 8 * stage, 3);  // frees the stage in both CTAs
+          if (tr) p.trace[titer * 4 + 3] = clock64();
+          }
+          __syncwarp();
+          ++titer;
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (ok && elect_one()) tc_commit_pair_mc(bar_acc_full, 3);  // accumulator ready in both CTAs
+        __syncwarp();
+        if (ttr) p.trace[1024 + it * 8 + 2] = clock64();
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..9, both CTAs) ----------------
+    // Warp w reads TMEM lanes [32*(w%4), +32). Two warps share a lane quarter: the one with
+    // h == 0 takes the first two 64-column groups in drain order (the first of which overlaps the
+    // other accumulator), h == 1 the last two.
+    const uint32_t q = warp & 3, h = uint32_t(warp - 2) >> 2;
+    const uint32_t buf = sStaging + uint32_t(warp - 2) * 4096u;
+    uint8_t* buf_gen = smem_gen + (buf - smem_base);
+    const uint32_t acc_free_leader = mapa_cluster(bar_acc_free, 0);
+    uint32_t it = 0;
+    bool ok = true;
+    const uint32_t mode = (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.gate ? 4u : 0u);
+    for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+      const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
+      const uint32_t row0 = tm2 * 256u + rank * 128u + q * 32u;
+      const uint32_t n0 = tn * 256u;
+      const uint32_t b = it & 1u;
+      const uint32_t first = b ? 0u : 3u;  // 64-column group that overlaps the other accumulator
+      const uint32_t g0 = (2u * h + first) & 3u, g1 = (2u * h + 1u + first) & 3u;
+      // warm L1 with this warp's bias / gate lines while the main loop is still running
+      if (lane < 2) {
+        const uint32_t nc = n0 + (lane ? g1 : g0) * 64u;
+        if (nc < p.n) {
+          if (p.bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + nc));
+          if (p.gate) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + nc));
+        }
+      }
+      const bool ttr = (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == 2;
+      if (ttr) p.trace[1024 + it * 8 + 3] = clock64();
+      if (!mbar_wait_bounded(bar_acc_full, it & 1u, abort_flag, kStatusEpilogueTimeout)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (ttr) p.trace[1024 + it * 8 + 4] = clock64();
+      const uint32_t t_addr = tmem_base + b * kAccStride + ((q * 32u) << 16);
+      uint32_t ra[64], rb[64];
+      tmem_ld_32x32b_x32(t_addr + g0 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&ra[0]));
+      tmem_ld_32x32b_x32(t_addr + g0 * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&ra[32]));
+      tmem_ld_wait();
+      if (ttr) p.trace[1024 + it * 8 + 7] = clock64();
+      if (h == 0) {  // the overlapping columns are in registers: the next tile's MMA may start
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_free_leader);
+        if (ttr) p.trace[1024 + it * 8 + 5] = clock64();
+      }
+      // second group's TMEM read runs under the first group's math
+      tmem_ld_32x32b_x32(t_addr + g1 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&rb[0]));
+      tmem_ld_32x32b_x32(t_addr + g1 * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&rb[32]));
+      const uint32_t row = row0 + lane;
+      if (row0 < p.m) {  // warp-uniform
+        if (n0 + g0 * 64u < p.n) {
+          if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
+          __syncwarp();
+          epilogue_pair_dispatch(mode, ra, p, row, n0 + g0 * 64u, buf_gen, lane);
+          fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
+          __syncwarp();
+          if (lane == 0) {
+            if (!(p.diag & 1u))
+              for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(n0 + g0 * 64u), int32_t(row0));
+            bulk_commit_group();
+          }
+        }
+        tmem_ld_wait();
+        if (n0 + g1 * 64u < p.n) {
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+          epilogue_pair_dispatch(mode, rb, p, row, n0 + g1 * 64u, buf_gen, lane);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if (!(p.diag & 1u))
+              for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(n0 + g1 * 64u), int32_t(row0));
+            bulk_commit_group();
+          }
+        }
+      } else {
+        tmem_ld_wait();
+      }
+      if (ttr) p.trace[1024 + it * 8 + 6] = clock64();
+    }
+    if (lane == 0) bulk_wait_group_read<0>();
+  }
+
+  // ---------------- tear-down ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0u, *abort_flag);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight retire
+  }
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+static uint32_t env_u32_pair(const char* name, uint32_t dflt) {
+  const char* v = getenv(name);
+  return v ? uint32_t(strtoul(v, nullptr, 0)) : dflt;
+}
+
+bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
+  (void)n;
+  (void)k;
+  static uint32_t force = env_u32_pair("TNF_GEMM_KERNEL", 0);  // tuning knob: 1 = always 1-CTA, 2 = always pair
+  if (force == 1) return false;
+  if (force == 2) return true;
+  return m > 128;
+}
+
+cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
+                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p_in,
+                                   int sm_count, cudaStream_t s) {
+  static bool attr_set = false;
+  static int max_pairs = 0;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(sm_count & ~1), 1, 1);
+    cfg.blockDim = dim3(pair::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = pair::kSmemBytes;
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemm_pair_kernel, &cfg);
+    if (e != cudaSuccess || clusters <= 0) {
+      cudaGetLastError();
+      clusters = sm_count / 2;
+    }
+    max_pairs = std::min(clusters, sm_count / 2);
+    attr_set = true;
+  }
+  GemmParams p = p_in;
+  static uint32_t diag = env_u32_pair("TNF_GEMM_DIAG", 0);
+  p.diag = diag;
+  p.tiles_m = (p.m + 255u) / 256u;
+  p.tiles_n = (p.n + 255u) / 256u;
+  const uint32_t tiles = p.tiles_m * p.tiles_n;
+  if (tiles == 0) return cudaSuccess;
+  const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs));
+  PairOutMaps om;
+  for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
+  nvfp4_gemm_pair_kernel<<<pairs * 2, pair::kThreads, pair::kSmemBytes, s>>>(map_a, map_w, map_sfa, map_sfb, om, p);
+  return cudaGetLastError();
+}
+
+}  // namespace tnf

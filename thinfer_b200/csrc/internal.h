@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdint>
+#include <tuple>
 
 namespace tnf {
 
@@ -41,7 +42,9 @@ struct GemmParams {
   uint32_t tiles_m, tiles_n;
   uint32_t* status;            // device status word
   uint32_t diag;               // diagnostic bits from TNF_GEMM_DIAG (0 in normal use): 1 no output stores,
-                               // 2 scale copies only on the first K tile, 4 no MMA, 8 no operand loads
+                               // 2 scale copies only on the first K tile, 4 no MMA, 8 no operand loads,
+                               // 16 record clock64 stamps of the first K tiles of pair 0 into `trace`
+  unsigned long long* trace;   // 4 stamps per K tile (diag bit 16), 256 K tiles
 };
 
 cudaError_t launch_amax(const void* x, int dtype, uint64_t n, uint32_t* amax_bits, cudaStream_t s);
@@ -53,8 +56,26 @@ cudaError_t launch_scales_to_device(const uint8_t* in, uint32_t rows, uint32_t k
 // tcgen05 GEMM. a_codes [m, k/2], w_codes [n, k/2]; tensor maps are built (and cached) by the caller.
 cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmParams& p, int sm_count,
                               cudaStream_t s);
-// Tensor map over packed E2M1 codes viewed as bytes [rows, k/2], box {128 bytes, box_rows}, 128-byte swizzle.
-int make_codes_tensor_map(CUtensorMap* out, const void* base, uint32_t rows, uint32_t k, uint32_t box_rows);
-uint32_t gemm_tile_n(uint32_t n);  // tile width the launcher will pick for this n (for the map of W)
+// CTA-pair kernel (256x256 tiles, large M). out_maps[i] covers destination i's [m, n] window.
+cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
+                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
+                                   int sm_count, cudaStream_t s);
+bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k);
+
+// 2-D tensor map description (dim0 is the contiguous one); all maps are built through this.
+struct MapSpec {
+  const void* base;
+  uint32_t elem_bytes;   // 1 (uint8) or 2 (bf16)
+  uint64_t dim0, dim1;   // extents in elements
+  uint64_t stride1;      // bytes between rows
+  uint32_t box0, box1;   // box in elements
+  uint32_t swizzle128;   // 1: 128-byte swizzle, 0: none
+  bool operator<(const MapSpec& o) const {
+    return std::tie(base, elem_bytes, dim0, dim1, stride1, box0, box1, swizzle128) <
+           std::tie(o.base, o.elem_bytes, o.dim0, o.dim1, o.stride1, o.box0, o.box1, o.swizzle128);
+  }
+};
+int make_tensor_map(CUtensorMap* out, const MapSpec& spec);
+uint32_t gemm_tile_n(uint32_t n);  // tile width the 1-CTA launcher will pick for this n (for the map of W)
 
 }  // namespace tnf
