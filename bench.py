@@ -221,7 +221,10 @@ def run_single_gpu(args):
     qkv = be.allocate(M * 9216 * 2)
     attn = be.allocate(M * HIDDEN * 2)
     h1 = be.allocate(M * HIDDEN * 2)
-    h2 = be.allocate(M * 12288 * 2)
+    h2 = be.allocate(M * 12288 * 2)  # bf16 GELU output: calibration only
+    from thinfer_b200.backend import device_scales_bytes
+    h2c = be.allocate(M * 12288 // 2)  # the MLP-up epilogue emits the down-proj operand in NVFP4 directly
+    h2s = be.allocate(device_scales_bytes(M, 12288))
     x0 = (torch.randn(M, HIDDEN, device=dev, generator=gen)).to(torch.bfloat16)
     as_torch(be, attn, torch.bfloat16, (M, HIDDEN)).copy_(torch.randn(M, HIDDEN, device=dev, generator=gen).to(torch.bfloat16))
     as_torch(be, xs[0], torch.bfloat16, (M, HIDDEN)).copy_(x0)
@@ -242,15 +245,26 @@ def run_single_gpu(args):
     be.submit()
 
     def step(instrument=None):
+        # per layer: 3 activation-quantiser launches (x, attention output, h1) + 4 GEMM launches; the
+        # MLP-up GEMM writes its GELU output already quantised for the down projection
         for li in range(layers):
             for j, ((src, dst), (_, k, n, act)) in enumerate(zip(layer_io(li), QWEN_LINEARS)):
-                if instrument is None:
-                    sc.linear(src, M, weights[li][j], scales[li][j], dst, act=act)
-                else:
-                    sc.act_quant_shared(src, M, k, scales[li][j])
+                w, g = weights[li][j], scales[li][j]
+                if instrument is not None:
+                    if j != 3:
+                        sc.act_quant_shared(src, M, k, g)
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record(compute)
-                    sc.linear(None, M, weights[li][j], scales[li][j], dst, act=act, flags=L.LINEAR_A_PREQUANTIZED)
+                if j == 2:
+                    flags = L.LINEAR_A_PREQUANTIZED if instrument is not None else 0
+                    sc.linear(None if flags else src, M, w, g, None, act=act, flags=flags, out_nvfp4=(h2c, h2s, scales[li][3]))
+                elif j == 3:
+                    sc.matmul(h2c, h2s, M, w, g, dst, act=act)
+                elif instrument is not None:
+                    sc.linear(None, M, w, g, dst, act=act, flags=L.LINEAR_A_PREQUANTIZED)
+                else:
+                    sc.linear(src, M, w, g, dst, act=act)
+                if instrument is not None:
                     e1.record(compute)
                     instrument.append((j, e0, e1))
 
@@ -332,7 +346,7 @@ def run_single_gpu(args):
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": out_ok},
-        "gpu_launches": args.steps * layers * len(QWEN_LINEARS) * 2,
+        "gpu_launches": args.steps * layers * 7,  # per layer: 3 activation quantisers + 4 GEMMs
         "mem": be.mem_snapshot(),
     }
     print(json.dumps(line))

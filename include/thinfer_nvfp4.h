@@ -140,12 +140,20 @@ typedef struct tnf_linear_args {
   uint32_t n_offset;    /* column offset into out (N-split) */
   uint32_t ldo;         /* leading dimension of out in elements; 0 = n */
   uint32_t flags;       /* TNF_LINEAR_* */
-  uint32_t reserved;
+  float out_global;     /* TNF_LINEAR_OUT_NVFP4: per-tensor scale of the quantised output; > 0 */
+  tnf_buf out_codes;    /* TNF_LINEAR_OUT_NVFP4: [m, n/2] E2M1 codes of the bf16-rounded output */
+  tnf_buf out_scales;   /* TNF_LINEAR_OUT_NVFP4: DEVICE-layout scales of an [m, n] operand */
 } tnf_linear_args;
 
 enum {
   TNF_LINEAR_A_PREQUANTIZED = 1u, /* a_bf16 unused; a_codes/a_scales of the ctx scratch come from tnf_quantize_act_shared */
-  TNF_LINEAR_SCATTER_PEERS = 2u   /* epilogue also stores to every peer registered with tnf_peer_outputs */
+  TNF_LINEAR_SCATTER_PEERS = 2u,  /* epilogue also stores to every peer registered with tnf_peer_outputs */
+  /* The epilogue also quantises its bf16-rounded result to NVFP4 (same bits as tnf_quantize_act
+   * on out_bf16 would give), ready to be the A operand of tnf_gemm_nvfp4: MLP up -> GELU -> down
+   * (thinfer-models/src/qwen_image/dit.rs:745-754) without the act_quant dispatch between.
+   * Requires n % 64 == 0. */
+  TNF_LINEAR_OUT_NVFP4 = 4u,
+  TNF_LINEAR_NO_BF16_OUT = 8u     /* with OUT_NVFP4: skip the bf16 store (out_bf16 may have len 0) */
 };
 
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);

@@ -30,7 +30,7 @@ def test_struct_layouts_match_header():
     from thinfer_b200._lib import Buf, LinearArgs, StackLinear
 
     assert ctypes.sizeof(Buf) == 24
-    assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4  # 5 scalars (+pad to 8), 7 views, 6 words
+    assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4 + 2 * 24  # 5 scalars (+pad), 7 views, 6 words, 2 views
     assert ctypes.sizeof(StackLinear) == 24
 
 
@@ -50,7 +50,7 @@ def test_abi_version_and_sizes():
     from thinfer_b200 import _lib
 
     lib = _lib.load()
-    assert lib.tnf_abi_version() == 1
+    assert lib.tnf_abi_version() == 2
     # 128-row x 4-block atoms of 512 bytes; K atoms rounded up to a multiple of 4
     assert lib.tnf_device_scales_bytes(128, 256) == 4 * 512
     assert lib.tnf_device_scales_bytes(129, 3072) == 2 * 48 * 512

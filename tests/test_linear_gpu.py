@@ -78,7 +78,7 @@ def test_epilogue_modes(backend, mode):
     got, _, _ = _run(backend, a, w, b, **kw)
     want = O.linear(a, ga, wc, ws, gw, bias=b, **okw)
     assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
-    assert (got == want).mean() > 0.99
+    assert (got == want).mean() > (0.9 if mode.startswith("gelu") else 0.99)  # tanh.approx vs libm tanh
     if mode == "gate":
         backend.free(gb)
         backend.free(rb)
@@ -134,6 +134,55 @@ def test_n_split_window_and_shared_activation(backend):
         Wp.free(backend)
     backend.free(abuf)
     backend.free(out)
+
+
+@pytest.mark.parametrize("m,hidden,ffn", [(256, 512, 1024), (200, 256, 320), (96, 128, 192)])
+def test_fused_output_quantisation_mlp(backend, m, hidden, ffn):
+    """MLP up -> GELU -> down with the up epilogue emitting the down's NVFP4 operand: the emitted
+    codes/scales must equal what the standalone quantiser makes of the bf16 output, bit for bit,
+    and the down result must match the oracle chain."""
+    import thinfer_b200 as T
+    from thinfer_b200.backend import device_scales_bytes
+    from conftest import dev_scales_to_canonical
+
+    a, w1, b1 = _inputs(m, ffn, hidden, 21)
+    _, w2, b2 = _inputs(m, hidden, ffn, 22)
+    be = backend
+    W1, W2 = T.Nvfp4Weight.from_dense(be, w1, b1), T.Nvfp4Weight.from_dense(be, w2, b2)
+    ga, g_mid = O.global_scale(O.amax_bf16(a)), 0.0009765625
+    abuf = be.upload(a)
+    mid = be.allocate(m * ffn * 2)
+    qc = be.allocate(m * ffn // 2)
+    qs = be.allocate(device_scales_bytes(m, ffn))
+    be.write_buffer(qs, np.full(qs.len, 0x7F, np.uint8))  # NaN canary in every scale byte
+    out = be.allocate(m * hidden * 2)
+    sc = be.scope()
+    sc.linear(abuf, m, W1, ga, mid, act=1, out_nvfp4=(qc, qs, g_mid))
+    sc.matmul(qc, qs, m, W2, g_mid, out)
+    be.submit(30000)
+    mid_h = be.read_buffer(mid, np.uint16).reshape(m, ffn)
+    codes = be.read_buffer(qc).reshape(m, ffn // 2)
+    scales = dev_scales_to_canonical(be.read_buffer(qs), m, ffn)
+    oc, os_ = O.quantize_act(mid_h, g_mid)  # oracle quantiser on the GPU's own bf16 output
+    assert np.array_equal(codes, oc) and np.array_equal(scales, os_)
+    got = be.read_buffer(out, np.uint16).reshape(m, hidden)
+    assert not np.isnan(O.bf16_to_f32(got)).any()
+    # bf16-free variant gives the same final result
+    out2 = be.allocate(m * hidden * 2)
+    sc.linear(abuf, m, W1, ga, None, act=1, out_nvfp4=(qc, qs, g_mid))
+    sc.matmul(qc, qs, m, W2, g_mid, out2)
+    be.submit(30000)
+    assert np.array_equal(be.read_buffer(out2, np.uint16).reshape(m, hidden), got)
+    # oracle chain
+    w1c, w1s, g1 = O.quantize_weight(w1)
+    w2c, w2s, g2 = O.quantize_weight(w2)
+    mid_o = O.linear(a, ga, w1c, w1s, g1, bias=b1, act=1)
+    want = O.linear(mid_o, g_mid, w2c, w2s, g2, bias=b2)
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= 5e-3  # GELU approximation flips a few FP4 codes
+    for b in (abuf, mid, qc, qs, out, out2):
+        be.free(b)
+    W1.free(be)
+    W2.free(be)
 
 
 def test_linearity_and_zero_activation(backend):

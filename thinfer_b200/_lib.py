@@ -14,7 +14,7 @@ CAT_WEIGHTS, CAT_WORKSPACE, CAT_STAGING = 0, 1, 2
 DTYPE_F32, DTYPE_BF16 = 0, 1
 SCALES_CANONICAL, SCALES_DEVICE = 0, 1
 ACT_NONE, ACT_GELU_TANH = 0, 1
-LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS = 1, 2
+LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS, LINEAR_OUT_NVFP4, LINEAR_NO_BF16_OUT = 1, 2, 4, 8
 
 
 class Buf(C.Structure):
@@ -29,7 +29,8 @@ class LinearArgs(C.Structure):
         ("a_bf16", Buf), ("w_codes", Buf), ("w_scales", Buf), ("bias_bf16", Buf),
         ("gate_bf16", Buf), ("residual_bf16", Buf), ("out_bf16", Buf),
         ("act", C.c_uint32), ("parity_mode", C.c_uint32), ("n_offset", C.c_uint32),
-        ("ldo", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("ldo", C.c_uint32), ("flags", C.c_uint32), ("out_global", C.c_float),
+        ("out_codes", Buf), ("out_scales", Buf),
     ]
 
 

@@ -252,7 +252,8 @@ class BatchScope:
     def act_quant_shared(self, a_bf16: Buf, m: int, k: int, global_scale: float) -> None:
         _check(self.be.lib.tnf_quantize_act_shared(self.be._ctx, a_bf16, m, k, global_scale))
 
-    def _args(self, m, w: Nvfp4Weight, a, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias):
+    def _args(self, m, w: Nvfp4Weight, a, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias,
+              out_nvfp4=None):
         args = LinearArgs()
         args.m, args.n, args.k = m, w.n, w.k
         args.a_global, args.w_global = a_global, w.global_scale
@@ -262,23 +263,31 @@ class BatchScope:
         args.bias_bf16 = use_bias if use_bias is not None else _NONE
         args.gate_bf16 = gate if gate is not None else _NONE
         args.residual_bf16 = residual if residual is not None else _NONE
-        args.out_bf16 = out
+        args.out_bf16 = out if out is not None else _NONE
         args.act, args.parity_mode = act, int(chain)
+        if out_nvfp4 is not None:  # (codes, device-layout scales, per-tensor scale): quantised copy of the output
+            args.out_codes, args.out_scales, args.out_global = out_nvfp4
+            flags |= L.LINEAR_OUT_NVFP4 | (L.LINEAR_NO_BF16_OUT if out is None else 0)
+        else:
+            args.out_codes, args.out_scales = _NONE, _NONE
         args.n_offset, args.ldo, args.flags = n_offset, ldo, flags
         return args
 
-    def linear(self, a_bf16: Optional[Buf], m: int, w: Nvfp4Weight, a_global: float, out: Buf, act: int = L.ACT_NONE,
-               gate: Optional[Buf] = None, residual: Optional[Buf] = None, chain: bool = False, n_offset: int = 0,
-               ldo: int = 0, flags: int = 0, bias=None) -> None:
-        """out = epilogue(a_global*w_global * (quant(A) . Wq^T)): the ``biased`` call site, fused."""
-        args = self._args(m, w, a_bf16, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias)
+    def linear(self, a_bf16: Optional[Buf], m: int, w: Nvfp4Weight, a_global: float, out: Optional[Buf],
+               act: int = L.ACT_NONE, gate: Optional[Buf] = None, residual: Optional[Buf] = None, chain: bool = False,
+               n_offset: int = 0, ldo: int = 0, flags: int = 0, bias=None, out_nvfp4=None) -> None:
+        """out = epilogue(a_global*w_global * (quant(A) . Wq^T)): the ``biased`` call site, fused.
+
+        ``out_nvfp4=(codes, scales_device, g)`` also emits the result quantised to NVFP4 (the A operand
+        of the next linear: MLP up -> GELU -> down); ``out=None`` then skips the bf16 store."""
+        args = self._args(m, w, a_bf16, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias, out_nvfp4)
         _check(self.be.lib.tnf_linear_nvfp4(self.be._ctx, C.byref(args)))
 
-    def matmul(self, a_codes: Buf, a_scales_device: Buf, m: int, w: Nvfp4Weight, a_global: float, out: Buf,
+    def matmul(self, a_codes: Buf, a_scales_device: Buf, m: int, w: Nvfp4Weight, a_global: float, out: Optional[Buf],
                act: int = L.ACT_NONE, gate=None, residual=None, chain: bool = False, n_offset: int = 0, ldo: int = 0,
-               flags: int = 0, bias=None) -> None:
+               flags: int = 0, bias=None, out_nvfp4=None) -> None:
         """The GEMM alone on pre-quantised operands."""
-        args = self._args(m, w, None, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias)
+        args = self._args(m, w, None, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias, out_nvfp4)
         _check(self.be.lib.tnf_gemm_nvfp4(self.be._ctx, C.byref(args), a_codes, a_scales_device))
 
     def submit(self, timeout_ms: int = 0) -> None:

@@ -224,9 +224,30 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   if (!w_codes) return st;
   uint8_t* w_scales = resolve(ctx, a->w_scales, sf_device_bytes(a->n, a->k), "w_scales", &st);
   if (!w_scales) return st;
-  uint8_t* out = resolve(ctx, a->out_bf16, (uint64_t(a->m - 1) * ldo + a->n_offset + a->n) * 2, "out_bf16", &st);
-  if (!out) return st;
+  const bool q_out = (a->flags & TNF_LINEAR_OUT_NVFP4) != 0;
+  const bool store_bf16 = !(q_out && (a->flags & TNF_LINEAR_NO_BF16_OUT));
+  uint8_t* out = nullptr;
+  if (store_bf16) {
+    out = resolve(ctx, a->out_bf16, (uint64_t(a->m - 1) * ldo + a->n_offset + a->n) * 2, "out_bf16", &st);
+    if (!out) return st;
+  }
   GemmParams p{};
+  p.store_bf16 = store_bf16 ? 1u : 0u;
+  if (q_out) {
+    if (a->n % 64 != 0 || !(a->out_global > 0.0f) || (a->flags & TNF_LINEAR_SCATTER_PEERS)) {
+      set_error("TNF_LINEAR_OUT_NVFP4 needs n %% 64 == 0 (n=%u), out_global > 0 and no peer scatter", a->n);
+      return TNF_ERR_INVALID_ARGUMENT;
+    }
+    p.q_codes = resolve(ctx, a->out_codes, uint64_t(a->m) * (a->n / 2), "out_codes", &st);
+    if (!p.q_codes) return st;
+    p.q_scales = resolve(ctx, a->out_scales, sf_device_bytes(a->m, a->n), "out_scales", &st);
+    if (!p.q_scales) return st;
+    p.q_global = a->out_global;
+    p.q_inv_t = 1.0f / (6.0f * a->out_global);
+    p.q_k_atoms = sf_k_atoms(a->n);
+    if ((a->n / 64) % 4 != 0)  // K-padding atoms of the next operand must hold benign (zero) scales
+      TNF_CUDA(cudaMemsetAsync(p.q_scales, 0, sf_device_bytes(a->m, a->n), ctx->compute), "out_scales clear");
+  }
   p.m = a->m; p.n = a->n; p.k = a->k;
   p.k_atoms = sf_k_atoms(a->k);
   p.alpha = a->a_global * a->w_global;
@@ -258,7 +279,7 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.chain = a->parity_mode;
   p.status = ctx->dwords;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
-  if (gemm_use_pair(a->m, a->n, a->k)) {
+  if (q_out || gemm_use_pair(a->m, a->n, a->k)) {
     const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
     const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, 128));
     const CUtensorMap* msa = get_map(ctx, scales_spec(a_scales, a->m, a->k));
@@ -266,7 +287,8 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
     if (!ma || !mw || !msa || !msb) return TNF_ERR_INVALID_ARGUMENT;
     CUtensorMap outs[kMaxPeers];
     for (uint32_t d = 0; d < p.n_out; ++d) {
-      const CUtensorMap* mo = get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo));
+      // without a bf16 destination the map is never used; any valid one fills the slot
+      const CUtensorMap* mo = store_bf16 ? get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo)) : ma;
       if (!mo) return TNF_ERR_INVALID_ARGUMENT;
       outs[d] = *mo;
     }
@@ -287,7 +309,7 @@ using namespace tnf;
 
 extern "C" {
 
-uint32_t tnf_abi_version(void) { return 1; }
+uint32_t tnf_abi_version(void) { return 2; }
 const char* tnf_last_error(void) { return g_err; }
 
 int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out) {

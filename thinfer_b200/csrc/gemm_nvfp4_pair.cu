@@ -27,6 +27,7 @@
 
 #include "internal.h"
 #include "ptx.cuh"
+#include "quant_dev.cuh"
 
 namespace tnf {
 
@@ -97,6 +98,8 @@ template <bool kGelu, bool kChain, bool kGate>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
                                                    uint8_t* buf_gen, int lane) {
   const bool row_ok = row < p.m;
+  uint32_t cw[8], sw = 0;  // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes
+  uint4 prev = make_uint4(0, 0, 0, 0);
 #pragma unroll
   for (int sub = 0; sub < 2; ++sub) {
     uint4 b4[4], g4[4], s4[4];
@@ -116,7 +119,31 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
       const int j = sub * 4 + jj;
       const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4[jj], g4[jj], s4[jj]);
       *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+      if (p.q_codes) {  // uniform: quantise the bf16-ROUNDED values, 16 columns at a time
+        if (j & 1) {
+          const uint32_t w[8] = {prev.x, prev.y, prev.z, prev.w, o.x, o.y, o.z, o.w};
+          float x[16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x[2 * i] = bf16_lo(w[i]);
+            x[2 * i + 1] = bf16_hi(w[i]);
+          }
+          uint32_t lo, hi;
+          const uint32_t sc = quant_block16(x, p.q_global, p.q_inv_t, lo, hi);
+          cw[j - 1] = lo;
+          cw[j] = hi;
+          sw |= sc << (8 * (j >> 1));
+        } else {
+          prev = o;
+        }
+      }
     }
+  }
+  if (p.q_codes && row_ok && ncol0 < p.n) {  // n % 64 == 0: the whole group is in range
+    uint4* qc = reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.n >> 1) + (ncol0 >> 1));
+    qc[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    qc[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
+    *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, ncol0 >> 4, p.q_k_atoms)) = sw;
   }
 }
 
@@ -315,9 +342,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       tc_fence_after();
       if (ttr) p.trace[1024 + it * 8 + 4] = clock64();
       const uint32_t t_addr = tmem_base + b * kAccStride + ((q * 32u) << 16);
-      uint32_t ra[64], rb[64];
-      tmem_ld_32x32b_x32(t_addr + g0 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&ra[0]));
-      tmem_ld_32x32b_x32(t_addr + g0 * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&ra[32]));
+      uint32_t r[64];
+      tmem_ld_32x32b_x32(t_addr + g0 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_ld_32x32b_x32(t_addr + g0 * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
       tmem_ld_wait();
       if (ttr) p.trace[1024 + it * 8 + 7] = clock64();
       if (h == 0) {  // the overlapping columns are in registers: the next tile's MMA may start
@@ -326,38 +353,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (lane == 0) mbar_arrive_cluster(acc_free_leader);
         if (ttr) p.trace[1024 + it * 8 + 5] = clock64();
       }
-      // second group's TMEM read runs under the first group's math
-      tmem_ld_32x32b_x32(t_addr + g1 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&rb[0]));
-      tmem_ld_32x32b_x32(t_addr + g1 * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&rb[32]));
       const uint32_t row = row0 + lane;
-      if (row0 < p.m) {  // warp-uniform
-        if (n0 + g0 * 64u < p.n) {
-          if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
-          __syncwarp();
-          epilogue_pair_dispatch(mode, ra, p, row, n0 + g0 * 64u, buf_gen, lane);
-          fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
-          __syncwarp();
-          if (lane == 0) {
-            if (!(p.diag & 1u))
-              for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(n0 + g0 * 64u), int32_t(row0));
-            bulk_commit_group();
-          }
+#pragma unroll 1
+      for (uint32_t half = 0; half < 2; ++half) {
+        const uint32_t g = half ? g1 : g0;
+        if (half) {
+          tmem_ld_32x32b_x32(t_addr + g * 64u, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_ld_32x32b_x32(t_addr + g * 64u + 32u, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tmem_ld_wait();
         }
-        tmem_ld_wait();
-        if (n0 + g1 * 64u < p.n) {
-          if (lane == 0) bulk_wait_group_read<0>();
-          __syncwarp();
-          epilogue_pair_dispatch(mode, rb, p, row, n0 + g1 * 64u, buf_gen, lane);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) {
-            if (!(p.diag & 1u))
-              for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(n0 + g1 * 64u), int32_t(row0));
-            bulk_commit_group();
-          }
+        const uint32_t ncol0 = n0 + g * 64u;
+        if (row0 >= p.m || ncol0 >= p.n) continue;  // warp-uniform
+        if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
+        __syncwarp();
+        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, lane);
+        fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
+        __syncwarp();
+        if (lane == 0) {
+          if (!(p.diag & 1u) && p.store_bf16)
+            for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(ncol0), int32_t(row0));
+          bulk_commit_group();
         }
-      } else {
-        tmem_ld_wait();
       }
       if (ttr) p.trace[1024 + it * 8 + 6] = clock64();
     }

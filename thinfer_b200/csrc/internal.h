@@ -40,6 +40,11 @@ struct GemmParams {
   uint32_t ldo, n_offset;
   uint32_t act, chain;
   uint32_t tiles_m, tiles_n;
+  uint8_t* q_codes;            // optional NVFP4 copy of the output: codes [m, n/2] ...
+  uint8_t* q_scales;           // ... and device-layout scales of an [m, n] operand
+  float q_global, q_inv_t;     // its per-tensor scale g and 1/(6g)
+  uint32_t q_k_atoms;          // sf_k_atoms(n)
+  uint32_t store_bf16;         // 0: skip the bf16 store
   uint32_t* status;            // device status word
   uint32_t diag;               // diagnostic bits from TNF_GEMM_DIAG (0 in normal use): 1 no output stores,
                                // 2 scale copies only on the first K tile, 4 no MMA, 8 no operand loads,

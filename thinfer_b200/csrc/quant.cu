@@ -13,45 +13,9 @@
 #include <cstdint>
 
 #include "internal.h"
+#include "quant_dev.cuh"
 
 namespace tnf {
-
-__device__ __forceinline__ float e4m3_decode_dev(uint32_t c) {
-  uint32_t e = (c >> 3) & 0xFu, m = c & 7u;
-  return e == 0 ? float(m) * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
-}
-
-// 16 f32 values -> 8 code bytes (returned as two u32) + the E4M3 scale byte.
-__device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], float g, uint32_t& lo, uint32_t& hi) {
-  float bmax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(x[i]));
-  float t = __fmul_rn(6.0f, g);
-  float inv_t = __fdiv_rn(1.0f, t);
-  float s_raw = __fmul_rn(bmax, inv_t);
-  uint32_t sc = (uint32_t)__nv_cvt_float_to_fp8(s_raw, __NV_SATFINITE, __NV_E4M3) & 0xFFu;
-  if (sc == 0x7Fu || sc == 0xFFu) sc = 0;  // NaN scale -> treated as a zero block
-  sc &= 0x7Fu;
-  lo = 0;
-  hi = 0;
-  if (sc != 0) {
-    float d = __fmul_rn(e4m3_decode_dev(sc), g);
-    float inv_d = __fdiv_rn(1.0f, d);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float2 v = make_float2(__fmul_rn(x[2 * i], inv_d), __fmul_rn(x[2 * i + 1], inv_d));
-      uint32_t b = (uint32_t)__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest) & 0xFFu;
-      if (i < 4) lo |= b << (8 * i);
-      else hi |= b << (8 * (i - 4));
-    }
-  }
-  return sc;
-}
-
-__device__ __forceinline__ uint64_t sf_device_offset(uint32_t r, uint32_t b, uint32_t k_atoms) {
-  uint64_t atom = uint64_t(r >> 7) * k_atoms + (b >> 2);
-  return atom * 512u + (r & 31u) * 16u + ((r & 127u) >> 5) * 4u + (b & 3u);
-}
 
 // ---- absolute maximum -----------------------------------------------------------------------
 template <typename T>
@@ -72,7 +36,9 @@ __global__ void amax_kernel(const T* __restrict__ x, uint64_t n, uint32_t* __res
 // amax bits -> per-tensor scale amax/(6*448), 1.0 for an all-zero tensor.
 __global__ void global_scale_kernel(const uint32_t* amax_bits, float* g) {
   float a = __uint_as_float(*amax_bits);
-  *g = a > 0.0f ? __fdiv_rn(a, 2688.0f) : 1.0f;
+  float gv = a > 0.0f ? __fdiv_rn(a, 2688.0f) : 1.0f;
+  g[0] = gv;
+  g[1] = __fdiv_rn(1.0f, __fmul_rn(6.0f, gv));  // 1/(6g), shared by every block
 }
 
 // ---- block quantiser --------------------------------------------------------------------------
@@ -81,7 +47,7 @@ __global__ void global_scale_kernel(const uint32_t* amax_bits, float* g) {
 // written as zero. g_ptr (device) wins over g_val when not null.
 template <typename T, bool kDeviceLayout>
 __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32_t k, const float* __restrict__ g_ptr,
-                                float g_val, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                float g_val, float inv_t_val, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
                                 uint32_t k_atoms) {
   const uint32_t nb = k >> 4;
   const uint32_t nb_grid = kDeviceLayout ? k_atoms * 4u : nb;
@@ -89,11 +55,14 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
   uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= uint64_t(rows_grid) * nb_grid) return;
   uint32_t r = uint32_t(t / nb_grid), b = uint32_t(t % nb_grid);
-  if (r >= rows || b >= nb) {
-    if (kDeviceLayout) scales[sf_device_offset(r, b, k_atoms)] = 0;
-    return;
-  }
-  const float g = g_ptr ? *g_ptr : g_val;
+  // Device layout: the grid is padded so that each aligned group of 4 lanes owns one 4-byte word
+  // (row r, blocks 4i..4i+3); the word is assembled with shuffles and written by its first lane.
+  const bool valid = r < rows && b < nb;
+  if (!kDeviceLayout && !valid) return;
+  uint32_t sc = 0;
+  if (valid) {
+  const float g = g_ptr ? g_ptr[0] : g_val;
+  const float inv_t = g_ptr ? g_ptr[1] : inv_t_val;
   float x[16];
   const T* p = src + uint64_t(r) * k + uint64_t(b) * 16u;
   if constexpr (sizeof(T) == 2) {
@@ -114,10 +83,17 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
     }
   }
   uint32_t lo, hi;
-  uint32_t sc = quant_block16(x, g, lo, hi);
+  sc = quant_block16(x, g, inv_t, lo, hi);
   *reinterpret_cast<uint2*>(codes + uint64_t(r) * (k >> 1) + uint64_t(b) * 8u) = make_uint2(lo, hi);
-  if (kDeviceLayout) scales[sf_device_offset(r, b, k_atoms)] = uint8_t(sc);
-  else scales[uint64_t(r) * nb + b] = uint8_t(sc);
+  }
+  if (kDeviceLayout) {
+    uint32_t w = sc << (8u * (b & 3u));
+    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+    if ((b & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(r, b, k_atoms)) = w;
+  } else {
+    scales[uint64_t(r) * nb + b] = uint8_t(sc);
+  }
 }
 
 // canonical [rows, k/16] -> device layout, padding written as zero
@@ -149,17 +125,18 @@ cudaError_t launch_global_scale(const uint32_t* amax_bits, float* g, cudaStream_
 cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t k, const float* g_ptr, float g_val,
                             uint8_t* codes, uint8_t* scales, bool device_layout, cudaStream_t s) {
   const uint32_t k_atoms = sf_k_atoms(k);
+  const float inv_t_val = 1.0f / (6.0f * g_val);  // same f32 operations as the device and the oracle
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
   unsigned blocks = unsigned((threads + 255) / 256);
   if (dtype == 1) {
     auto* p = (const __nv_bfloat16*)src;
-    if (device_layout) quantize_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, codes, scales, k_atoms);
-    else quantize_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, codes, scales, k_atoms);
+    if (device_layout) quantize_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    else quantize_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
   } else {
     auto* p = (const float*)src;
-    if (device_layout) quantize_kernel<float, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, codes, scales, k_atoms);
-    else quantize_kernel<float, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, codes, scales, k_atoms);
+    if (device_layout) quantize_kernel<float, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    else quantize_kernel<float, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
   }
   return cudaGetLastError();
 }

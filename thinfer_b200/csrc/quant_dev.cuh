@@ -1,0 +1,47 @@
+// Device-side NVFP4 block quantiser shared by the standalone quantisers and the GEMM epilogue.
+// Explicitly rounded IEEE f32 operations and the hardware cvt.rn.satfinite narrowing: bit-exact
+// with the CPU oracle (see quant.cu).
+#pragma once
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+namespace tnf {
+
+__device__ __forceinline__ float e4m3_decode_dev(uint32_t c) {
+  uint32_t e = (c >> 3) & 0xFu, m = c & 7u;
+  return e == 0 ? float(m) * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
+}
+
+// 16 f32 values -> 8 code bytes (returned as two u32) + the E4M3 scale byte.
+__device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], float g, float inv_t, uint32_t& lo, uint32_t& hi) {
+  float bmax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(x[i]));
+  float s_raw = __fmul_rn(bmax, inv_t);
+  uint32_t sc = (uint32_t)__nv_cvt_float_to_fp8(s_raw, __NV_SATFINITE, __NV_E4M3) & 0xFFu;
+  if (sc == 0x7Fu || sc == 0xFFu) sc = 0;  // NaN scale -> treated as a zero block
+  sc &= 0x7Fu;
+  lo = 0;
+  hi = 0;
+  if (sc != 0) {
+    float d = __fmul_rn(e4m3_decode_dev(sc), g);
+    float inv_d = __fdiv_rn(1.0f, d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float2 v = make_float2(__fmul_rn(x[2 * i], inv_d), __fmul_rn(x[2 * i + 1], inv_d));
+      uint32_t b = (uint32_t)__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest) & 0xFFu;
+      if (i < 4) lo |= b << (8 * i);
+      else hi |= b << (8 * (i - 4));
+    }
+  }
+  return sc;
+}
+
+__device__ __forceinline__ uint64_t sf_device_offset(uint32_t r, uint32_t b, uint32_t k_atoms) {
+  uint64_t atom = uint64_t(r >> 7) * k_atoms + (b >> 2);
+  return atom * 512u + (r & 31u) * 16u + ((r & 127u) >> 5) * 4u + (b & 3u);
+}
+
+
+}  // namespace tnf
