@@ -194,24 +194,35 @@ typedef struct tnf_stack_linear {
   uint32_t n, k;
   uint32_t act;        /* TNF_ACT_* */
   uint32_t has_bias;
-  uint32_t input;      /* 0: the layer input X; 1: the previous linear's output */
+  uint32_t input;      /* 0: the stream's layer input X; 1: the previous linear's output; 2: the stream's
+                          auxiliary input (stands for the attention output that feeds the out-projection) */
   uint32_t stream_id;  /* which activation stream (0 img, 1 txt, 2 mod ...) */
 } tnf_stack_linear;
 
 /* Describe a stack of `layers` identical layers, each `n_linears` linears applied to
- * `n_streams` activation streams of m_rows[s] rows. Weights live in the pinned arena
- * `host_id` as consecutive per-linear records {codes, device scales, bias, f32 global};
- * tnf_stack_record_bytes gives the record size. `vram_budget` bounds resident + ring
- * weight bytes; ring_slots per linear kind defaults to 4 when 0 (residency.rs:50). */
+ * `n_streams` activation streams of m_rows[s] rows. Weights wait in the pinned arena
+ * `host_id`, layer-major then linear-minor, one record per linear: {codes [n,k/2], DEVICE
+ * scales, bias bf16 [n], f32 per-tensor scale}, each section 256-byte aligned
+ * (tnf_stack_record_offsets); tnf_stack_record_bytes gives the record size.
+ * `weight_budget_bytes` (0 = unlimited) bounds resident + ring weight bytes: every linear
+ * kind gets a ring of `ring_slots` records (0 = 4, thinfer-core/src/residency.rs:50) and the
+ * rest of the budget pins whole linear kinds across all layers, largest first (role-major
+ * pin plan). A budget below the ring reserve fails with TNF_ERR_BUDGET_EXCEEDED on the host.
+ * The last linear of a stream feeds the next layer's X when its n equals `hidden`. */
 uint64_t tnf_stack_record_bytes(uint32_t n, uint32_t k);
+int32_t tnf_stack_record_offsets(uint32_t n, uint32_t k, uint64_t out[4]); /* codes, scales, bias, global */
 int32_t tnf_stack_create(tnf_ctx* ctx, uint32_t layers, uint32_t n_linears, const tnf_stack_linear* linears,
                          uint32_t n_streams, const uint32_t* m_rows, uint32_t hidden, uint64_t host_id,
                          uint64_t weight_budget_bytes, uint32_t ring_slots, tnf_stack** out);
-/* One pass over all layers (one "DiT step" of the GEMM stack). x_ids[s] are [m_rows[s],
- * hidden] bf16 inputs; outputs are written to out_ids[s] ([m_rows[s], n_last]). */
-int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* out_ids, float a_global);
-/* out = {pinned layers' bytes, ring bytes, bytes uploaded in the last step, uploads in
- * the last step, resident linears, streamed linears}. */
+/* One pass over all layers (one "DiT step" of the GEMM stack), enqueued without blocking the
+ * host: uploads on the copy stream run ring_slots layers ahead of the GEMMs and wrap around to
+ * the next step's first layers. x_ids[s]: [m_rows[s], hidden] bf16 inputs; aux_ids[s]
+ * (may be NULL when no linear has input 2): [m_rows[s], k]; out_ids[s] receives the last
+ * layer's last linear of stream s. a_global: per-tensor activation scale used by every linear. */
+int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* aux_ids, const uint64_t* out_ids,
+                       float a_global);
+/* out = {resident weight bytes, ring bytes, bytes uploaded by the last step, uploads in
+ * the last step, resident (layer, linear) records, streamed records}. */
 int32_t tnf_stack_stats(tnf_stack* st, uint64_t out[6]);
 int32_t tnf_stack_destroy(tnf_stack* st);
 

@@ -73,7 +73,8 @@ SIGNATURES = {
     "tnf_stack_record_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
     "tnf_stack_create": (C.c_int32, [_ctx, C.c_uint32, C.c_uint32, C.POINTER(StackLinear), C.c_uint32, _u32p,
                                      C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, C.POINTER(C.c_void_p)]),
-    "tnf_stack_step": (C.c_int32, [C.c_void_p, _u64p, _u64p, C.c_float]),
+    "tnf_stack_record_offsets": (C.c_int32, [C.c_uint32, C.c_uint32, _u64p]),
+    "tnf_stack_step": (C.c_int32, [C.c_void_p, _u64p, _u64p, _u64p, C.c_float]),
     "tnf_stack_stats": (C.c_int32, [C.c_void_p, _u64p]),
     "tnf_stack_destroy": (C.c_int32, [C.c_void_p]),
     "tnf_comm_unique_id": (C.c_int32, [C.c_void_p]),
