@@ -1,0 +1,142 @@
+"""Multi-GPU arm of bench.py (launched by torchrun, one rank per GPU).
+
+Workload: BASELINE configs[4], the batched Wan-5B-shaped FFN pair at M = 26520 —
+up 3072 -> 14336 (+bias, tanh-GELU), down 14336 -> 3072 (+bias). Weights are split by OUTPUT
+columns over the ranks (each rank holds its slices resident); every rank holds the full
+activations and ends each linear with the full [M, N] output:
+  --gather fused : the GEMM epilogue TMA-stores each output tile into its own output buffer and
+                   into every peer's (CUDA IPC windows), then a stream-ordered barrier;
+  --gather nccl  : the GEMM writes its slice locally, then an NCCL all-gather of the slices.
+Strong scaling: total work is fixed as N grows. The output bytes every rank must receive
+((G-1)/G * 2*M*N) do not shrink with G, so NVLink ingest, not the tensor pipe, bounds this scheme.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+
+def run_multi_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import thinfer_b200 as T
+    from bench import (ClockSampler, HIDDEN, NOMINAL_FP4_TFLOPS, WAN_FFN, WAN_M, as_torch, cpu_sample, make_weight,
+                       measured_peaks, workload_config)
+    from thinfer_b200 import _lib as L
+    from thinfer_b200.nsplit import NSplitGroup, column_partition
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{local}"))
+    dev = f"cuda:{local}"
+    be = T.Backend(local)
+    sc = be.scope()
+    grp = NSplitGroup(be, rank, world)
+    M = WAN_M
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0xC5)  # same seed on every rank: identical full tensors, each rank keeps its slice
+
+    def sliced_weight(n, k):
+        # generate the rank's slice only; the per-tensor scale of a slice stands for the full tensor's
+        off, width = column_partition(n, world)[rank]
+        g = torch.Generator(device=dev)
+        g.manual_seed(0xC500 + n + 31 * rank)
+        return make_weight(be, T, L, g, width, k), off, width
+
+    w_up, up_off, up_w = sliced_weight(WAN_FFN, HIDDEN)
+    w_dn, dn_off, dn_w = sliced_weight(HIDDEN, WAN_FFN)
+    x = be.allocate(M * HIDDEN * 2)
+    h = be.allocate(M * WAN_FFN * 2)
+    y = be.allocate(M * HIDDEN * 2)
+    as_torch(be, x, torch.bfloat16, (M, HIDDEN)).copy_(torch.randn(M, HIDDEN, device=dev, generator=gen).to(torch.bfloat16))
+    torch.cuda.synchronize()
+    fused = args.gather == "fused"
+    if fused:
+        grp.register_output(0, h)
+        grp.register_output(1, y)
+    ga_x, ga_h = 0.0018, 0.0009765625  # calibrated static activation scales (N(0,1) input; GELU output)
+    compute = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+
+    def step():
+        if fused:
+            sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN, flags=grp.scatter_flags(0))
+            grp.barrier()
+            sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN, flags=grp.scatter_flags(1))
+            grp.barrier()
+        else:
+            sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN)
+            grp.all_gather_cols(h, M, WAN_FFN)
+            sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN)
+            grp.all_gather_cols(y, M, HIDDEN)
+
+    def compute_only():  # same GEMMs, no delivery to peers (for the breakdown)
+        sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN)
+        sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN)
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record(compute)
+        for _ in range(n):
+            fn()
+        e1.record(compute)
+        be.submit()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # max over ranks
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    be.submit()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed(step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_compute = timed(compute_only, max(2, min(args.steps, 5)))
+
+    # end to end through the public API with host buffers: x in from pinned memory, y back
+    from bench import _e2e_step, _pinned
+    hin, hout = _pinned(be, M * HIDDEN * 2), _pinned(be, M * HIDDEN * 2)
+    hin["np"][:] = as_torch(be, x, torch.int16, (M * HIDDEN,)).cpu().numpy().view(np.uint16)
+    ms_e2e = timed(lambda: _e2e_step(be, step, x, y, hin, hout), max(2, min(args.steps, 5)))
+    finite = bool(np.isfinite((hout["np"].astype(np.uint32) << 16).view(np.float32)).all())
+
+    flops = 2.0 * M * HIDDEN * WAN_FFN * 2
+    out_bytes = 2.0 * M * (WAN_FFN + HIDDEN)
+    ingest = out_bytes * (world - 1) / world  # bytes every rank must receive per step
+    if rank == 0:
+        peaks = measured_peaks()
+        t_link = ingest / 770e9 * 1e3  # measured peer-copy bandwidth per direction on this pool
+        t_math = flops / world / (4.0 * peaks["bf16_sustained"] * 1e12) * 1e3
+        line = {
+            "metric": "nvfp4_linear_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3 block scales, f32 accumulate, bf16 in/out)",
+            "data": "synthetic (seeded torch.randn on device: weights N(0,0.02) quantised by the library, activations N(0,1) bf16)",
+            "config": dict(workload_config(world), gather=args.gather),
+            "ms_compute_only": ms_compute, "ms_gather_exposed": ms - ms_compute,
+            "ingest_bytes_per_rank": ingest, "nvlink_gbs_per_rank": ingest / (ms * 1e-3) / 1e9,
+            "roofline": {"bound": "nvlink" if t_link > t_math else "tensor", "achieved": ingest / (ms * 1e-3) / 1e9,
+                         "peak": 770.0, "unit": "GB/s", "frac": max(t_link, t_math) / ms,
+                         "target_ms": max(t_link, t_math), "t_link_ms": t_link, "t_math_ms": t_math, "traffic": None,
+                         "note": "target = slower of (FLOPs / 4x measured sustained bf16) and (ingest bytes / measured 770 GB/s peer copy)"},
+            "clocks": clocks,
+            "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": finite},
+            "gpu_launches": args.steps * 4,
+            "frac_of_nominal_fp4": flops / (ms * 1e-3) / 1e12 / (NOMINAL_FP4_TFLOPS * world),
+        }
+        print(json.dumps(line))
+    be.submit()
+    dist.barrier()
+    be.close()
+    dist.destroy_process_group()

@@ -235,9 +235,15 @@ int32_t tnf_comm_init(tnf_ctx* ctx, int32_t world, int32_t rank, const void* uni
 /* All-gather the column slices of an N-split output: every rank holds out[m, n_total]
  * with its own n_local columns at rank*n_local filled; on return all columns are filled. */
 int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t n_total, uint32_t n_local);
-/* Peer output windows for the fused epilogue scatter: 64-byte CUDA IPC handles. */
+/* Peer output windows for the fused epilogue scatter. tnf_ipc_export gives the 64-byte CUDA
+ * IPC handle of a buffer; tnf_peer_outputs opens the other ranks' handles of the SAME logical
+ * output as window set `set` (0..3). A linear with TNF_LINEAR_SCATTER_PEERS | TNF_LINEAR_PEER_SET(set)
+ * then stores every output tile to its own out_bf16 and to each window of that set (plain
+ * TMA stores into peer memory, no multicast). Follow with tnf_comm_barrier before any rank
+ * reads the gathered output. */
 int32_t tnf_ipc_export(tnf_ctx* ctx, uint64_t id, void* handle_64);
-int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t n_peers, const void* handles_64xn);
+int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t set, int32_t n_peers, const void* handles_64xn);
+#define TNF_LINEAR_PEER_SET(i) (((uint32_t)(i) & 3u) << 8)
 /* Stream-ordered barrier across the communicator (after a scatter epilogue). */
 int32_t tnf_comm_barrier(tnf_ctx* ctx);
 

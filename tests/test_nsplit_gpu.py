@@ -1,0 +1,91 @@
+"""N-split on real GPUs (2 ranks, one process per GPU): the fused peer-store epilogue and the NCCL
+all-gather must both reproduce the unsplit result. Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    import oracle as O
+    import thinfer_b200 as T
+    from thinfer_b200.nsplit import NSplitGroup, column_partition
+
+    m, n, k = 300, 1024, 512
+    a = O.f32_to_bf16(O.gaussian(m * k, 1).reshape(m, k))
+    w = (O.gaussian(n * k, 2) * np.float32(0.03)).reshape(n, k)
+    bias = O.f32_to_bf16(O.gaussian(n, 3) * np.float32(0.01))
+    wc, ws, gw = O.quantize_weight(w)
+    ga = O.global_scale(O.amax_bf16(a))
+    want = O.linear(a, ga, wc, ws, gw, bias=bias, act=1)
+    be = T.Backend(rank)
+    grp = NSplitGroup(be, rank, world)
+    off, width = column_partition(n, world)[rank]
+    W = T.Nvfp4Weight.from_packed(be, wc[off:off + width], ws[off:off + width], gw, bias[off:off + width])
+    abuf = be.upload(a)
+    ok = True
+    for mode in ("fused", "nccl"):
+        out = be.allocate(m * n * 2)
+        be.write_buffer(out, np.full(m * n, 0x7FC0, np.uint16))
+        be.submit()
+        dist.barrier()
+        sc = be.scope()
+        if mode == "fused":
+            grp.register_output(0, out)
+            sc.linear(abuf, m, W, ga, out, act=1, n_offset=off, ldo=n, flags=grp.scatter_flags(0))
+            grp.barrier()
+        else:
+            sc.linear(abuf, m, W, ga, out, act=1, n_offset=off, ldo=n)
+            grp.all_gather_cols(out, m, n)
+        be.submit(30000)
+        dist.barrier()
+        got = be.read_buffer(out, np.uint16).reshape(m, n)
+        g, e = O.bf16_to_f32(got).astype(np.float64), O.bf16_to_f32(want).astype(np.float64)
+        err = np.linalg.norm(g - e) / np.linalg.norm(e)
+        ok = ok and bool(err <= 1e-3) and not np.isnan(g).any()
+        dist.barrier()
+    t = torch.tensor([1 if ok else 0], device=f"cuda:{rank}")
+    dist.all_reduce(t)
+    if rank == 0:
+        ret.put(int(t.item()))
+    be.submit()
+    dist.barrier()  # no rank leaves while a peer may still hold its windows
+    be.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_scatter_and_gather():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert p.exitcode == 0
+    assert ret.get(timeout=5) == 2

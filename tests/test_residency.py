@@ -87,8 +87,8 @@ def test_stack_streamed_equals_resident_and_oracle(backend):
             got1 = be.read_buffer(ob[1], np.uint16)[:192].reshape(1, 192)
             results.append((got0, got1))
             s = st.stats()
-            if budget:
-                assert s["uploads_last_step"] == s["streamed_records"] + (sum(1 for _ in specs) * 0)
+            if budget and step > 0:  # the first step also fills the rings; afterwards: each streamed record once
+                assert s["uploads_last_step"] == s["streamed_records"]
         be.lib.tnf_stack_destroy(st._stack)
         st._stack = type(st._stack)()
     for got0, got1 in results:

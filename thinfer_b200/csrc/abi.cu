@@ -267,11 +267,12 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.out[0] = reinterpret_cast<uint16_t*>(out);
   p.n_out = 1;
   if (a->flags & TNF_LINEAR_SCATTER_PEERS) {
-    if (ctx->n_peers <= 0) {
-      set_error("TNF_LINEAR_SCATTER_PEERS without tnf_peer_outputs");
+    const int set = int((a->flags >> 8) & 3u);
+    if (ctx->n_peers[set] <= 0) {
+      set_error("TNF_LINEAR_SCATTER_PEERS: peer set %d has no windows (tnf_peer_outputs)", set);
       return TNF_ERR_INVALID_ARGUMENT;
     }
-    for (int i = 0; i < ctx->n_peers; ++i) p.out[p.n_out++] = reinterpret_cast<uint16_t*>(ctx->peer_out[i]);
+    for (int i = 0; i < ctx->n_peers[set]; ++i) p.out[p.n_out++] = reinterpret_cast<uint16_t*>(ctx->peer_out[set][i]);
   }
   p.ldo = ldo;
   p.n_offset = a->n_offset;

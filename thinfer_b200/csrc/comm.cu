@@ -86,9 +86,11 @@ void tnf_comm_teardown(tnf_ctx* ctx) {
     if (api) api->CommDestroy(static_cast<ncclComm_t>(ctx->nccl_comm));
     ctx->nccl_comm = nullptr;
   }
-  for (int i = 0; i < ctx->n_peers; ++i)
-    if (ctx->peer_out[i]) cudaIpcCloseMemHandle(ctx->peer_out[i]);
-  ctx->n_peers = 0;
+  for (int s = 0; s < tnf_ctx::kPeerSets; ++s) {
+    for (int i = 0; i < ctx->n_peers[s]; ++i)
+      if (ctx->peer_out[s][i]) cudaIpcCloseMemHandle(ctx->peer_out[s][i]);
+    ctx->n_peers[s] = 0;
+  }
   if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
   ctx->gather_tmp = nullptr;
 }
@@ -196,25 +198,25 @@ int32_t tnf_ipc_export(tnf_ctx* ctx, uint64_t id, void* handle_64) {
   return TNF_OK;
 }
 
-int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t n_peers, const void* handles_64xn) {
-  if (!ctx || n_peers < 0 || n_peers > kMaxPeers - 1 || (n_peers > 0 && !handles_64xn)) {
-    set_error("tnf_peer_outputs: bad arguments (n_peers %d, at most %d)", n_peers, kMaxPeers - 1);
+int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t set, int32_t n_peers, const void* handles_64xn) {
+  if (!ctx || set < 0 || set >= tnf_ctx::kPeerSets || n_peers < 0 || n_peers > kMaxPeers - 1 || (n_peers > 0 && !handles_64xn)) {
+    set_error("tnf_peer_outputs: bad arguments (set %d of %d, n_peers %d, at most %d)", set, tnf_ctx::kPeerSets, n_peers, kMaxPeers - 1);
     return TNF_ERR_INVALID_ARGUMENT;
   }
   cudaError_t e = cudaSetDevice(ctx->device);
   if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
   e = cudaStreamSynchronize(ctx->compute);
   if (e != cudaSuccess) return cuda_fail(e, "tnf_peer_outputs sync");
-  for (int i = 0; i < ctx->n_peers; ++i)
-    if (ctx->peer_out[i]) cudaIpcCloseMemHandle(ctx->peer_out[i]);
-  ctx->n_peers = 0;
+  for (int i = 0; i < ctx->n_peers[set]; ++i)
+    if (ctx->peer_out[set][i]) cudaIpcCloseMemHandle(ctx->peer_out[set][i]);
+  ctx->n_peers[set] = 0;
   for (int i = 0; i < n_peers; ++i) {
     cudaIpcMemHandle_t h;
     std::memcpy(&h, static_cast<const uint8_t*>(handles_64xn) + 64 * i, 64);
     void* p = nullptr;
     e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle");
-    ctx->peer_out[ctx->n_peers++] = p;
+    ctx->peer_out[set][ctx->n_peers[set]++] = p;
   }
   return TNF_OK;
 }

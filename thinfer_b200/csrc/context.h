@@ -46,8 +46,9 @@ struct tnf_ctx {
   uint32_t* dwords = nullptr;
   std::map<tnf::MapSpec, CUtensorMap> maps;
   // fused-scatter peer windows (opened CUDA IPC mappings), index 0 unused
-  void* peer_out[tnf::kMaxPeers] = {nullptr};
-  int n_peers = 0;
+  static constexpr int kPeerSets = 4;
+  void* peer_out[kPeerSets][tnf::kMaxPeers] = {{nullptr}};
+  int n_peers[kPeerSets] = {0, 0, 0, 0};
   // NCCL
   void* nccl_comm = nullptr;
   int world = 1, rank = 0;
