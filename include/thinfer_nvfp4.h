@@ -158,6 +158,17 @@ enum {
 
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);
 
+/* Same linear, for callers that must not allocate device memory (a fixed memory plan, a
+ * latency-critical thread, a host that forbids allocation after start-up). It has no counterpart
+ * in the reference. The quantised activations go to a 16 MiB array built into the library
+ * image (tnf_noalloc_scratch_bytes) instead of context scratch grown with cudaMalloc; a problem
+ * whose m*k/2 + tnf_device_scales_bytes(m,k) exceeds it is refused with
+ * TNF_ERR_INVALID_ARGUMENT. flags must be 0. The first call on a device resolves the array's
+ * device address: make it before any stream capture. All calls share the array, which keeps the
+ * last call's contents; calls whose kernels overlap on the GPU race on it. */
+int32_t tnf_linear_nvfp4_noalloc(tnf_ctx* ctx, const tnf_linear_args* args);
+uint64_t tnf_noalloc_scratch_bytes(void);
+
 /* Quantise A once into context scratch so that several linears can share it (q, k and v
  * read one A: thinfer-models/src/qwen_image/dit.rs:511-560). Follow with
  * tnf_linear_nvfp4(flags = TNF_LINEAR_A_PREQUANTIZED). */

@@ -62,6 +62,8 @@ SIGNATURES = {
     "tnf_prepare_scales": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, Buf]),
     "tnf_quantize_act": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float, C.c_int32, Buf, Buf, C.POINTER(C.c_float)]),
     "tnf_linear_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_linear_nvfp4_noalloc": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_noalloc_scratch_bytes": (C.c_uint64, []),
     "tnf_quantize_act_shared": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float]),
     "tnf_gemm_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs), Buf, Buf]),
     "tnf_host_register": (C.c_int32, [_ctx, C.c_void_p, C.c_uint64, _u64p]),
