@@ -140,7 +140,7 @@ int make_tensor_map(CUtensorMap* out, const MapSpec& sp) {
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, sp.elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                   const_cast<void*>(sp.base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  sp.swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  sp.swizzle128 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (sp.swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p dims %llu x %llu stride %llu box %u x %u)", int(r),
@@ -166,8 +166,12 @@ static MapSpec codes_spec(const void* base, uint32_t rows, uint32_t k, uint32_t 
   return MapSpec{base, 1, k / 2, rows, k / 2, 128, box_rows, 1};
 }
 // device-layout scales viewed as rows of 128 bytes: box = 16 rows = four 512-byte atoms
-static MapSpec scales_spec(const void* base, uint32_t rows, uint32_t k) {
-  return MapSpec{base, 1, 128, sf_device_bytes(rows, k) / 128, 128, 128, 16, 0};
+static MapSpec scales_spec(const void* base, uint32_t rows, uint32_t k, uint32_t atoms_per_box) {
+  return MapSpec{base, 1, 128, sf_device_bytes(rows, k) / 128, 128, 128, atoms_per_box * 4, 0};
+}
+// codes for the pair kernel: box {kb*32 bytes, 128 rows}, swizzle = box width
+static MapSpec pair_codes_spec(const void* base, uint32_t rows, uint32_t k, uint32_t kb) {
+  return MapSpec{base, 1, k / 2, rows, k / 2, kb * 32, 128, kb * 32};
 }
 // bf16 output window [m, n] with leading dimension ldo: box {64 columns, 32 rows}, 128-byte swizzle
 static MapSpec out_spec(const void* base, uint32_t m, uint32_t n, uint32_t ldo) {
@@ -281,10 +285,11 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.status = ctx->dwords;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
   if (q_out || gemm_use_pair(a->m, a->n, a->k)) {
-    const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
-    const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, 128));
-    const CUtensorMap* msa = get_map(ctx, scales_spec(a_scales, a->m, a->k));
-    const CUtensorMap* msb = get_map(ctx, scales_spec(w_scales, a->n, a->k));
+    const uint32_t kb = gemm_pair_kblocks();
+    const CUtensorMap* ma = get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb));
+    const CUtensorMap* mw = get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb));
+    const CUtensorMap* msa = get_map(ctx, scales_spec(a_scales, a->m, a->k, kb));
+    const CUtensorMap* msb = get_map(ctx, scales_spec(w_scales, a->n, a->k, kb));
     if (!ma || !mw || !msa || !msb) return TNF_ERR_INVALID_ARGUMENT;
     CUtensorMap outs[kMaxPeers];
     for (uint32_t d = 0; d < p.n_out; ++d) {

@@ -33,19 +33,37 @@ namespace tnf {
 
 namespace pair {
 constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
-constexpr int kStages = 5;
-constexpr int kABytes = 128 * 128;        // 128 rows x 256 E2M1
-constexpr int kBBytes = 128 * 128;        // this CTA's half of the 256-row W tile
-constexpr int kSfaBytes = 2048;           // 4 atoms: 128 rows x 16 blocks
-constexpr int kSfbBytes = 4096;           // 2 x 4 atoms: 256 rows x 16 blocks
-constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;  // 38912
 constexpr int kStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
-constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 192;  // accumulator b starts at column b * 192
 constexpr uint32_t kSfaCol = 448, kSfbCol = 464;
-static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 }  // namespace pair
+
+// KB = 64-element K blocks (one MMA each) per pipeline stage: 4 -> five 38 KB stages of 256 K
+// elements (128-byte swizzled rows), 2 -> ten 19 KB stages of 128 K elements (64-byte swizzled
+// rows). Same bytes in flight; the finer stages keep more of them in flight while one stage is
+// being consumed and let the scale factors of consecutive stages alternate between two TMEM slots.
+// Measured on B200: the finer stages are SLOWER (3.0 vs 4.3 PFLOP/s on 4352x12288x3072), so 4 is the default.
+template <int KB>
+struct PairCfg {
+  static constexpr int kStages = KB == 4 ? 5 : 10;
+  static constexpr int kRowBytes = KB * 32;             // packed E2M1 bytes per operand row and stage
+  static constexpr int kABytes = 128 * kRowBytes;       // this CTA's 128 rows of A
+  static constexpr int kBBytes = 128 * kRowBytes;       // this CTA's half of the 256-row W tile
+  static constexpr int kSfaBytes = 512 * KB;            // KB atoms: 128 rows x 4 blocks each
+  static constexpr int kSfbBytes = 2 * 512 * KB;        // two 128-row groups
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + pair::kStagingBytes + 1024 + 256;
+  static constexpr int kSfSlots = KB == 4 ? 1 : 2;      // scale-factor slots in TMEM
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
+};
+template <int KB>
+__device__ __forceinline__ uint64_t make_desc_operand(uint32_t saddr) {
+  // K-major rows of KB*32 bytes, swizzle = row width; SBO = 8 rows
+  constexpr uint64_t kLayout = KB == 4 ? 2 : 4;  // SWIZZLE_128B : SWIZZLE_64B
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t((8 * KB * 32) >> 4) << 32) | (uint64_t(1) << 46) |
+         (kLayout << 61);
+}
 
 struct PairOutMaps {
   CUtensorMap m[kMaxPeers];
@@ -161,12 +179,17 @@ __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint
   }
 }
 
+template <int KB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                            const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                            const __grid_constant__ PairOutMaps out_maps, const GemmParams p) {
   using namespace pair;
-  constexpr int S = kStages;
+  using Cfg = PairCfg<KB>;
+  constexpr int S = Cfg::kStages;
+  constexpr int kABytes = Cfg::kABytes, kBBytes = Cfg::kBBytes, kSfaBytes = Cfg::kSfaBytes, kSfbBytes = Cfg::kSfbBytes;
+  constexpr int kStageBytes = Cfg::kStageBytes;
+  constexpr uint32_t kStageK = KB * 64;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -188,7 +211,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const uint32_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const uint32_t tiles_m2 = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
-  const uint32_t num_k_tiles = (p.k + 255u) / 256u;
+  const uint32_t num_k_tiles = (p.k + kStageK - 1u) / kStageK;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -196,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       mbar_init(bar_empty + 8 * i, 1);
     }
     mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_free, 8);
+    mbar_init(bar_acc_free, 16);  // every epilogue warp of both CTAs arrives once per tile
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_a);
@@ -238,13 +261,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
             if (tr) p.trace[titer * 4 + 0] = clock64();
             if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * kStageBytes);
             if (!skip_ab) {
-              tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * 128u), m0);
-              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * 128u), n0 + int32_t(rank * 128u));
+              tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * Cfg::kRowBytes), m0);
+              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * Cfg::kRowBytes), n0 + int32_t(rank * 128u));
             }
-            tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * 16u));
-            tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * 16u));
-            tma_load_2d_pair(sSfb + stage * kSfbBytes + 2048, &map_sfb, full, 0,
-                             sfb_row0 + int32_t(p.k_atoms * 4u + kt * 16u));
+            tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * (KB * 4u)));
+            tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * (KB * 4u)));
+            tma_load_2d_pair(sSfb + stage * kSfbBytes + 512 * KB, &map_sfb, full, 0,
+                             sfb_row0 + int32_t(p.k_atoms * 4u + kt * (KB * 4u)));
             if (tr) p.trace[titer * 4 + 1] = clock64();
           }
           __syncwarp();
@@ -282,18 +305,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
           if (tr) p.trace[titer * 4 + 2] = clock64();
           const uint32_t a_addr = sA + stage * kABytes, b_addr = sB + stage * kBBytes;
           const uint32_t sfa_addr = sSfa + stage * kSfaBytes, sfb_addr = sSfb + stage * kSfbBytes;
+          // scale factors of this stage: slot (kt & 1) when two slots exist, so that these copies
+          // do not wait for the previous stage's MMAs to finish reading theirs
+          const uint32_t sf_slot = Cfg::kSfSlots == 2 ? (kt & 1u) : 0u;
+          const uint32_t t_sfa = tmem_base + kSfaCol + sf_slot * (KB * 4), t_sfb = tmem_base + kSfbCol + sf_slot * (KB * 8);
           if (!(p.diag & 2u) || kt == 0)
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            tc_cp_32x128b_warpx4_pair(tmem_base + kSfaCol + kb * 4, make_desc_sf(sfa_addr + kb * 512));
-            tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + kb * 8, make_desc_sf(sfb_addr + kb * 512));
-            tc_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + kb * 8 + 4, make_desc_sf(sfb_addr + 2048 + kb * 512));
+          for (int kb = 0; kb < KB; ++kb) {
+            tc_cp_32x128b_warpx4_pair(t_sfa + kb * 4, make_desc_sf(sfa_addr + kb * 512));
+            tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8, make_desc_sf(sfb_addr + kb * 512));
+            tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8 + 4, make_desc_sf(sfb_addr + 512 * KB + kb * 512));
           }
           if (!(p.diag & 4u))
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            tc_mma_nvfp4_pair(d_tmem, make_desc_sw128(a_addr + kb * 32), make_desc_sw128(b_addr + kb * 32), idesc,
-                              tmem_base + kSfaCol + kb * 4, tmem_base + kSfbCol + kb * 8, (kt | kb) != 0u);
+          for (int kb = 0; kb < KB; ++kb)
+            tc_mma_nvfp4_pair(d_tmem, make_desc_operand<KB>(a_addr + kb * 32), make_desc_operand<KB>(b_addr + kb * 32), idesc,
+                              t_sfa + kb * 4, t_sfb + kb * 8, (kt | uint32_t(kb)) != 0u);
           tc_commit_pair_mc(bar_empty + 8 * stage, 3);  // frees the stage in both CTAs
           if (tr) p.trace[titer * 4 + 3] = clock64();
           }
@@ -341,6 +368,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       }
       tc_fence_after();
       if (ttr) p.trace[1024 + it * 8 + 4] = clock64();
+      // The next tile's MMA overwrites the accumulator of tile it-1 and this tile's overlapping
+      // columns. h == 0 warps arrive once those columns are in registers (below); h == 1 warps never
+      // touch them and arrive here: having passed this wait they are done reading tile it-1.
+      if (h == 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_free_leader);
+      }
       const uint32_t t_addr = tmem_base + b * kAccStride + ((q * 32u) << 16);
       uint32_t r[64];
       tmem_ld_32x32b_x32(t_addr + g0 * 64u, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
@@ -409,20 +444,27 @@ bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
   return m > 128;
 }
 
-cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
-                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p_in,
-                                   int sm_count, cudaStream_t s) {
+uint32_t gemm_pair_kblocks() {
+  static uint32_t v = env_u32_pair("TNF_GEMM_STAGE_K", 256) == 128 ? 2u : 4u;  // tuning knob: K elements per stage
+  return v;
+}
+
+template <int KB>
+static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
+                                  const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p_in,
+                                  int sm_count, cudaStream_t s) {
+  using Cfg = PairCfg<KB>;
   static bool attr_set = false;
   static int max_pairs = 0;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(sm_count & ~1), 1, 1);
     cfg.blockDim = dim3(pair::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = pair::kSmemBytes;
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     int clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemm_pair_kernel, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemm_pair_kernel<KB>, &cfg);
     if (e != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = sm_count / 2;
@@ -440,8 +482,15 @@ cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& 
   const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs));
   PairOutMaps om;
   for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
-  nvfp4_gemm_pair_kernel<<<pairs * 2, pair::kThreads, pair::kSmemBytes, s>>>(map_a, map_w, map_sfa, map_sfb, om, p);
+  nvfp4_gemm_pair_kernel<KB><<<pairs * 2, pair::kThreads, Cfg::kSmemBytes, s>>>(map_a, map_w, map_sfa, map_sfb, om, p);
   return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
+                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
+                                   int sm_count, cudaStream_t s) {
+  return gemm_pair_kblocks() == 4 ? launch_pair_kb<4>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s)
+                                  : launch_pair_kb<2>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s);
 }
 
 }  // namespace tnf

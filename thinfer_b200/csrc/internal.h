@@ -66,6 +66,7 @@ cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& 
                                    const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
                                    int sm_count, cudaStream_t s);
 bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k);
+uint32_t gemm_pair_kblocks();  // 64-element K blocks per pipeline stage of the pair kernel (2 or 4): sets the TMA boxes
 
 // 2-D tensor map description (dim0 is the contiguous one); all maps are built through this.
 struct MapSpec {
@@ -74,7 +75,7 @@ struct MapSpec {
   uint64_t dim0, dim1;   // extents in elements
   uint64_t stride1;      // bytes between rows
   uint32_t box0, box1;   // box in elements
-  uint32_t swizzle128;   // 1: 128-byte swizzle, 0: none
+  uint32_t swizzle128;   // swizzle span in bytes: 128, 64 or 0 (none); 1 also means 128
   bool operator<(const MapSpec& o) const {
     return std::tie(base, elem_bytes, dim0, dim1, stride1, box0, box1, swizzle128) <
            std::tie(o.base, o.elem_bytes, o.dim0, o.dim1, o.stride1, o.box0, o.box1, o.swizzle128);

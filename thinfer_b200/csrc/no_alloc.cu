@@ -138,13 +138,15 @@ int32_t tnf_linear_nvfp4_noalloc(tnf_ctx* ctx, const tnf_linear_args* a) {
 
   const bool pair = gemm_use_pair(a->m, a->n, a->k);
   CUtensorMap ma, mw;
-  if (make_tensor_map(&ma, MapSpec{a_codes, 1, a->k / 2, a->m, a->k / 2, 128, 128, 1}) != TNF_OK) return TNF_ERR_INVALID_ARGUMENT;
-  if (make_tensor_map(&mw, MapSpec{w_codes, 1, a->k / 2, a->n, a->k / 2, 128, pair ? 128u : gemm_tile_n(a->n), 1}) != TNF_OK)
+  const uint32_t kb = gemm_pair_kblocks();
+  const uint32_t box_bytes = pair ? kb * 32 : 128, swz = box_bytes;  // the pair kernel's stage width sets the box
+  if (make_tensor_map(&ma, MapSpec{a_codes, 1, a->k / 2, a->m, a->k / 2, box_bytes, 128, swz}) != TNF_OK) return TNF_ERR_INVALID_ARGUMENT;
+  if (make_tensor_map(&mw, MapSpec{w_codes, 1, a->k / 2, a->n, a->k / 2, box_bytes, pair ? 128u : gemm_tile_n(a->n), swz}) != TNF_OK)
     return TNF_ERR_INVALID_ARGUMENT;
   if (pair) {
     CUtensorMap msa, msb, outs[kMaxPeers];
-    if (make_tensor_map(&msa, MapSpec{a_scales, 1, 128, scales_bytes / 128, 128, 128, 16, 0}) != TNF_OK) return TNF_ERR_INVALID_ARGUMENT;
-    if (make_tensor_map(&msb, MapSpec{w_scales, 1, 128, sf_device_bytes(a->n, a->k) / 128, 128, 128, 16, 0}) != TNF_OK)
+    if (make_tensor_map(&msa, MapSpec{a_scales, 1, 128, scales_bytes / 128, 128, 128, kb * 4, 0}) != TNF_OK) return TNF_ERR_INVALID_ARGUMENT;
+    if (make_tensor_map(&msb, MapSpec{w_scales, 1, 128, sf_device_bytes(a->n, a->k) / 128, 128, 128, kb * 4, 0}) != TNF_OK)
       return TNF_ERR_INVALID_ARGUMENT;
     if (make_tensor_map(&outs[0], MapSpec{p.out[0] + a->n_offset, 2, a->n, a->m, uint64_t(ldo) * 2, 64, 32, 1}) != TNF_OK)
       return TNF_ERR_INVALID_ARGUMENT;

@@ -42,57 +42,75 @@ __global__ void global_scale_kernel(const uint32_t* amax_bits, float* g) {
 }
 
 // ---- block quantiser --------------------------------------------------------------------------
-// One thread per 16-element block over the PADDED block grid (rows up to a multiple of 128,
-// blocks up to k_atoms*4) when the scales go to the device layout, so that padding bytes are
-// written as zero. g_ptr (device) wins over g_val when not null.
+// One 16-element block per (thread, round); a warp covers 128 consecutive blocks of the block grid
+// in 4 rounds (lane l takes block base + 32*round + l), and issues the loads of all four rounds
+// before any arithmetic so that four 32-byte reads per thread are in flight. With the device scale
+// layout the grid is PADDED (rows up to a multiple of 128, blocks up to k_atoms*4), each aligned
+// group of 4 lanes owns one 4-byte scale word (row r, blocks 4i..4i+3), assembled with shuffles;
+// padding words are written as zero. g_ptr (device: {g, 1/(6g)}) wins over g_val when not null.
 template <typename T, bool kDeviceLayout>
 __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32_t k, const float* __restrict__ g_ptr,
                                 float g_val, float inv_t_val, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
                                 uint32_t k_atoms) {
+  constexpr int kRounds = 4;
   const uint32_t nb = k >> 4;
   const uint32_t nb_grid = kDeviceLayout ? k_atoms * 4u : nb;
   const uint32_t rows_grid = kDeviceLayout ? ((rows + 127u) & ~127u) : rows;
-  uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= uint64_t(rows_grid) * nb_grid) return;
-  uint32_t r = uint32_t(t / nb_grid), b = uint32_t(t % nb_grid);
-  // Device layout: the grid is padded so that each aligned group of 4 lanes owns one 4-byte word
-  // (row r, blocks 4i..4i+3); the word is assembled with shuffles and written by its first lane.
-  const bool valid = r < rows && b < nb;
-  if (!kDeviceLayout && !valid) return;
-  uint32_t sc = 0;
-  if (valid) {
+  const uint64_t total = uint64_t(rows_grid) * nb_grid;
+  const uint64_t warp_base = (uint64_t(blockIdx.x) * blockDim.x + (threadIdx.x & ~31u)) * kRounds;
+  const uint32_t lane = threadIdx.x & 31u;
+  if (warp_base >= total) return;  // warp-uniform
   const float g = g_ptr ? g_ptr[0] : g_val;
   const float inv_t = g_ptr ? g_ptr[1] : inv_t_val;
-  float x[16];
-  const T* p = src + uint64_t(r) * k + uint64_t(b) * 16u;
-  if constexpr (sizeof(T) == 2) {
-    const uint4* p4 = reinterpret_cast<const uint4*>(p);
-    uint4 v0 = __ldg(p4), v1 = __ldg(p4 + 1);
-    uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+
+  uint32_t r[kRounds], b[kRounds];
+  bool valid[kRounds];
+  uint4 raw[kRounds][sizeof(T) == 2 ? 2 : 4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      x[2 * i] = __uint_as_float(w[i] << 16);
-      x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-  } else {
-    const float4* p4 = reinterpret_cast<const float4*>(p);
+  for (int j = 0; j < kRounds; ++j) {
+    const uint64_t t = warp_base + uint64_t(j) * 32u + lane;
+    r[j] = uint32_t(t / nb_grid);
+    b[j] = uint32_t(t % nb_grid);
+    valid[j] = t < total && r[j] < rows && b[j] < nb;
+    if (valid[j]) {
+      const uint4* p4 = reinterpret_cast<const uint4*>(src + uint64_t(r[j]) * k + uint64_t(b[j]) * 16u);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 v = __ldg(p4 + i);
-      x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+      for (int i = 0; i < int(sizeof(T) == 2 ? 2 : 4); ++i) raw[j][i] = __ldg(p4 + i);
     }
   }
-  uint32_t lo, hi;
-  sc = quant_block16(x, g, inv_t, lo, hi);
-  *reinterpret_cast<uint2*>(codes + uint64_t(r) * (k >> 1) + uint64_t(b) * 8u) = make_uint2(lo, hi);
-  }
-  if (kDeviceLayout) {
-    uint32_t w = sc << (8u * (b & 3u));
-    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-    w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-    if ((b & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(r, b, k_atoms)) = w;
-  } else {
-    scales[uint64_t(r) * nb + b] = uint8_t(sc);
+#pragma unroll
+  for (int j = 0; j < kRounds; ++j) {
+    uint32_t sc = 0;
+    if (valid[j]) {
+      float x[16];
+      if constexpr (sizeof(T) == 2) {
+        const uint32_t w[8] = {raw[j][0].x, raw[j][0].y, raw[j][0].z, raw[j][0].w, raw[j][1].x, raw[j][1].y, raw[j][1].z, raw[j][1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[2 * i] = __uint_as_float(w[i] << 16);
+          x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          x[4 * i] = __uint_as_float(raw[j][i].x);
+          x[4 * i + 1] = __uint_as_float(raw[j][i].y);
+          x[4 * i + 2] = __uint_as_float(raw[j][i].z);
+          x[4 * i + 3] = __uint_as_float(raw[j][i].w);
+        }
+      }
+      uint32_t lo, hi;
+      sc = quant_block16(x, g, inv_t, lo, hi);
+      *reinterpret_cast<uint2*>(codes + uint64_t(r[j]) * (k >> 1) + uint64_t(b[j]) * 8u) = make_uint2(lo, hi);
+    }
+    if (kDeviceLayout) {  // the padded grid is a multiple of 128 blocks: every lane of the warp is in range here
+      uint32_t w = sc << (8u * (b[j] & 3u));
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+      if ((b[j] & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(r[j], b[j], k_atoms)) = w;
+    } else if (valid[j]) {
+      scales[uint64_t(r[j]) * nb + b[j]] = uint8_t(sc);
+    }
   }
 }
 
@@ -128,7 +146,7 @@ cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t 
   const float inv_t_val = 1.0f / (6.0f * g_val);  // same f32 operations as the device and the oracle
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
-  unsigned blocks = unsigned((threads + 255) / 256);
+  unsigned blocks = unsigned((threads + 1023) / 1024);  // 256 threads x 4 rounds per block
   if (dtype == 1) {
     auto* p = (const __nv_bfloat16*)src;
     if (device_layout) quantize_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
