@@ -303,7 +303,7 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
     return TNF_OK;
   }
   const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
-  const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, gemm_tile_n(a->n)));
+  const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, gemm_tile_n(a->m, a->n)));
   if (!ma || !mw) return TNF_ERR_INVALID_ARGUMENT;
   TNF_CUDA(launch_gemm_nvfp4(*ma, *mw, p, ctx->sm_count, ctx->compute), "nvfp4 gemm launch");
   return TNF_OK;

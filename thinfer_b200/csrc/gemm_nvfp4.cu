@@ -112,8 +112,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = *tmem_holder_gen;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
+    // ---------------- TMA producer: the whole warp runs the loop (uniform addresses), one lane issues ----------------
+    {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -122,11 +122,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint8_t* sfa_src = p.sfa + uint64_t(tm) * p.k_atoms * 512u;
         const uint8_t* sfb_src = p.sfb + uint64_t(n0 >> 7) * p.k_atoms * 512u;
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
             ok = false;
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
+          if (elect_one()) {
           if (p.diag & 8u) {
             mbar_arrive_expect_tx(full, Cfg::kSfaBytes + Cfg::kSfbBytes);
           } else {
@@ -139,35 +140,34 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int j = 0; j < Cfg::kSfbAtoms; ++j)
             bulk_load_1d(sSfb + stage * Cfg::kSfbBytes + j * 2048, sfb_src + (uint64_t(j) * p.k_atoms + kt * 4u) * 512u,
                          2048u, full);
+          }
+          __syncwarp();
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
-      // drain: every stage this lane armed must have landed before the CTA may exit
-      if (!ok) {
-        for (int i = 0; i < S; ++i) mbar_wait_bounded(bar_full + 8 * i, 0, abort_flag, 0, 20000000ll);
-      }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // ---------------- MMA issuer: whole warp runs the loop, one elected lane issues ----------------
+    {
       constexpr uint32_t idesc = make_idesc_nvfp4(kBlockM, BN);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const uint32_t n0 = (tile / p.tiles_m) * BN;
         const uint32_t sfb_shift = (n0 & 127u) >> 5;  // TMEM column shift when the tile starts inside a 128-row scale block
-        if (!mbar_wait_bounded(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusAccEmptyTimeout)) {
+        if (!mbar_wait_warp(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusAccEmptyTimeout)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + Cfg::kAccCol0 + acc * BN;
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_bounded(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          if (elect_one()) {
           const uint32_t a_addr = sA + stage * Cfg::kABytes, b_addr = sB + stage * Cfg::kBBytes;
           const uint32_t sfa_addr = sSfa + stage * Cfg::kSfaBytes, sfb_addr = sSfb + stage * Cfg::kSfbBytes;
           if (!(p.diag & 2u) || kt == 0)
@@ -187,9 +187,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                          tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + sfb_shift, (kt | kb) != 0u);
           }
           tc_commit(bar_empty + 8 * stage);
+          }
+          __syncwarp();
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(bar_acc_full + 8 * acc);
+        if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);
+        __syncwarp();
         if (++acc == AS) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -286,10 +289,11 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
   return v ? uint32_t(strtoul(v, nullptr, 0)) : dflt;
 }
 
-uint32_t gemm_tile_n(uint32_t n) {
-  (void)n;
+uint32_t gemm_tile_n(uint32_t m, uint32_t n) {
   static uint32_t forced = env_u32("TNF_GEMM_TILE_N", 0);  // tuning knob: 128 or 256
-  return forced == 128 ? 128 : 256;
+  if (forced == 128 || forced == 256) return forced;
+  // 256-wide tiles only when they still fill the SMs; 128-wide tiles also double-buffer the accumulator
+  return uint64_t((m + 127u) / 128u) * ((n + 255u) / 256u) >= 148u ? 256u : 128u;
 }
 
 template <int BN>
@@ -315,7 +319,7 @@ static cudaError_t launch_bn(const CUtensorMap& map_a, const CUtensorMap& map_w,
 
 cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmParams& p, int sm_count,
                               cudaStream_t s) {
-  switch (gemm_tile_n(p.n)) {
+  switch (gemm_tile_n(p.m, p.n)) {
     case 128: return launch_bn<128>(map_a, map_w, p, sm_count, s);
     default: return launch_bn<256>(map_a, map_w, p, sm_count, s);
   }

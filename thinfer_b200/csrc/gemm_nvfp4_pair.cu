@@ -34,6 +34,7 @@ namespace tnf {
 namespace pair {
 constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
+constexpr int kBiasBytes = 8 * 256;      // 8 epilogue warps x 128 bf16 bias values (the warp's two column groups)
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 192;  // accumulator b starts at column b * 192
 constexpr uint32_t kSfaCol = 448, kSfbCol = 464;
@@ -53,7 +54,7 @@ struct PairCfg {
   static constexpr int kSfaBytes = 512 * KB;            // KB atoms: 128 rows x 4 blocks each
   static constexpr int kSfbBytes = 2 * 512 * KB;        // two 128-row groups
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + pair::kStagingBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + pair::kStagingBytes + pair::kBiasBytes + 1024 + 256;
   static constexpr int kSfSlots = KB == 4 ? 1 : 2;      // scale-factor slots in TMEM
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 };
@@ -114,7 +115,7 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool 
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
 template <bool kGelu, bool kChain, bool kGate>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
-                                                   uint8_t* buf_gen, int lane) {
+                                                   uint8_t* buf_gen, const uint4* bias_smem, int lane) {
   const bool row_ok = row < p.m;
   uint32_t cw[8], sw = 0;  // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes
   uint4 prev = make_uint4(0, 0, 0, 0);
@@ -126,7 +127,7 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
       const uint32_t nc = ncol0 + (sub * 4 + jj) * 8;
       const bool col_ok = nc < p.n;
       b4[jj] = g4[jj] = s4[jj] = make_uint4(0, 0, 0, 0);
-      if (p.bias && col_ok) b4[jj] = __ldg(reinterpret_cast<const uint4*>(p.bias + nc));
+      if (p.bias) b4[jj] = bias_smem[sub * 4 + jj];  // staged per tile (zero past n); broadcast read
       if (kGate && col_ok) {
         g4[jj] = __ldg(reinterpret_cast<const uint4*>(p.gate + nc));
         if (row_ok) s4[jj] = __ldg(reinterpret_cast<const uint4*>(p.residual + uint64_t(row) * p.n + nc));
@@ -166,16 +167,17 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
 }
 
 __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
-                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, int lane) {
+                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const uint4* bias_smem,
+                                                       int lane) {
   switch (mode) {
-    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, lane); break;
-    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, lane); break;
-    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, lane); break;
-    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, lane); break;
-    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, lane); break;
-    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, lane); break;
-    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, lane); break;
-    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, lane); break;
+    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
   }
 }
 
@@ -198,7 +200,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   const uint32_t sSfa = sB + S * kBBytes;
   const uint32_t sSfb = sSfa + S * kSfaBytes;
   const uint32_t sStaging = sSfb + S * kSfbBytes;  // 1024-aligned: every size above is a multiple of 1024
-  const uint32_t sBar = sStaging + kStagingBytes;
+  const uint32_t sBias = sStaging + kStagingBytes;
+  const uint32_t sBar = sBias + kBiasBytes;
   const uint32_t bar_full = sBar;               // S barriers, used in the leader only
   const uint32_t bar_empty = bar_full + 8 * S;  // S
   const uint32_t bar_acc_full = bar_empty + 8 * S;
@@ -209,6 +212,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool ktr = (p.diag & 16u) && blockIdx.x == 0 && threadIdx.x == 0;
+  if (ktr) p.trace[1200] = clock64();
   const uint32_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const uint32_t tiles_m2 = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
   const uint32_t num_k_tiles = (p.k + kStageK - 1u) / kStageK;
@@ -238,6 +243,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder_gen;
+  if (ktr) p.trace[1201] = clock64();
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs): the whole warp runs the loop, one lane issues ----------------
@@ -341,6 +347,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     const uint32_t q = warp & 3, h = uint32_t(warp - 2) >> 2;
     const uint32_t buf = sStaging + uint32_t(warp - 2) * 4096u;
     uint8_t* buf_gen = smem_gen + (buf - smem_base);
+    uint4* bias_gen = reinterpret_cast<uint4*>(smem_gen + (sBias - smem_base) + uint32_t(warp - 2) * 256u);
     const uint32_t acc_free_leader = mapa_cluster(bar_acc_free, 0);
     uint32_t it = 0;
     bool ok = true;
@@ -352,13 +359,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       const uint32_t b = it & 1u;
       const uint32_t first = b ? 0u : 3u;  // 64-column group that overlaps the other accumulator
       const uint32_t g0 = (2u * h + first) & 3u, g1 = (2u * h + 1u + first) & 3u;
-      // warm L1 with this warp's bias / gate lines while the main loop is still running
-      if (lane < 2) {
-        const uint32_t nc = n0 + (lane ? g1 : g0) * 64u;
-        if (nc < p.n) {
-          if (p.bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.bias + nc));
-          if (p.gate) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + nc));
+      // stage this warp's 2 x 64 bias values in shared memory while the main loop is still running:
+      // lanes 0-7 fetch group g0, lanes 8-15 group g1, 16 bytes each (zero past n)
+      if (p.bias) {
+        __syncwarp();  // the previous tile's reads of the staging area are done
+        if (lane < 16) {
+          const uint32_t nc = n0 + ((lane >> 3) ? g1 : g0) * 64u + (lane & 7u) * 8u;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (nc < p.n) v = __ldg(reinterpret_cast<const uint4*>(p.bias + nc));
+          bias_gen[lane] = v;
         }
+        __syncwarp();
+      }
+      if (lane == 0 && p.gate) {
+        if (n0 + g0 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g0 * 64u));
+        if (n0 + g1 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g1 * 64u));
       }
       const bool ttr = (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == 2;
       if (ttr) p.trace[1024 + it * 8 + 3] = clock64();
@@ -401,7 +416,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (row0 >= p.m || ncol0 >= p.n) continue;  // warp-uniform
         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
         __syncwarp();
-        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, lane);
+        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen + half * 8, lane);
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {
@@ -418,6 +433,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   // ---------------- tear-down ----------------
   tc_fence_before();
   __syncthreads();
+  if (ktr) p.trace[1202] = clock64();
   if (*abort_flag != 0u) {
     if (threadIdx.x == 0) atomicCAS(p.status, 0u, *abort_flag);
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let copies and MMAs in flight retire
@@ -428,6 +444,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (ktr) p.trace[1203] = clock64();
 }
 
 static uint32_t env_u32_pair(const char* name, uint32_t dflt) {
@@ -436,12 +453,12 @@ static uint32_t env_u32_pair(const char* name, uint32_t dflt) {
 }
 
 bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
-  (void)n;
   (void)k;
   static uint32_t force = env_u32_pair("TNF_GEMM_KERNEL", 0);  // tuning knob: 1 = always 1-CTA, 2 = always pair
   if (force == 1) return false;
   if (force == 2) return true;
-  return m > 128;
+  // a pair works on a 256x256 tile; with few tiles (skinny M) the 1-CTA kernel's 128x128 tiles fill more SMs
+  return m > 128 && uint64_t((m + 255u) / 256u) * ((n + 255u) / 256u) >= 32u;
 }
 
 uint32_t gemm_pair_kblocks() {

@@ -82,6 +82,6 @@ struct MapSpec {
   }
 };
 int make_tensor_map(CUtensorMap* out, const MapSpec& spec);
-uint32_t gemm_tile_n(uint32_t n);  // tile width the 1-CTA launcher will pick for this n (for the map of W)
+uint32_t gemm_tile_n(uint32_t m, uint32_t n);  // tile width the 1-CTA launcher will pick for this n (for the map of W)
 
 }  // namespace tnf

@@ -141,7 +141,7 @@ int32_t tnf_linear_nvfp4_noalloc(tnf_ctx* ctx, const tnf_linear_args* a) {
   const uint32_t kb = gemm_pair_kblocks();
   const uint32_t box_bytes = pair ? kb * 32 : 128, swz = box_bytes;  // the pair kernel's stage width sets the box
   if (make_tensor_map(&ma, MapSpec{a_codes, 1, a->k / 2, a->m, a->k / 2, box_bytes, 128, swz}) != TNF_OK) return TNF_ERR_INVALID_ARGUMENT;
-  if (make_tensor_map(&mw, MapSpec{w_codes, 1, a->k / 2, a->n, a->k / 2, box_bytes, pair ? 128u : gemm_tile_n(a->n), swz}) != TNF_OK)
+  if (make_tensor_map(&mw, MapSpec{w_codes, 1, a->k / 2, a->n, a->k / 2, box_bytes, pair ? 128u : gemm_tile_n(a->m, a->n), swz}) != TNF_OK)
     return TNF_ERR_INVALID_ARGUMENT;
   if (pair) {
     CUtensorMap msa, msb, outs[kMaxPeers];
