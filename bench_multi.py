@@ -4,8 +4,11 @@ Workload: BASELINE configs[4], the batched Wan-5B-shaped FFN pair at M = 26520 â
 up 3072 -> 14336 (+bias, tanh-GELU), down 14336 -> 3072 (+bias). Weights are split by OUTPUT
 columns over the ranks (each rank holds its slices resident); every rank holds the full
 activations and ends each linear with the full [M, N] output:
-  --gather fused : the GEMM epilogue TMA-stores each output tile into its own output buffer and
-                   into every peer's (CUDA IPC windows), then a stream-ordered barrier;
+  --gather fused : the GEMM epilogue stores each output tile into its own output buffer (TMA) and
+                   into every peer's (16-byte vector stores through CUDA IPC windows), then a
+                   stream-ordered barrier;
+  --gather copy  : the linear runs in row bands; while band i+1 computes, the copy engines push
+                   band i of the rank's column slice to every peer (one strided peer copy each);
   --gather nccl  : the GEMM writes its slice locally, then an NCCL all-gather of the slices.
 Strong scaling: total work is fixed as N grows. The output bytes every rank must receive
 ((G-1)/G * 2*M*N) do not shrink with G, so NVLink ingest, not the tensor pipe, bounds this scheme.
@@ -28,6 +31,9 @@ def run_multi_gpu(args):
     from thinfer_b200 import _lib as L
     from thinfer_b200.nsplit import NSplitGroup, column_partition
 
+    import sys
+    saved_stdout = os.dup(1)  # libraries (NCCL) print banners on stdout: keep it clean for the one JSON line
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -39,6 +45,8 @@ def run_multi_gpu(args):
     sc = be.scope()
     grp = NSplitGroup(be, rank, world)
     M = WAN_M
+    if args.gather == "auto":  # measured: epilogue peer stores win with one peer (394 vs 344 GB/s), lose with three (148 vs 305)
+        args.gather = "fused" if world == 2 else "copy"
     gen = torch.Generator(device=dev)
     gen.manual_seed(0xC5)  # same seed on every rank: identical full tensors, each rank keeps its slice
 
@@ -57,9 +65,12 @@ def run_multi_gpu(args):
     as_torch(be, x, torch.bfloat16, (M, HIDDEN)).copy_(torch.randn(M, HIDDEN, device=dev, generator=gen).to(torch.bfloat16))
     torch.cuda.synchronize()
     fused = args.gather == "fused"
-    if fused:
+    if fused or args.gather == "copy":
         grp.register_output(0, h)
         grp.register_output(1, y)
+    from thinfer_b200._lib import Buf
+    bands = args.bands
+    band_rows = [((M * b // bands) + 255) // 256 * 256 if 0 < b < bands else (0 if b == 0 else M) for b in range(bands + 1)]
     ga_x, ga_h = 0.0018, 0.0009765625  # calibrated static activation scales (N(0,1) input; GELU output)
     compute = torch.cuda.ExternalStream(be.streams()[0], device=dev)
 
@@ -69,6 +80,19 @@ def run_multi_gpu(args):
             grp.barrier()
             sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN, flags=grp.scatter_flags(1))
             grp.barrier()
+        elif args.gather == "copy":
+            # row bands: the GEMM of band i+1 runs while the copy engines push band i to the peers
+            for (src, w, ga, dst, act, off, wd, ld, ws) in ((x, w_up, ga_x, h, 1, up_off, up_w, WAN_FFN, 0),
+                                                            (h, w_dn, ga_h, y, 0, dn_off, dn_w, HIDDEN, 1)):
+                k = w.k
+                for b in range(bands):
+                    r0, r1 = band_rows[b], band_rows[b + 1]
+                    a_view = Buf(src.id, r0 * k * 2, (r1 - r0) * k * 2)
+                    o_view = Buf(dst.id, r0 * ld * 2, (M - r0) * ld * 2)
+                    sc.linear(a_view, r1 - r0, w, ga, o_view, act=act, n_offset=off, ldo=ld)
+                    grp.scatter_rows(ws, dst, r0, r1 - r0, off, wd, ld)
+                grp.wait_scatter()
+                grp.barrier()
         else:
             sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN)
             grp.all_gather_cols(h, M, WAN_FFN)
@@ -135,7 +159,10 @@ def run_multi_gpu(args):
             "gpu_launches": args.steps * 4,
             "frac_of_nominal_fp4": flops / (ms * 1e-3) / 1e12 / (NOMINAL_FP4_TFLOPS * world),
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     be.submit()
     dist.barrier()
     be.close()

@@ -255,6 +255,15 @@ int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t
 int32_t tnf_ipc_export(tnf_ctx* ctx, uint64_t id, void* handle_64);
 int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t set, int32_t n_peers, const void* handles_64xn);
 #define TNF_LINEAR_PEER_SET(i) (((uint32_t)(i) & 3u) << 8)
+/* Copy-engine delivery, overlapped by row bands: once the work queued so far on the compute
+ * stream is done (the GEMM that produced rows [row0, row0+rows) of this rank's column slice),
+ * the copy stream pushes that band of out[:, n_offset : n_offset+n] to every window of `set` with
+ * one strided peer copy each. Call tnf_compute_after_copy, then tnf_comm_barrier, before any rank
+ * reads the gathered output. */
+int32_t tnf_scatter_rows(tnf_ctx* ctx, int32_t set, tnf_buf out_bf16, uint32_t row0, uint32_t rows, uint32_t n_offset,
+                         uint32_t n, uint32_t ldo);
+/* Compute stream waits for everything queued so far on the copy stream. */
+int32_t tnf_compute_after_copy(tnf_ctx* ctx);
 /* Stream-ordered barrier across the communicator (after a scatter epilogue). */
 int32_t tnf_comm_barrier(tnf_ctx* ctx);
 

@@ -42,7 +42,7 @@ def _worker(rank, world, port, ret):
     W = T.Nvfp4Weight.from_packed(be, wc[off:off + width], ws[off:off + width], gw, bias[off:off + width])
     abuf = be.upload(a)
     ok = True
-    for mode in ("fused", "nccl"):
+    for mode in ("fused", "copy", "nccl"):
         out = be.allocate(m * n * 2)
         be.write_buffer(out, np.full(m * n, 0x7FC0, np.uint16))
         be.submit()
@@ -51,6 +51,15 @@ def _worker(rank, world, port, ret):
         if mode == "fused":
             grp.register_output(0, out)
             sc.linear(abuf, m, W, ga, out, act=1, n_offset=off, ldo=n, flags=grp.scatter_flags(0))
+            grp.barrier()
+        elif mode == "copy":  # two row bands pushed by the copy engines
+            from thinfer_b200._lib import Buf
+            grp.register_output(1, out)
+            for r0, r1 in ((0, 256), (256, m)):
+                sc.linear(Buf(abuf.id, r0 * k * 2, (r1 - r0) * k * 2), r1 - r0, W, ga, Buf(out.id, r0 * n * 2, (m - r0) * n * 2),
+                          act=1, n_offset=off, ldo=n)
+                grp.scatter_rows(1, out, r0, r1 - r0, off, width, n)
+            grp.wait_scatter()
             grp.barrier()
         else:
             sc.linear(abuf, m, W, ga, out, act=1, n_offset=off, ldo=n)

@@ -221,6 +221,75 @@ int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t set, int32_t n_peers, const void*
   return TNF_OK;
 }
 
+int32_t tnf_scatter_rows(tnf_ctx* ctx, int32_t set, tnf_buf out_bf16, uint32_t row0, uint32_t rows, uint32_t n_offset,
+                         uint32_t n, uint32_t ldo) {
+  if (!ctx || set < 0 || set >= tnf_ctx::kPeerSets || rows == 0 || n == 0 || n_offset + n > ldo) {
+    set_error("tnf_scatter_rows: bad arguments (set %d, rows %u, n_offset %u, n %u, ldo %u)", set, rows, n_offset, n, ldo);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  int32_t st = TNF_OK;
+  uint8_t* base = resolve(ctx, out_bf16, (uint64_t(row0 + rows - 1) * ldo + n_offset + n) * 2, "out_bf16", &st);
+  if (!base) return st;
+  // the copies start when everything launched so far on the compute stream (the GEMM of these rows) is done
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->event_pool.empty()) {
+      ev = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    }
+  }
+  if (!ev) {
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+  }
+  e = cudaEventRecord(ev, ctx->compute);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy, ev, 0);
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->event_pool.push_back(ev);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_scatter_rows: stream order");
+  const uint64_t off = (uint64_t(row0) * ldo + n_offset) * 2;
+  for (int i = 0; i < ctx->n_peers[set]; ++i) {
+    e = cudaMemcpy2DAsync(static_cast<uint8_t*>(ctx->peer_out[set][i]) + off, uint64_t(ldo) * 2, base + off, uint64_t(ldo) * 2,
+                          uint64_t(n) * 2, rows, cudaMemcpyDeviceToDevice, ctx->copy);
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_scatter_rows: peer copy");
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_compute_after_copy(tnf_ctx* ctx) {
+  if (!ctx) {
+    set_error("null context");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->event_pool.empty()) {
+      ev = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    }
+  }
+  if (!ev) {
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+  }
+  e = cudaEventRecord(ev, ctx->copy);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->compute, ev, 0);
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->event_pool.push_back(ev);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_compute_after_copy");
+  return TNF_OK;
+}
+
 int32_t tnf_comm_barrier(tnf_ctx* ctx) {
   if (!ctx || !ctx->nccl_comm) {
     set_error("tnf_comm_barrier: no communicator (call tnf_comm_init)");

@@ -420,9 +420,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {
-          if (!(p.diag & 1u) && p.store_bf16)
-            for (uint32_t d = 0; d < p.n_out; ++d) tma_store_2d(&out_maps.m[d], buf, int32_t(ncol0), int32_t(row0));
+          if (!(p.diag & 1u) && p.store_bf16) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
           bulk_commit_group();
+        }
+        // Peer windows: coalesced 16-byte stores straight from the staging rows (8 lanes cover one
+        // 128-byte row segment, a warp instruction writes 4 rows). TMA stores to peer memory reached
+        // only ~160 GB/s per GPU with three peers; plain vector stores are what NVLink packs well.
+        if (p.n_out > 1u && !(p.diag & 1u)) {
+          const uint32_t chunk = lane & 7u, col = ncol0 + chunk * 8u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t rr = uint32_t(i) * 4u + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(buf_gen + rr * 128u + ((chunk ^ (rr & 7u)) << 4));
+            if (row0 + rr < p.m && col < p.n) {
+              const uint64_t off = uint64_t(row0 + rr) * p.ldo + p.n_offset + col;
+              for (uint32_t d = 1; d < p.n_out; ++d) *reinterpret_cast<uint4*>(p.out[d] + off) = v;
+            }
+          }
         }
       }
       if (ttr) p.trace[1024 + it * 8 + 6] = clock64();

@@ -55,6 +55,15 @@ class NSplitGroup:
     def scatter_flags(self, window_set: int) -> int:
         return L.LINEAR_SCATTER_PEERS | ((window_set & 3) << 8) if self.world > 1 else 0
 
+    def scatter_rows(self, window_set: int, out: Buf, row0: int, rows: int, n_offset: int, n: int, ldo: int) -> None:
+        """Copy-engine push of a finished row band of this rank's slice to every peer (asynchronous)."""
+        if self.world > 1:
+            _check(self.be.lib.tnf_scatter_rows(self.be._ctx, window_set, out, row0, rows, n_offset, n, ldo))
+
+    def wait_scatter(self) -> None:
+        """Compute stream waits for the pushes queued so far; follow with ``barrier``."""
+        _check(self.be.lib.tnf_compute_after_copy(self.be._ctx))
+
     def barrier(self) -> None:
         """Stream-ordered: later work on the compute stream starts after every rank got here."""
         _check(self.be.lib.tnf_comm_barrier(self.be._ctx))
