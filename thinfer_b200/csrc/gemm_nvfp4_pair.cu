@@ -35,6 +35,7 @@ namespace pair {
 constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
 constexpr int kBiasBytes = 8 * 256;      // 8 epilogue warps x 128 bf16 bias values (the warp's two column groups)
+constexpr int kLutBytes = 512;           // 1/(scale*g) per E4M3 code for the quantising epilogue
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 192;  // accumulator b starts at column b * 192
 constexpr uint32_t kSfaCol = 448, kSfbCol = 464;
@@ -54,7 +55,7 @@ struct PairCfg {
   static constexpr int kSfaBytes = 512 * KB;            // KB atoms: 128 rows x 4 blocks each
   static constexpr int kSfbBytes = 2 * 512 * KB;        // two 128-row groups
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + pair::kStagingBytes + pair::kBiasBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + pair::kStagingBytes + pair::kBiasBytes + pair::kLutBytes + 1024 + 256;
   static constexpr int kSfSlots = KB == 4 ? 1 : 2;      // scale-factor slots in TMEM
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 };
@@ -115,7 +116,7 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool 
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
 template <bool kGelu, bool kChain, bool kGate>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
-                                                   uint8_t* buf_gen, const uint4* bias_smem, int lane) {
+                                                   uint8_t* buf_gen, const uint4* bias_smem, const float* lut, int lane) {
   const bool row_ok = row < p.m;
   uint32_t cw[8], sw = 0;  // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes
   uint4 prev = make_uint4(0, 0, 0, 0);
@@ -148,7 +149,7 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
             x[2 * i + 1] = bf16_hi(w[i]);
           }
           uint32_t lo, hi;
-          const uint32_t sc = quant_block16(x, p.q_global, p.q_inv_t, lo, hi);
+          const uint32_t sc = quant_block16(x, lut, p.q_inv_t, lo, hi);
           cw[j - 1] = lo;
           cw[j] = hi;
           sw |= sc << (8 * (j >> 1));
@@ -168,16 +169,16 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
 
 __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
                                                        uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const uint4* bias_smem,
-                                                       int lane) {
+                                                       const float* lut, int lane) {
   switch (mode) {
-    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
-    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lane); break;
+    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
   }
 }
 
@@ -201,7 +202,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   const uint32_t sSfb = sSfa + S * kSfaBytes;
   const uint32_t sStaging = sSfb + S * kSfbBytes;  // 1024-aligned: every size above is a multiple of 1024
   const uint32_t sBias = sStaging + kStagingBytes;
-  const uint32_t sBar = sBias + kBiasBytes;
+  const uint32_t sLut = sBias + kBiasBytes;
+  const uint32_t sBar = sLut + kLutBytes;
+  float* lut_gen = reinterpret_cast<float*>(smem_gen + (sLut - smem_base));
   const uint32_t bar_full = sBar;               // S barriers, used in the leader only
   const uint32_t bar_empty = bar_full + 8 * S;  // S
   const uint32_t bar_acc_full = bar_empty + 8 * S;
@@ -233,6 +236,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     prefetch_tensormap(&map_sfb);
     prefetch_tensormap(&out_maps.m[0]);
   }
+  if (p.q_codes) fill_inv_scale_lut(lut_gen, p.q_global, threadIdx.x, blockDim.x);
   if (warp == 1) {
     tmem_alloc_pair(tmem_holder, kTmemCols);
     tmem_relinquish_pair();
@@ -416,7 +420,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (row0 >= p.m || ncol0 >= p.n) continue;  // warp-uniform
         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
         __syncwarp();
-        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen + half * 8, lane);
+        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen + half * 8, lut_gen, lane);
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {

@@ -59,9 +59,12 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
   const uint64_t total = uint64_t(rows_grid) * nb_grid;
   const uint64_t warp_base = (uint64_t(blockIdx.x) * blockDim.x + (threadIdx.x & ~31u)) * kRounds;
   const uint32_t lane = threadIdx.x & 31u;
-  if (warp_base >= total) return;  // warp-uniform
   const float g = g_ptr ? g_ptr[0] : g_val;
   const float inv_t = g_ptr ? g_ptr[1] : inv_t_val;
+  __shared__ float inv_d_lut[128];
+  fill_inv_scale_lut(inv_d_lut, g, threadIdx.x, blockDim.x);
+  __syncthreads();
+  if (warp_base >= total) return;  // warp-uniform
 
   uint32_t r[kRounds], b[kRounds];
   bool valid[kRounds];
@@ -100,7 +103,7 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
         }
       }
       uint32_t lo, hi;
-      sc = quant_block16(x, g, inv_t, lo, hi);
+      sc = quant_block16(x, inv_d_lut, inv_t, lo, hi);
       *reinterpret_cast<uint2*>(codes + uint64_t(r[j]) * (k >> 1) + uint64_t(b[j]) * 8u) = make_uint2(lo, hi);
     }
     if (kDeviceLayout) {  // the padded grid is a multiple of 128 blocks: every lane of the warp is in range here

@@ -13,8 +13,17 @@ __device__ __forceinline__ float e4m3_decode_dev(uint32_t c) {
   return e == 0 ? float(m) * 0.001953125f : __uint_as_float(((e + 120u) << 23) | (m << 20));
 }
 
+// Table of 1/(decode(sc) * g) for every E4M3 scale code, filled once per kernel (g is fixed for a
+// launch) with the same two IEEE operations the per-block form used, so the codes do not change;
+// it takes the division out of the per-block path. `lut` holds 128 floats; threads tid..tid+stride.
+__device__ __forceinline__ void fill_inv_scale_lut(float* lut, float g, uint32_t tid, uint32_t stride) {
+  for (uint32_t sc = tid; sc < 128u; sc += stride)
+    lut[sc] = (sc == 0u || sc == 127u) ? 0.0f : __fdiv_rn(1.0f, __fmul_rn(e4m3_decode_dev(sc), g));
+}
+
 // 16 f32 values -> 8 code bytes (returned as two u32) + the E4M3 scale byte.
-__device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], float g, float inv_t, uint32_t& lo, uint32_t& hi) {
+__device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], const float* inv_d_lut, float inv_t, uint32_t& lo,
+                                                  uint32_t& hi) {
   float bmax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(x[i]));
@@ -25,8 +34,7 @@ __device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], float g,
   lo = 0;
   hi = 0;
   if (sc != 0) {
-    float d = __fmul_rn(e4m3_decode_dev(sc), g);
-    float inv_d = __fdiv_rn(1.0f, d);
+    const float inv_d = inv_d_lut[sc];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float2 v = make_float2(__fmul_rn(x[2 * i], inv_d), __fmul_rn(x[2 * i + 1], inv_d));
