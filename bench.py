@@ -307,7 +307,7 @@ def run_single_gpu(args):
     peak_fp4 = 4.0 * peaks["bf16_sustained"]
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
     roofline = {
-        "bound": "tensor", "kernel": "nvfp4_gemm_kernel", "achieved": achieved, "peak": peak_fp4, "unit": "TFLOP/s",
+        "bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel", "achieved": achieved, "peak": peak_fp4, "unit": "TFLOP/s",
         "frac": achieved / peak_fp4,
         "peak_note": f"4 x sustained bf16 cuBLAS ({peaks['source']}); MEASURED_PEAKS has no FP4 figure; "
                      f"burst 4x = {4 * peaks['bf16']:.0f}; nominal dense FP4 = {NOMINAL_FP4_TFLOPS:.0f}",
@@ -316,7 +316,9 @@ def run_single_gpu(args):
         "per_shape": {QWEN_LINEARS[j][0]: {"ms": float(np.mean(v)),
                                             "tflops": 2.0 * M * QWEN_LINEARS[j][1] * QWEN_LINEARS[j][2] / (np.mean(v) * 1e-3) / 1e12}
                       for j, v in sorted(per_shape.items())},
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
+        # profiles/nvfp4_gemm_pair_qkv_and_down.md (qkv 52.9 MB, down 60.0 MB; algorithmic 103.7 / 78.1 MB)
+        "traffic": 56.4e6, "traffic_note": "mean of the two captured shapes; below the algorithmic bytes (outputs stay in L2)",
     }
 
     # ---- end to end through the public API with host buffers ----

@@ -86,6 +86,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+  const bool ktr = (p.diag & 16u) && blockIdx.x == 0;
+
   const uint32_t num_k_tiles = (p.k + kBlockK - 1) / kBlockK;
 
   if (threadIdx.x == 0) {
@@ -110,6 +112,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder_gen;
+  pdl_launch_dependents();
+  pdl_wait();  // before any access to global memory
+  if (ktr && threadIdx.x == 0) p.trace[1201] = clock64();
 
   if (warp == 0) {
     // ---------------- TMA producer: the whole warp runs the loop (uniform addresses), one lane issues ----------------
@@ -167,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tc_fence_after();
+          if (ktr && kt == 0 && lane == 0) p.trace[1204] = clock64();
           if (elect_one()) {
           const uint32_t a_addr = sA + stage * Cfg::kABytes, b_addr = sB + stage * Cfg::kBBytes;
           const uint32_t sfa_addr = sSfa + stage * Cfg::kSfaBytes, sfb_addr = sSfb + stage * Cfg::kSfbBytes;
@@ -191,6 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           __syncwarp();
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
+        if (ktr && lane == 0) p.trace[1205] = clock64();
         if (ok && elect_one()) tc_commit(bar_acc_full + 8 * acc);
         __syncwarp();
         if (++acc == AS) { acc = 0; acc_phase ^= 1u; }
@@ -210,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after();
+      if (ktr && warp == 2 && lane == 0) p.trace[1206] = clock64();
       const uint32_t t_addr = tmem_base + Cfg::kAccCol0 + acc * BN + ((quarter * 32u) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -269,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_fence_before();
       __syncwarp();
+      if (ktr && warp == 2 && lane == 0) p.trace[1207] = clock64();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
       if (++acc == AS) { acc = 0; acc_phase ^= 1u; }
     }
@@ -277,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---------------- tear-down ----------------
   tc_fence_before();
   __syncthreads();
+  if (ktr && threadIdx.x == 0) p.trace[1202] = clock64();
   if (threadIdx.x == 0 && *abort_flag != 0u) atomicCAS(p.status, 0u, *abort_flag);
   if (warp == 1) {
     tc_fence_after();
@@ -313,8 +323,7 @@ static cudaError_t launch_bn(const CUtensorMap& map_a, const CUtensorMap& map_w,
   uint32_t tiles = p.tiles_m * p.tiles_n;
   if (tiles == 0) return cudaSuccess;
   uint32_t grid = std::min<uint32_t>(tiles, uint32_t(sm_count));
-  nvfp4_gemm_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, s>>>(map_a, map_w, p);
-  return cudaGetLastError();
+  return launch_pdl(nvfp4_gemm_kernel<BN>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, s, map_a, map_w, p);
 }
 
 cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmParams& p, int sm_count,

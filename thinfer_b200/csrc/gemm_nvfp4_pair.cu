@@ -247,6 +247,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder_gen;
+  pdl_launch_dependents();  // the next kernel's CTAs may be scheduled as ours retire
+  pdl_wait();               // operands written by the previous kernel are complete and visible
   if (ktr) p.trace[1201] = clock64();
 
   if (warp == 0) {
@@ -517,8 +519,8 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
   const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs));
   PairOutMaps om;
   for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
-  nvfp4_gemm_pair_kernel<KB><<<pairs * 2, pair::kThreads, Cfg::kSmemBytes, s>>>(map_a, map_w, map_sfa, map_sfb, om, p);
-  return cudaGetLastError();
+  return launch_pdl(nvfp4_gemm_pair_kernel<KB>, dim3(pairs * 2), dim3(pair::kThreads), Cfg::kSmemBytes, s, map_a, map_w, map_sfa,
+                    map_sfb, om, p);
 }
 
 cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,

@@ -5,8 +5,27 @@
 #include <algorithm>
 #include <cstdint>
 #include <tuple>
+#include <utility>
 
 namespace tnf {
+
+// Launch with programmatic dependent launch allowed: the kernel's prologue and CTA scheduling may
+// overlap the tail of the previous kernel in the stream. Only for kernels that call pdl_wait()
+// before touching global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // 512-byte scale atoms along K per 128-row block: ceil(K/64) rounded up to a multiple of 4,
 // so that a 256-element K tile always reads four whole, contiguous atoms.

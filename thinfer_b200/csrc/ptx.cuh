@@ -145,6 +145,15 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream is still running; pdl_wait() blocks until the predecessor has
+// completed and its memory is visible, and must precede every access to global memory.
+// pdl_launch_dependents() lets the successor's CTAs be scheduled as this grid's CTAs retire.
+// Both are no-ops for launches without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- thread-block clusters (CTA pairs) -----------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

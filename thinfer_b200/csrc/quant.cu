@@ -59,6 +59,8 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
   const uint64_t total = uint64_t(rows_grid) * nb_grid;
   const uint64_t warp_base = (uint64_t(blockIdx.x) * blockDim.x + (threadIdx.x & ~31u)) * kRounds;
   const uint32_t lane = threadIdx.x & 31u;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // launched with programmatic dependent launch: see internal.h
   const float g = g_ptr ? g_ptr[0] : g_val;
   const float inv_t = g_ptr ? g_ptr[1] : inv_t_val;
   __shared__ float inv_d_lut[128];
@@ -150,14 +152,25 @@ cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t 
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
   unsigned blocks = unsigned((threads + 1023) / 1024);  // 256 threads x 4 rounds per block
+  // Keep the SMs in the same L1/shared-memory split as the GEMMs that run before and after (they take
+  // the whole 227 KB as shared memory): a kernel that prefers L1 makes every following GEMM launch wait
+  // for the split to be switched back.
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(quantize_kernel<float, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(quantize_kernel<float, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    carveout_set = true;
+  }
   if (dtype == 1) {
     auto* p = (const __nv_bfloat16*)src;
-    if (device_layout) quantize_kernel<__nv_bfloat16, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
-    else quantize_kernel<__nv_bfloat16, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    if (device_layout) return launch_pdl(quantize_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(256), 0, s, p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    return launch_pdl(quantize_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(256), 0, s, p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
   } else {
     auto* p = (const float*)src;
-    if (device_layout) quantize_kernel<float, true><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
-    else quantize_kernel<float, false><<<blocks, 256, 0, s>>>(p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    if (device_layout) return launch_pdl(quantize_kernel<float, true>, dim3(blocks), dim3(256), 0, s, p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
+    return launch_pdl(quantize_kernel<float, false>, dim3(blocks), dim3(256), 0, s, p, rows, k, g_ptr, g_val, inv_t_val, codes, scales, k_atoms);
   }
   return cudaGetLastError();
 }
