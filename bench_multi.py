@@ -45,8 +45,8 @@ def run_multi_gpu(args):
     sc = be.scope()
     grp = NSplitGroup(be, rank, world)
     M = WAN_M
-    if args.gather == "auto":  # measured: epilogue peer stores win with one peer (394 vs 344 GB/s), lose with three (148 vs 305)
-        args.gather = "fused" if world == 2 else "copy"
+    if args.gather == "auto":  # measured: epilogue peer stores win with one peer (394 vs 344 GB/s), lose with three (148 vs 305-320); at 8 ranks NCCL (382 GB/s) beats the strided copy-engine bands (186)
+        args.gather = "fused" if world == 2 else "nccl"
     gen = torch.Generator(device=dev)
     gen.manual_seed(0xC5)  # same seed on every rank: identical full tensors, each rank keeps its slice
 
@@ -126,6 +126,31 @@ def run_multi_gpu(args):
     clocks = sampler.stop() if sampler else None
     ms_compute = timed(compute_only, max(2, min(args.steps, 5)))
 
+    # ---- for comparison: the natural partition of this path, rows split over the ranks, no collective ----
+    # every rank holds the full weights (2 x 24.8 MB) and computes its own M/G rows of both linears; the
+    # MLP-up epilogue hands the down projection its NVFP4 operand directly
+    from thinfer_b200.backend import device_scales_bytes
+    gfull = torch.Generator(device=dev)
+    gfull.manual_seed(0xC5AA)
+    w_up_full = make_weight(be, T, L, gfull, WAN_FFN, HIDDEN)
+    w_dn_full = make_weight(be, T, L, gfull, HIDDEN, WAN_FFN)
+    r0 = (M * rank // world + 255) // 256 * 256 if rank else 0
+    r1 = (M * (rank + 1) // world + 255) // 256 * 256 if rank + 1 < world else M
+    mr = r1 - r0
+    hq_c = be.allocate(mr * WAN_FFN // 2)
+    hq_s = be.allocate(device_scales_bytes(mr, WAN_FFN))
+    x_rows = Buf(x.id, r0 * HIDDEN * 2, mr * HIDDEN * 2)
+    y_rows = Buf(y.id, r0 * HIDDEN * 2, mr * HIDDEN * 2)
+
+    def step_msplit():
+        sc.linear(x_rows, mr, w_up_full, ga_x, None, act=1, out_nvfp4=(hq_c, hq_s, ga_h))
+        sc.matmul(hq_c, hq_s, mr, w_dn_full, ga_h, y_rows)
+
+    for _ in range(3):
+        step_msplit()
+    be.submit()
+    ms_msplit = timed(step_msplit, args.steps)
+
     # end to end through the public API with host buffers: x in from pinned memory, y back
     from bench import _e2e_step, _pinned
     hin, hout = _pinned(be, M * HIDDEN * 2), _pinned(be, M * HIDDEN * 2)
@@ -157,6 +182,9 @@ def run_multi_gpu(args):
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": finite},
             "gpu_launches": args.steps * 4,
+            "m_split_no_collective": {"ms_per_step": ms_msplit, "value": flops / (ms_msplit * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                      "note": "same FFN pair with ROWS split over the ranks (full weights per rank, no exchange): "
+                                              "the partition this path shards on naturally; reported beside the mandated N-split"},
             "frac_of_nominal_fp4": flops / (ms * 1e-3) / 1e12 / (NOMINAL_FP4_TFLOPS * world),
         }
         sys.stdout.flush()
