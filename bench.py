@@ -503,7 +503,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=60, help="layers in the single-GPU stack (60 = the named workload)")
-    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl"],
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl", "nvfp4"],
                     help="N>1: how slices reach every rank (auto: fused epilogue stores for 2 ranks, copy-engine row bands beyond)")
     ap.add_argument("--bands", type=int, default=4, help="N>1 with --gather copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -185,6 +185,42 @@ def test_fused_output_quantisation_mlp(backend, m, hidden, ffn):
     W2.free(be)
 
 
+def test_fused_output_quantisation_column_windows(backend):
+    """An N-split linear fills its own column window of the NVFP4 copy ([m, ldo] operand, columns
+    n_offset .. n_offset+n): two window calls must leave the bytes one whole call leaves."""
+    import thinfer_b200 as T
+    from thinfer_b200.backend import device_scales_bytes
+
+    m, hidden, ffn = 300, 256, 512
+    a, w1, b1 = _inputs(m, ffn, hidden, 31)
+    be = backend
+    wc, ws, gw = O.quantize_weight(w1)
+    ga, g_mid = O.global_scale(O.amax_bf16(a)), 0.0009765625
+    abuf = be.upload(a)
+    sc = be.scope()
+    whole = T.Nvfp4Weight.from_packed(be, wc, ws, gw, b1)
+    qc0, qs0 = be.allocate(m * ffn // 2), be.allocate(device_scales_bytes(m, ffn))
+    be.write_buffer(qs0, np.zeros(qs0.len, np.uint8))  # rows past m of the last 128-row block are never written
+    sc.linear(abuf, m, whole, ga, None, act=1, out_nvfp4=(qc0, qs0, g_mid))
+    qc1, qs1 = be.allocate(m * ffn // 2), be.allocate(device_scales_bytes(m, ffn))
+    be.write_buffer(qc1, np.full(qc1.len, 0xEE, np.uint8))
+    be.write_buffer(qs1, np.zeros(qs1.len, np.uint8))
+    halves = []
+    for off in (0, ffn // 2):
+        Wh = T.Nvfp4Weight.from_packed(be, wc[off:off + ffn // 2], ws[off:off + ffn // 2], gw, b1[off:off + ffn // 2])
+        halves.append(Wh)
+        sc.linear(abuf, m, Wh, ga, None, act=1, n_offset=off, ldo=ffn, out_nvfp4=(qc1, qs1, g_mid))
+    be.submit(30000)
+    assert np.array_equal(be.read_buffer(qc1), be.read_buffer(qc0))
+    assert np.array_equal(be.read_buffer(qs1), be.read_buffer(qs0))
+    with pytest.raises(T.backend.InvalidArgument):  # windows of the NVFP4 copy move in whole 64-column groups
+        sc.linear(abuf, m, halves[1], ga, None, act=1, n_offset=32, ldo=ffn, out_nvfp4=(qc1, qs1, g_mid))
+    for b in (abuf, qc0, qs0, qc1, qs1):
+        be.free(b)
+    for Wp in [whole] + halves:
+        Wp.free(be)
+
+
 def test_linearity_and_zero_activation(backend):
     """Size-independent properties: a zero A gives exactly the bias; doubling A's per-tensor
     scale with the same codes doubles the pre-bias result."""

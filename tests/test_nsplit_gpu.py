@@ -71,6 +71,22 @@ def _worker(rank, world, port, ret):
         err = np.linalg.norm(g - e) / np.linalg.norm(e)
         ok = ok and bool(err <= 1e-3) and not np.isnan(g).any()
         dist.barrier()
+    # NVFP4 gather: every rank's epilogue quantises its window; codes + scales are gathered; the gathered
+    # operand must hold the bits the whole (unsplit) linear leaves on one GPU
+    from thinfer_b200.backend import device_scales_bytes
+    sc = be.scope()
+    g_mid = 0.0009765625
+    qc, qs = be.allocate(m * n // 2), be.allocate(device_scales_bytes(m, n))
+    be.write_buffer(qs, np.zeros(qs.len, np.uint8))
+    sc.linear(abuf, m, W, ga, None, act=1, n_offset=off, ldo=n, out_nvfp4=(qc, qs, g_mid))
+    grp.all_gather_nvfp4(qc, qs, m, n)
+    whole = T.Nvfp4Weight.from_packed(be, wc, ws, gw, bias)
+    qc0, qs0 = be.allocate(m * n // 2), be.allocate(device_scales_bytes(m, n))
+    be.write_buffer(qs0, np.zeros(qs0.len, np.uint8))
+    sc.linear(abuf, m, whole, ga, None, act=1, out_nvfp4=(qc0, qs0, g_mid))
+    be.submit(30000)
+    ok = ok and np.array_equal(be.read_buffer(qc), be.read_buffer(qc0)) and np.array_equal(be.read_buffer(qs), be.read_buffer(qs0))
+    dist.barrier()
     t = torch.tensor([1 if ok else 0], device=f"cuda:{rank}")
     dist.all_reduce(t)
     if rank == 0:

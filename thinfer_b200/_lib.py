@@ -82,6 +82,7 @@ SIGNATURES = {
     "tnf_comm_unique_id": (C.c_int32, [C.c_void_p]),
     "tnf_comm_init": (C.c_int32, [_ctx, C.c_int32, C.c_int32, C.c_void_p]),
     "tnf_all_gather_cols": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "tnf_all_gather_nvfp4": (C.c_int32, [_ctx, Buf, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
     "tnf_ipc_export": (C.c_int32, [_ctx, C.c_uint64, C.c_void_p]),
     "tnf_peer_outputs": (C.c_int32, [_ctx, C.c_int32, C.c_int32, C.c_void_p]),
     "tnf_scatter_rows": (C.c_int32, [_ctx, C.c_int32, Buf, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),

@@ -239,19 +239,22 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   GemmParams p{};
   p.store_bf16 = store_bf16 ? 1u : 0u;
   if (q_out) {
-    if (a->n % 64 != 0 || !(a->out_global > 0.0f) || (a->flags & TNF_LINEAR_SCATTER_PEERS)) {
-      set_error("TNF_LINEAR_OUT_NVFP4 needs n %% 64 == 0 (n=%u), out_global > 0 and no peer scatter", a->n);
+    if (a->n % 64 != 0 || a->n_offset % 64 != 0 || ldo % 64 != 0 || !(a->out_global > 0.0f) ||
+        (a->flags & TNF_LINEAR_SCATTER_PEERS)) {
+      set_error("TNF_LINEAR_OUT_NVFP4 needs n, n_offset and ldo multiples of 64 (n=%u, n_offset=%u, ldo=%u), "
+                "out_global > 0 and no peer scatter", a->n, a->n_offset, ldo);
       return TNF_ERR_INVALID_ARGUMENT;
     }
-    p.q_codes = resolve(ctx, a->out_codes, uint64_t(a->m) * (a->n / 2), "out_codes", &st);
+    // the NVFP4 copy is the [m, ldo] operand of the next linear; this call fills columns n_offset .. n_offset + n
+    p.q_codes = resolve(ctx, a->out_codes, uint64_t(a->m) * (ldo / 2), "out_codes", &st);
     if (!p.q_codes) return st;
-    p.q_scales = resolve(ctx, a->out_scales, sf_device_bytes(a->m, a->n), "out_scales", &st);
+    p.q_scales = resolve(ctx, a->out_scales, sf_device_bytes(a->m, ldo), "out_scales", &st);
     if (!p.q_scales) return st;
     p.q_global = a->out_global;
     p.q_inv_t = 1.0f / (6.0f * a->out_global);
-    p.q_k_atoms = sf_k_atoms(a->n);
-    if ((a->n / 64) % 4 != 0)  // K-padding atoms of the next operand must hold benign (zero) scales
-      TNF_CUDA(cudaMemsetAsync(p.q_scales, 0, sf_device_bytes(a->m, a->n), ctx->compute), "out_scales clear");
+    p.q_k_atoms = sf_k_atoms(ldo);
+    if ((ldo / 64) % 4 != 0)  // K-padding atoms of the next operand must hold benign (zero) scales
+      TNF_CUDA(cudaMemsetAsync(p.q_scales, 0, sf_device_bytes(a->m, ldo), ctx->compute), "out_scales clear");
   }
   p.m = a->m; p.n = a->n; p.k = a->k;
   p.k_atoms = sf_k_atoms(a->k);

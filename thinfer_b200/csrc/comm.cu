@@ -56,24 +56,35 @@ static int32_t nccl_fail(NcclApi* api, ncclResult_t r, const char* what) {
   return TNF_ERR_NCCL;
 }
 
-// own column slice of out[m, n_total] -> contiguous [m, n_local]
-__global__ void pack_cols_kernel(const uint4* __restrict__ out, uint4* __restrict__ packed, uint32_t m,
-                                 uint32_t n_total8, uint32_t n_local8, uint32_t col0_8) {
+// own column slice of a row-major matrix -> contiguous [rows, n_local]; all extents in 16-byte units
+__global__ void pack_cols_kernel(const uint4* __restrict__ out, uint4* __restrict__ packed, uint32_t rows,
+                                 uint32_t row_stride, uint32_t n_local, uint32_t col0) {
   uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= uint64_t(m) * n_local8) return;
-  uint32_t r = uint32_t(t / n_local8), c = uint32_t(t % n_local8);
-  packed[t] = out[uint64_t(r) * n_total8 + col0_8 + c];
+  if (t >= uint64_t(rows) * n_local) return;
+  uint32_t r = uint32_t(t / n_local), c = uint32_t(t % n_local);
+  packed[t] = out[uint64_t(r) * row_stride + col0 + c];
 }
-// gathered [world, m, n_local] -> out[m, n_total], skipping this rank's own slice
-__global__ void unpack_cols_kernel(const uint4* __restrict__ gathered, uint4* __restrict__ out, uint32_t m,
-                                   uint32_t n_total8, uint32_t n_local8, uint32_t world, uint32_t self) {
+// gathered: rank w's [rows, n_local] block starts at w * rank_stride -> out columns w * n_local, skipping this rank's own
+__global__ void unpack_cols_kernel(const uint4* __restrict__ gathered, uint4* __restrict__ out, uint32_t rows,
+                                   uint32_t row_stride, uint32_t n_local, uint64_t rank_stride, uint32_t world,
+                                   uint32_t self) {
   uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= uint64_t(world) * m * n_local8) return;
-  uint32_t c = uint32_t(t % n_local8);
-  uint64_t q = t / n_local8;
-  uint32_t r = uint32_t(q % m), w = uint32_t(q / m);
+  if (t >= uint64_t(world) * rows * n_local) return;
+  uint32_t c = uint32_t(t % n_local);
+  uint64_t q = t / n_local;
+  uint32_t r = uint32_t(q % rows), w = uint32_t(q / rows);
   if (w == self) return;
-  out[uint64_t(r) * n_total8 + uint64_t(w) * n_local8 + c] = gathered[t];
+  out[uint64_t(r) * row_stride + uint64_t(w) * n_local + c] = gathered[uint64_t(w) * rank_stride + uint64_t(r) * n_local + c];
+}
+
+static cudaError_t ensure_gather_tmp(tnf_ctx* ctx, uint64_t need) {
+  if (need <= ctx->gather_tmp_bytes) return cudaSuccess;
+  if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
+  ctx->gather_tmp = nullptr;
+  ctx->gather_tmp_bytes = 0;
+  cudaError_t e = cudaMalloc(&ctx->gather_tmp, need);
+  if (e == cudaSuccess) ctx->gather_tmp_bytes = need;
+  return e;
 }
 
 }  // namespace tnf
@@ -145,15 +156,8 @@ int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t
   if (!out) return st;
   NcclApi* api = nccl_api();
   const uint64_t slice = uint64_t(m) * n_local * 2;
-  const uint64_t need = slice * (uint64_t(ctx->world) + 1);
-  if (need > ctx->gather_tmp_bytes) {
-    if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
-    ctx->gather_tmp = nullptr;
-    ctx->gather_tmp_bytes = 0;
-    e = cudaMalloc(&ctx->gather_tmp, need);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
-    ctx->gather_tmp_bytes = need;
-  }
+  e = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
   uint8_t* send = static_cast<uint8_t*>(ctx->gather_tmp);
   uint8_t* recv = send + slice;
   const uint32_t nl8 = n_local / 8, nt8 = n_total / 8;
@@ -166,8 +170,55 @@ int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t
   if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllGather");
   threads *= uint64_t(ctx->world);
   unpack_cols_kernel<<<unsigned((threads + 255) / 256), 256, 0, ctx->compute>>>(
-      reinterpret_cast<const uint4*>(recv), reinterpret_cast<uint4*>(out), m, nt8, nl8, uint32_t(ctx->world),
-      uint32_t(ctx->rank));
+      reinterpret_cast<const uint4*>(recv), reinterpret_cast<uint4*>(out), m, nt8, nl8, uint64_t(m) * nl8,
+      uint32_t(ctx->world), uint32_t(ctx->rank));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
+  return TNF_OK;
+}
+
+int32_t tnf_all_gather_nvfp4(tnf_ctx* ctx, tnf_buf codes, tnf_buf scales, uint32_t m, uint32_t n_total, uint32_t n_local) {
+  if (!ctx || !ctx->nccl_comm) {
+    set_error("tnf_all_gather_nvfp4: no communicator (call tnf_comm_init)");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  if (n_local % 64 || n_total != n_local * uint32_t(ctx->world) || m == 0) {
+    set_error("tnf_all_gather_nvfp4: n_total %u must be world %d x n_local %u, n_local a multiple of 64", n_total,
+              ctx->world, n_local);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  uint8_t* pc = resolve(ctx, codes, uint64_t(m) * (n_total / 2), "codes", &st);
+  if (!pc) return st;
+  uint8_t* ps = resolve(ctx, scales, sf_device_bytes(m, n_total), "scales", &st);
+  if (!ps) return st;
+  NcclApi* api = nccl_api();
+  // 16-byte units: a code row is n/32 of them; a 128-row block of scales is 32 per 64-column atom
+  const uint32_t row_blocks = (m + 127) / 128;
+  const uint32_t c_loc = n_local / 32, c_tot = n_total / 32;
+  const uint32_t s_loc = (n_local / 64) * 32, s_tot = sf_k_atoms(n_total) * 32;
+  const uint64_t c_units = uint64_t(m) * c_loc, s_units = uint64_t(row_blocks) * s_loc;
+  const uint64_t slice = (c_units + s_units) * 16;
+  e = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
+  uint4* send = static_cast<uint4*>(ctx->gather_tmp);
+  uint4* recv = send + slice / 16;
+  const uint32_t rank = uint32_t(ctx->rank), world = uint32_t(ctx->world);
+  pack_cols_kernel<<<unsigned((c_units + 255) / 256), 256, 0, ctx->compute>>>(reinterpret_cast<const uint4*>(pc), send, m,
+                                                                             c_tot, c_loc, rank * c_loc);
+  pack_cols_kernel<<<unsigned((s_units + 255) / 256), 256, 0, ctx->compute>>>(reinterpret_cast<const uint4*>(ps),
+                                                                             send + c_units, row_blocks, s_tot, s_loc,
+                                                                             rank * s_loc);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "pack launch");
+  ncclResult_t r = api->AllGather(send, recv, slice, ncclUint8, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->compute);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllGather");
+  unpack_cols_kernel<<<unsigned((c_units * world + 255) / 256), 256, 0, ctx->compute>>>(
+      recv, reinterpret_cast<uint4*>(pc), m, c_tot, c_loc, slice / 16, world, rank);
+  unpack_cols_kernel<<<unsigned((s_units * world + 255) / 256), 256, 0, ctx->compute>>>(
+      recv + c_units, reinterpret_cast<uint4*>(ps), row_blocks, s_tot, s_loc, slice / 16, world, rank);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
   return TNF_OK;

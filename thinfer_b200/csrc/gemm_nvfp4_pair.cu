@@ -160,10 +160,12 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
     }
   }
   if (p.q_codes && row_ok && ncol0 < p.n) {  // n % 64 == 0: the whole group is in range
-    uint4* qc = reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.n >> 1) + (ncol0 >> 1));
+    // the NVFP4 copy is an [m, ldo] operand; this launch fills its columns n_offset .. n_offset + n
+    const uint32_t qcol = p.n_offset + ncol0;
+    uint4* qc = reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.ldo >> 1) + (qcol >> 1));
     qc[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
     qc[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
-    *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, ncol0 >> 4, p.q_k_atoms)) = sw;
+    *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, qcol >> 4, p.q_k_atoms)) = sw;
   }
 }
 

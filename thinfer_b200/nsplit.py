@@ -70,3 +70,7 @@ class NSplitGroup:
 
     def all_gather_cols(self, out: Buf, m: int, n_total: int) -> None:
         _check(self.be.lib.tnf_all_gather_cols(self.be._ctx, out, m, n_total, n_total // self.world))
+
+    def all_gather_nvfp4(self, codes: Buf, scales_device: Buf, m: int, n_total: int) -> None:
+        """Gather an output the epilogue left in NVFP4 (codes + device-layout scales), 0.5625 B per element."""
+        _check(self.be.lib.tnf_all_gather_nvfp4(self.be._ctx, codes, scales_device, m, n_total, n_total // self.world))
