@@ -503,9 +503,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=60, help="layers in the single-GPU stack (60 = the named workload)")
-    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl", "nvfp4"],
-                    help="N>1: how slices reach every rank (auto: fused epilogue stores for 2 ranks, copy-engine row bands beyond)")
-    ap.add_argument("--bands", type=int, default=4, help="N>1 with --gather copy: row bands per linear")
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl", "nvfp4", "push"],
+                    help="N>1: how slices reach every rank (auto = push: packed NVFP4/bf16 slices, contiguous copy-engine pushes)")
+    ap.add_argument("--bands", type=int, default=2, help="N>1 with --gather push/copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="stack", choices=["stack", "stream"],
                     help="N=1: 'stack' = resident 60-layer block-linear stack (default); 'stream' = streamed variant under 6 GiB")

@@ -12,7 +12,10 @@ activations and ends each linear with the full [M, N] output:
   --gather nccl  : the GEMM writes its slice locally, then an NCCL all-gather of the slices;
   --gather nvfp4 : the MLP-up epilogue quantises its slice to NVFP4 (what the down projection consumes
                    anyway) and the all-gather moves codes + scales, 0.5625 B per element instead of 2;
-                   the final output is gathered as bf16. Same result bits as --gather nccl.
+                   the final output is gathered as bf16. Same result bits as --gather nccl;
+  --gather push  : the same bytes as nvfp4, but each rank writes its slice packed and the copy engines push
+                   finished row bands to every peer's receive area with contiguous copies while the next
+                   band computes; one barrier and an interleave kernel per linear.
 Strong scaling: total work is fixed as N grows. The output bytes every rank must receive
 ((G-1)/G * 2*M*N) do not shrink with G, so NVLink ingest, not the tensor pipe, bounds this scheme.
 """
@@ -48,8 +51,10 @@ def run_multi_gpu(args):
     sc = be.scope()
     grp = NSplitGroup(be, rank, world)
     M = WAN_M
-    if args.gather == "auto":  # measured: epilogue peer stores win with one peer (394 vs 344 GB/s), lose with three (148 vs 305-320); at 8 ranks NCCL (382 GB/s) beats the strided copy-engine bands (186)
-        args.gather = "fused" if world == 2 else "nvfp4"
+    if args.gather == "auto":
+        # measured ms/step at 2 / 4 / 8 ranks: push 1.12 / 1.09 / 1.23-1.32, nvfp4 (NCCL) 1.32 / 1.09 / 1.29,
+        # fused 1.20 / 4.3 / -, nccl (bf16) 2.2 / 2.15 / 2.12, copy (strided) 1.34 / 2.27 / 4.35
+        args.gather = "push"
     gen = torch.Generator(device=dev)
     gen.manual_seed(0xC5)  # same seed on every rank: identical full tensors, each rank keeps its slice
 
@@ -79,8 +84,24 @@ def run_multi_gpu(args):
     from thinfer_b200.backend import device_scales_bytes
     hq_full_c = be.allocate(M * WAN_FFN // 2)
     hq_full_s = be.allocate(device_scales_bytes(M, WAN_FFN))
+    hs_block = device_scales_bytes(128, WAN_FFN)  # bytes of one 128-row block of H's scales
+    if args.gather == "push":
+        from thinfer_b200.nsplit import PackedGather
+        pg_h = PackedGather(grp, 2, M, WAN_FFN, "nvfp4")
+        pg_y = PackedGather(grp, 3, M, HIDDEN, "bf16")
+
+    marks = []  # (label, event) on the compute stream, filled when a breakdown pass asks for it
+
+    def mark(label):
+        if marks is not None and trace_on[0]:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(compute)
+            marks.append((label, ev))
+
+    trace_on = [False]
 
     def step():
+        mark("start")
         if fused:
             sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN, flags=grp.scatter_flags(0))
             grp.barrier()
@@ -99,6 +120,33 @@ def run_multi_gpu(args):
                     grp.scatter_rows(ws, dst, r0, r1 - r0, off, wd, ld)
                 grp.wait_scatter()
                 grp.barrier()
+        elif args.gather == "push":
+            # packed slices, contiguous copy-engine pushes band by band, one barrier + interleave per linear
+            for b in range(bands):
+                r0, rows = band_rows[b], band_rows[b + 1] - band_rows[b]
+                sc.linear(Buf(x.id, r0 * HIDDEN * 2, rows * HIDDEN * 2), rows, w_up, ga_x, None, act=1,
+                          out_nvfp4=(pg_h.send_main(r0, rows), pg_h.send_scales(r0, rows), ga_h))
+                pg_h.push(r0, rows)
+            mark("up bands")
+            grp.wait_scatter()
+            mark("H pushes done")
+            grp.barrier()
+            mark("barrier")
+            pg_h.finish(hq_full_c, hq_full_s, sync=False)
+            mark("H interleave")
+            for b in range(bands):
+                r0, rows = band_rows[b], band_rows[b + 1] - band_rows[b]
+                sc.matmul(Buf(hq_full_c.id, r0 * WAN_FFN // 2, rows * WAN_FFN // 2),
+                          Buf(hq_full_s.id, (r0 // 128) * hs_block, ((rows + 127) // 128) * hs_block), rows, w_dn, ga_h,
+                          pg_y.send_main(r0, rows))
+                pg_y.push(r0, rows)
+            mark("down bands")
+            grp.wait_scatter()
+            mark("y pushes done")
+            grp.barrier()
+            mark("barrier")
+            pg_y.finish(y, sync=False)
+            mark("y interleave")
         elif args.gather == "nvfp4":
             sc.linear(x, M, w_up, ga_x, None, act=1, n_offset=up_off, ldo=WAN_FFN, out_nvfp4=(hq_full_c, hq_full_s, ga_h))
             grp.all_gather_nvfp4(hq_full_c, hq_full_s, M, WAN_FFN)
@@ -135,6 +183,15 @@ def run_multi_gpu(args):
     sampler = ClockSampler(local) if rank == 0 else None
     ms = timed(step, args.steps)
     clocks = sampler.stop() if sampler else None
+    breakdown = None
+    if os.environ.get("TNF_BENCH_BREAKDOWN"):  # one more step with an event after every stage (rank 0's view)
+        dist.barrier()
+        trace_on[0] = True
+        step()
+        trace_on[0] = False
+        be.submit()
+        torch.cuda.synchronize()
+        breakdown = [(b[0], round(a[1].elapsed_time(b[1]), 4)) for a, b in zip(marks, marks[1:])]
     compute_only()  # grows the activation scratch on first use
     be.submit()
     ms_compute = timed(compute_only, max(2, min(args.steps, 5)))
@@ -171,7 +228,7 @@ def run_multi_gpu(args):
     finite = bool(np.isfinite((hout["np"].astype(np.uint32) << 16).view(np.float32)).all())
 
     flops = 2.0 * M * HIDDEN * WAN_FFN * 2
-    out_bytes = (0.5625 if args.gather == "nvfp4" else 2.0) * M * WAN_FFN + 2.0 * M * HIDDEN
+    out_bytes = (0.5625 if args.gather in ("nvfp4", "push") else 2.0) * M * WAN_FFN + 2.0 * M * HIDDEN
     ingest = out_bytes * (world - 1) / world  # bytes every rank must receive per step
     if rank == 0:
         peaks = measured_peaks()
@@ -193,7 +250,7 @@ def run_multi_gpu(args):
             "clocks": clocks,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": finite},
-            "gpu_launches": args.steps * 4,
+            "gpu_launches": args.steps * 4, "breakdown_ms": breakdown,
             "m_split_no_collective": {"ms_per_step": ms_msplit, "value": flops / (ms_msplit * 1e-3) / 1e12, "unit": "TFLOP/s",
                                       "note": "same FFN pair with ROWS split over the ranks (full weights per rank, no exchange): "
                                               "the partition this path shards on naturally; reported beside the mandated N-split"},

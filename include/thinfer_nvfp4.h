@@ -269,6 +269,20 @@ int32_t tnf_peer_outputs(tnf_ctx* ctx, int32_t set, int32_t n_peers, const void*
  * reads the gathered output. */
 int32_t tnf_scatter_rows(tnf_ctx* ctx, int32_t set, tnf_buf out_bf16, uint32_t row0, uint32_t rows, uint32_t n_offset,
                          uint32_t n, uint32_t ldo);
+/* Contiguous copy-engine delivery. The linear writes its column slice PACKED (ldo = n, n_offset = 0;
+ * an NVFP4 copy packs the same way); once the work queued so far on the compute stream is done the
+ * copy stream copies src to byte dst_offset of every window of `set` (each peer's receive area,
+ * which the caller sized; ring order, so every rank receives from one sender at a time) and to
+ * self_dst, this rank's slot of its own receive area (len 0 to skip). Contiguous peer copies run
+ * at link rate where the strided ones of tnf_scatter_rows do not. Then tnf_compute_after_copy,
+ * tnf_comm_barrier, and tnf_interleave_cols to lay the slices side by side. */
+int32_t tnf_push_peers(tnf_ctx* ctx, int32_t set, tnf_buf src, uint64_t dst_offset, tnf_buf self_dst);
+/* out[r*out_row_bytes + w*local_row_bytes + c] = gathered[w*rank_stride + r*src_row_bytes + c] for
+ * w < world, r < rows, c < local_row_bytes: the receive area's per-rank blocks become the column
+ * slices of one row-major matrix (bf16 rows, NVFP4 code rows, or 128-row blocks of device-layout
+ * scales, whose rows may carry padding atoms). All byte counts are multiples of 16. */
+int32_t tnf_interleave_cols(tnf_ctx* ctx, tnf_buf gathered, uint64_t rank_stride, uint32_t src_row_bytes, uint32_t world,
+                            tnf_buf out, uint32_t out_row_bytes, uint32_t rows, uint32_t local_row_bytes);
 /* Compute stream waits for everything queued so far on the copy stream. */
 int32_t tnf_compute_after_copy(tnf_ctx* ctx);
 /* Stream-ordered barrier across the communicator (after a scatter epilogue). */

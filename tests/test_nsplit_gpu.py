@@ -1,5 +1,6 @@
-"""N-split on real GPUs (2 ranks, one process per GPU): the fused peer-store epilogue and the NCCL
-all-gather must both reproduce the unsplit result. Skipped when fewer than 2 GPUs are visible."""
+"""N-split on real GPUs (2 ranks, one process per GPU): the fused peer-store epilogue, the copy-engine
+deliveries (strided bands, packed pushes) and the NCCL all-gathers (bf16, NVFP4) must all reproduce the
+unsplit result. Skipped when fewer than 2 GPUs are visible."""
 import os
 import socket
 
@@ -86,6 +87,30 @@ def _worker(rank, world, port, ret):
     sc.linear(abuf, m, whole, ga, None, act=1, out_nvfp4=(qc0, qs0, g_mid))
     be.submit(30000)
     ok = ok and np.array_equal(be.read_buffer(qc), be.read_buffer(qc0)) and np.array_equal(be.read_buffer(qs), be.read_buffer(qs0))
+    dist.barrier()
+    # packed slices pushed by the copy engines in two row bands, then interleaved: bf16 and NVFP4 outputs
+    from thinfer_b200._lib import Buf
+    from thinfer_b200.nsplit import PackedGather
+    pg_b, pg_q = PackedGather(grp, 2, m, n, "bf16"), PackedGather(grp, 3, m, n, "nvfp4")
+    out_p = be.allocate(m * n * 2)
+    qc2, qs2 = be.allocate(m * n // 2), be.allocate(device_scales_bytes(m, n))
+    be.write_buffer(qs2, np.zeros(qs2.len, np.uint8))
+    be.write_buffer(pg_q.send, np.zeros(pg_q.send.len, np.uint8))
+    be.submit()
+    dist.barrier()
+    for r0, r1 in ((0, 256), (256, m)):
+        a_view = Buf(abuf.id, r0 * k * 2, (r1 - r0) * k * 2)
+        sc.linear(a_view, r1 - r0, W, ga, pg_b.send_main(r0, r1 - r0), act=1)
+        pg_b.push(r0, r1 - r0)
+        sc.linear(a_view, r1 - r0, W, ga, None, act=1, out_nvfp4=(pg_q.send_main(r0, r1 - r0), pg_q.send_scales(r0, r1 - r0), g_mid))
+        pg_q.push(r0, r1 - r0)
+    pg_b.finish(out_p)
+    pg_q.finish(qc2, qs2)
+    be.submit(30000)
+    got = O.bf16_to_f32(be.read_buffer(out_p, np.uint16).reshape(m, n)).astype(np.float64)
+    e = O.bf16_to_f32(want).astype(np.float64)
+    ok = ok and bool(np.linalg.norm(got - e) / np.linalg.norm(e) <= 1e-3)
+    ok = ok and np.array_equal(be.read_buffer(qc2), be.read_buffer(qc0)) and np.array_equal(be.read_buffer(qs2), be.read_buffer(qs0))
     dist.barrier()
     t = torch.tensor([1 if ok else 0], device=f"cuda:{rank}")
     dist.all_reduce(t)

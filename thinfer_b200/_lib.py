@@ -86,6 +86,8 @@ SIGNATURES = {
     "tnf_ipc_export": (C.c_int32, [_ctx, C.c_uint64, C.c_void_p]),
     "tnf_peer_outputs": (C.c_int32, [_ctx, C.c_int32, C.c_int32, C.c_void_p]),
     "tnf_scatter_rows": (C.c_int32, [_ctx, C.c_int32, Buf, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "tnf_push_peers": (C.c_int32, [_ctx, C.c_int32, Buf, C.c_uint64, Buf]),
+    "tnf_interleave_cols": (C.c_int32, [_ctx, Buf, C.c_uint64, C.c_uint32, C.c_uint32, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
     "tnf_compute_after_copy": (C.c_int32, [_ctx]),
     "tnf_comm_barrier": (C.c_int32, [_ctx]),
 }

@@ -372,6 +372,10 @@ int32_t tnf_destroy(tnf_ctx* ctx) {
   cudaFree(ctx->dwords);
   cudaStreamDestroy(ctx->compute);
   cudaStreamDestroy(ctx->copy);
+  for (int i = 0; i < 8; ++i) {
+    if (ctx->push[i]) cudaStreamDestroy(ctx->push[i]);
+    if (ctx->push_done[i]) cudaEventDestroy(ctx->push_done[i]);
+  }
   cudaGetLastError();
   delete ctx;
   return TNF_OK;

@@ -6,6 +6,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "context.h"
@@ -67,14 +68,14 @@ __global__ void pack_cols_kernel(const uint4* __restrict__ out, uint4* __restric
 // gathered: rank w's [rows, n_local] block starts at w * rank_stride -> out columns w * n_local, skipping this rank's own
 __global__ void unpack_cols_kernel(const uint4* __restrict__ gathered, uint4* __restrict__ out, uint32_t rows,
                                    uint32_t row_stride, uint32_t n_local, uint64_t rank_stride, uint32_t world,
-                                   uint32_t self) {
+                                   uint32_t self, uint32_t src_row_stride) {
   uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (t >= uint64_t(world) * rows * n_local) return;
   uint32_t c = uint32_t(t % n_local);
   uint64_t q = t / n_local;
   uint32_t r = uint32_t(q % rows), w = uint32_t(q / rows);
   if (w == self) return;
-  out[uint64_t(r) * row_stride + uint64_t(w) * n_local + c] = gathered[uint64_t(w) * rank_stride + uint64_t(r) * n_local + c];
+  out[uint64_t(r) * row_stride + uint64_t(w) * n_local + c] = gathered[uint64_t(w) * rank_stride + uint64_t(r) * src_row_stride + c];
 }
 
 static cudaError_t ensure_gather_tmp(tnf_ctx* ctx, uint64_t need) {
@@ -171,7 +172,7 @@ int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t
   threads *= uint64_t(ctx->world);
   unpack_cols_kernel<<<unsigned((threads + 255) / 256), 256, 0, ctx->compute>>>(
       reinterpret_cast<const uint4*>(recv), reinterpret_cast<uint4*>(out), m, nt8, nl8, uint64_t(m) * nl8,
-      uint32_t(ctx->world), uint32_t(ctx->rank));
+      uint32_t(ctx->world), uint32_t(ctx->rank), nl8);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
   return TNF_OK;
@@ -216,9 +217,9 @@ int32_t tnf_all_gather_nvfp4(tnf_ctx* ctx, tnf_buf codes, tnf_buf scales, uint32
   ncclResult_t r = api->AllGather(send, recv, slice, ncclUint8, static_cast<ncclComm_t>(ctx->nccl_comm), ctx->compute);
   if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllGather");
   unpack_cols_kernel<<<unsigned((c_units * world + 255) / 256), 256, 0, ctx->compute>>>(
-      recv, reinterpret_cast<uint4*>(pc), m, c_tot, c_loc, slice / 16, world, rank);
+      recv, reinterpret_cast<uint4*>(pc), m, c_tot, c_loc, slice / 16, world, rank, c_loc);
   unpack_cols_kernel<<<unsigned((s_units * world + 255) / 256), 256, 0, ctx->compute>>>(
-      recv + c_units, reinterpret_cast<uint4*>(ps), row_blocks, s_tot, s_loc, slice / 16, world, rank);
+      recv + c_units, reinterpret_cast<uint4*>(ps), row_blocks, s_tot, s_loc, slice / 16, world, rank, s_loc);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "unpack launch");
   return TNF_OK;
@@ -309,6 +310,111 @@ int32_t tnf_scatter_rows(tnf_ctx* ctx, int32_t set, tnf_buf out_bf16, uint32_t r
                           uint64_t(n) * 2, rows, cudaMemcpyDeviceToDevice, ctx->copy);
     if (e != cudaSuccess) return cuda_fail(e, "tnf_scatter_rows: peer copy");
   }
+  return TNF_OK;
+}
+
+int32_t tnf_push_peers(tnf_ctx* ctx, int32_t set, tnf_buf src, uint64_t dst_offset, tnf_buf self_dst) {
+  if (!ctx || set < 0 || set >= tnf_ctx::kPeerSets || src.len == 0 || (self_dst.len && self_dst.len != src.len)) {
+    set_error("tnf_push_peers: bad arguments (set %d, %llu bytes, own copy of %llu)", set, (unsigned long long)src.len,
+              (unsigned long long)self_dst.len);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  int32_t st = TNF_OK;
+  const uint8_t* from = resolve(ctx, src, src.len, "src", &st);
+  if (!from) return st;
+  uint8_t* own = nullptr;
+  if (self_dst.len) {
+    own = resolve(ctx, self_dst, self_dst.len, "self_dst", &st);
+    if (!own) return st;
+  }
+  // the copies start when everything launched so far on the compute stream (the GEMM that wrote src) is done
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (!ctx->event_pool.empty()) {
+      ev = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    }
+  }
+  if (!ev) {
+    e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+  }
+  // copies go out in ring order (next rank first), so with one lane every rank receives from one sender
+  // at a time; TNF_PUSH_STREAMS=k spreads them over k streams (measured: no gain with 3 peers, a loss with 7)
+  const int np = ctx->n_peers[set];
+  static const int want_lanes = [] {
+    const char* v = std::getenv("TNF_PUSH_STREAMS");
+    const int k = v ? std::atoi(v) : 1;
+    return k < 1 ? 1 : (k > 8 ? 8 : k);
+  }();
+  const int lanes = want_lanes < np + 1 ? want_lanes : np + 1;
+  for (int i = 0; i < lanes; ++i) {
+    if (!ctx->push[i]) {
+      e = cudaStreamCreateWithFlags(&ctx->push[i], cudaStreamNonBlocking);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->push_done[i], cudaEventDisableTiming);
+      if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: stream");
+    }
+  }
+  e = cudaEventRecord(ev, ctx->compute);
+  for (int i = 0; i < lanes && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(ctx->push[i], ev, 0);
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->event_pool.push_back(ev);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: stream order");
+  // windows are kept in rank order without this rank; the copy stream then waits for every lane
+  const int self = (ctx->world == np + 1) ? ctx->rank : 0;
+  for (int d = 1; d <= np; ++d) {
+    const int pr = (self + d) % (np + 1);
+    const int i = pr < self ? pr : pr - 1;
+    e = cudaMemcpyAsync(static_cast<uint8_t*>(ctx->peer_out[set][i]) + dst_offset, from, src.len, cudaMemcpyDeviceToDevice,
+                        ctx->push[(d - 1) % lanes]);
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: peer copy");
+  }
+  if (own) {
+    e = cudaMemcpyAsync(own, from, src.len, cudaMemcpyDeviceToDevice, ctx->push[np % lanes]);
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: own copy");
+  }
+  for (int i = 0; i < lanes; ++i) {
+    e = cudaEventRecord(ctx->push_done[i], ctx->push[i]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy, ctx->push_done[i], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: join");
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_interleave_cols(tnf_ctx* ctx, tnf_buf gathered, uint64_t rank_stride, uint32_t src_row_bytes, uint32_t world,
+                            tnf_buf out, uint32_t out_row_bytes, uint32_t rows, uint32_t local_row_bytes) {
+  if (!ctx || world == 0 || rows == 0 || local_row_bytes == 0 || (local_row_bytes | src_row_bytes | out_row_bytes) % 16 ||
+      rank_stride % 16 || src_row_bytes < local_row_bytes || uint64_t(local_row_bytes) * world > out_row_bytes ||
+      rank_stride < uint64_t(rows - 1) * src_row_bytes + local_row_bytes) {
+    set_error("tnf_interleave_cols: bad arguments (world %u, rows %u, %u of %u bytes per source row, %u per output row, "
+              "rank stride %llu; 16-byte units)", world, rows, local_row_bytes, src_row_bytes, out_row_bytes,
+              (unsigned long long)rank_stride);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  int32_t st = TNF_OK;
+  const uint8_t* g = resolve(ctx, gathered, uint64_t(world - 1) * rank_stride + uint64_t(rows - 1) * src_row_bytes + local_row_bytes,
+                             "gathered", &st);
+  if (!g) return st;
+  uint8_t* o = resolve(ctx, out, uint64_t(rows - 1) * out_row_bytes + uint64_t(local_row_bytes) * world, "out", &st);
+  if (!o) return st;
+  if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(o)) & 15) {
+    set_error("tnf_interleave_cols: views must start on 16-byte boundaries");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  const uint32_t nl = local_row_bytes / 16;
+  const uint64_t threads = uint64_t(world) * rows * nl;
+  unpack_cols_kernel<<<unsigned((threads + 255) / 256), 256, 0, ctx->compute>>>(
+      reinterpret_cast<const uint4*>(g), reinterpret_cast<uint4*>(o), rows, out_row_bytes / 16, nl, rank_stride / 16, world,
+      0xFFFFFFFFu, src_row_bytes / 16);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "interleave launch");
   return TNF_OK;
 }
 

@@ -74,3 +74,69 @@ class NSplitGroup:
     def all_gather_nvfp4(self, codes: Buf, scales_device: Buf, m: int, n_total: int) -> None:
         """Gather an output the epilogue left in NVFP4 (codes + device-layout scales), 0.5625 B per element."""
         _check(self.be.lib.tnf_all_gather_nvfp4(self.be._ctx, codes, scales_device, m, n_total, n_total // self.world))
+
+    def push_peers(self, window_set: int, src: Buf, dst_offset: int, self_dst: Buf) -> None:
+        """Copy-engine push of a contiguous range to the same offset of every peer's receive area."""
+        _check(self.be.lib.tnf_push_peers(self.be._ctx, window_set, src, dst_offset, self_dst))
+
+
+class PackedGather:
+    """One N-split output delivered by contiguous copy-engine pushes.
+
+    The linear writes this rank's column slice PACKED into ``send`` (ldo = n_local); finished row
+    bands are pushed to slot ``rank`` of every rank's receive area while the next band computes;
+    ``finish`` waits, meets the other ranks and lays the slots side by side in the full output.
+    ``kind`` is "bf16" (rows of n_local bf16) or "nvfp4" (rows of n_local/2 code bytes plus the
+    device-layout scales of the [m, n_local] operand).
+    """
+
+    def __init__(self, grp: NSplitGroup, window_set: int, m: int, n_total: int, kind: str = "bf16"):
+        from .backend import device_scales_bytes
+
+        be = grp.be
+        self.grp, self.set, self.m, self.n_total, self.kind = grp, window_set, m, n_total, kind
+        self.n_local = n_total // grp.world
+        if n_total % grp.world or self.n_local % (64 if kind == "nvfp4" else 8):
+            raise ValueError(f"n={n_total} does not split into {grp.world} slices of whole 16-byte groups")
+        self.row_bytes = self.n_local // 2 if kind == "nvfp4" else self.n_local * 2
+        self.main_bytes = m * self.row_bytes
+        self.main_cap = (self.main_bytes + 255) // 256 * 256
+        self.scale_bytes = device_scales_bytes(m, self.n_local) if kind == "nvfp4" else 0
+        self.scale_block = self.scale_bytes // ((m + 127) // 128) if kind == "nvfp4" else 0  # bytes per 128-row block
+        self.slot = self.main_cap + (self.scale_bytes + 255) // 256 * 256
+        self.send = be.allocate(self.slot)
+        self.recv = be.allocate(self.slot * grp.world)
+        grp.register_output(window_set, self.recv)
+
+    # views of the packed slice for a row band (row0 a multiple of 128)
+    def send_main(self, row0: int = 0, rows: int = 0) -> Buf:
+        rows = rows or self.m - row0
+        return Buf(self.send.id, self.send.offset + row0 * self.row_bytes, rows * self.row_bytes)
+
+    def send_scales(self, row0: int = 0, rows: int = 0) -> Buf:
+        rows = rows or self.m - row0
+        return Buf(self.send.id, self.send.offset + self.main_cap + (row0 // 128) * self.scale_block,
+                   ((rows + 127) // 128) * self.scale_block)
+
+    def push(self, row0: int = 0, rows: int = 0) -> None:
+        """Queue the delivery of a finished row band (after the compute work queued so far)."""
+        base = self.grp.rank * self.slot
+        parts = [self.send_main(row0, rows)] + ([self.send_scales(row0, rows)] if self.kind == "nvfp4" else [])
+        for v in parts:
+            off = base + (v.offset - self.send.offset)
+            self.grp.push_peers(self.set, v, off, Buf(self.recv.id, self.recv.offset + off, v.len))
+
+    def finish(self, out: Buf, out_scales: Buf = None, sync: bool = True) -> None:
+        """Wait for the pushes, meet the other ranks (``sync=False``: the caller already did both),
+        interleave the slots into the full output."""
+        g, lib, ctx = self.grp, self.grp.be.lib, self.grp.be._ctx
+        if sync:
+            g.wait_scatter()
+            g.barrier()
+        _check(lib.tnf_interleave_cols(ctx, self.recv, self.slot, self.row_bytes, g.world, out, self.row_bytes * g.world,
+                                       self.m, self.row_bytes))
+        if self.kind == "nvfp4":
+            k_atoms = ((self.n_total // 64) + 3) // 4 * 4
+            src = Buf(self.recv.id, self.recv.offset + self.main_cap, self.recv.len - self.main_cap)
+            _check(lib.tnf_interleave_cols(ctx, src, self.slot, self.scale_block, g.world, out_scales, k_atoms * 512,
+                                           (self.m + 127) // 128, (self.n_local // 64) * 512))
