@@ -5,7 +5,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libthinfer_nvfp4.so")
+# THINFER_B200_LIB points at another build of the same library (a variant compiled with different options)
+LIB_PATH = os.environ.get("THINFER_B200_LIB") or os.path.join(_HERE, "libthinfer_nvfp4.so")
 
 OK = 0
 ERR_UNKNOWN_BUFFER, ERR_ALLOCATE_OOM, ERR_BUDGET_EXCEEDED = -1, -2, -3

@@ -118,18 +118,21 @@ template <bool kGelu, bool kChain, bool kGate>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
                                                    uint8_t* buf_gen, const uint4* bias_smem, const float* lut, int lane) {
   const bool row_ok = row < p.m;
-  uint32_t cw[8], sw = 0;  // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes
+  // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes. Each 16-byte group of codes
+  // is stored as soon as it is complete, so only four code words are live beside the accumulators
+  // (holding all eight spilled, and the spill reloads, not the math, cost ~30 us on the MLP-up shape).
+  const bool q_on = p.q_codes != nullptr && row_ok && ncol0 < p.n;  // n % 64 == 0: the whole group is in range
+  const uint32_t qcol = p.n_offset + ncol0;  // the copy is an [m, ldo] operand; this launch fills n_offset .. n_offset + n
+  uint32_t cw[4], sw = 0;
   uint4 prev = make_uint4(0, 0, 0, 0);
 #pragma unroll
   for (int sub = 0; sub < 2; ++sub) {
-    uint4 b4[4], g4[4], s4[4];
+    uint4 g4[4], s4[4];
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {  // loads first so that their latencies overlap
+    for (int jj = 0; jj < 4; ++jj) {  // global loads first so that their latencies overlap
       const uint32_t nc = ncol0 + (sub * 4 + jj) * 8;
-      const bool col_ok = nc < p.n;
-      b4[jj] = g4[jj] = s4[jj] = make_uint4(0, 0, 0, 0);
-      if (p.bias) b4[jj] = bias_smem[sub * 4 + jj];  // staged per tile (zero past n); broadcast read
-      if (kGate && col_ok) {
+      g4[jj] = s4[jj] = make_uint4(0, 0, 0, 0);
+      if (kGate && nc < p.n) {
         g4[jj] = __ldg(reinterpret_cast<const uint4*>(p.gate + nc));
         if (row_ok) s4[jj] = __ldg(reinterpret_cast<const uint4*>(p.residual + uint64_t(row) * p.n + nc));
       }
@@ -137,36 +140,27 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const int j = sub * 4 + jj;
-      const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4[jj], g4[jj], s4[jj]);
+      uint4 b4 = make_uint4(0, 0, 0, 0);
+      if (p.bias) b4 = bias_smem[j];  // staged per tile (zero past n); broadcast read
+      const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4, g4[jj], s4[jj]);
       *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
       if (p.q_codes) {  // uniform: quantise the bf16-ROUNDED values, 16 columns at a time
-        if (j & 1) {
+        if (jj & 1) {
           const uint32_t w[8] = {prev.x, prev.y, prev.z, prev.w, o.x, o.y, o.z, o.w};
-          float x[16];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            x[2 * i] = bf16_lo(w[i]);
-            x[2 * i + 1] = bf16_hi(w[i]);
-          }
           uint32_t lo, hi;
-          const uint32_t sc = quant_block16(x, lut, p.q_inv_t, lo, hi);
-          cw[j - 1] = lo;
-          cw[j] = hi;
+          const uint32_t sc = quant_block16_bf16(w, lut, p.q_inv_t, lo, hi);
+          cw[jj - 1] = lo;
+          cw[jj] = hi;
           sw |= sc << (8 * (j >> 1));
         } else {
           prev = o;
         }
       }
     }
+    if (q_on)
+      *reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.ldo >> 1) + (qcol >> 1) + sub * 16) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
   }
-  if (p.q_codes && row_ok && ncol0 < p.n) {  // n % 64 == 0: the whole group is in range
-    // the NVFP4 copy is an [m, ldo] operand; this launch fills its columns n_offset .. n_offset + n
-    const uint32_t qcol = p.n_offset + ncol0;
-    uint4* qc = reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.ldo >> 1) + (qcol >> 1));
-    qc[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
-    qc[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
-    *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, qcol >> 4, p.q_k_atoms)) = sw;
-  }
+  if (q_on) *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, qcol >> 4, p.q_k_atoms)) = sw;
 }
 
 __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,

@@ -2,6 +2,7 @@
 // Explicitly rounded IEEE f32 operations and the hardware cvt.rn.satfinite narrowing: bit-exact
 // with the CPU oracle (see quant.cu).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 #include <cstdint>
@@ -38,6 +39,42 @@ __device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], const fl
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float2 v = make_float2(__fmul_rn(x[2 * i], inv_d), __fmul_rn(x[2 * i + 1], inv_d));
+      uint32_t b = (uint32_t)__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest) & 0xFFu;
+      if (i < 4) lo |= b << (8 * i);
+      else hi |= b << (8 * (i - 4));
+    }
+  }
+  return sc;
+}
+
+// The same block from 8 packed bf16 pairs (element 2i in the low half of w[i]): the block maximum is
+// taken on the packed values (exact: a maximum of bf16 magnitudes, NaNs dropped like fmaxf drops
+// them), which halves the instructions and the live registers of the f32 form. Same bits out.
+__device__ __forceinline__ uint32_t quant_block16_bf16(const uint32_t (&w)[8], const float* inv_d_lut, float inv_t,
+                                                       uint32_t& lo, uint32_t& hi) {
+  __nv_bfloat162 m2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t a = w[i] & 0x7FFF7FFFu;
+    m2[i] = *reinterpret_cast<const __nv_bfloat162*>(&a);
+  }
+#pragma unroll
+  for (int s = 4; s >= 1; s >>= 1)
+#pragma unroll
+    for (int i = 0; i < s; ++i) m2[i] = __hmax2(m2[i], m2[i + s]);
+  const uint32_t mm = *reinterpret_cast<const uint32_t*>(&m2[0]);
+  const float bmax = fmaxf(fmaxf(0.0f, __uint_as_float(mm << 16)), __uint_as_float(mm & 0xFFFF0000u));
+  float s_raw = __fmul_rn(bmax, inv_t);
+  uint32_t sc = (uint32_t)__nv_cvt_float_to_fp8(s_raw, __NV_SATFINITE, __NV_E4M3) & 0xFFu;
+  if (sc == 0x7Fu || sc == 0xFFu) sc = 0;  // NaN scale -> treated as a zero block
+  sc &= 0x7Fu;
+  lo = 0;
+  hi = 0;
+  if (sc != 0) {
+    const float inv_d = inv_d_lut[sc];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float2 v = make_float2(__fmul_rn(__uint_as_float(w[i] << 16), inv_d), __fmul_rn(__uint_as_float(w[i] & 0xFFFF0000u), inv_d));
       uint32_t b = (uint32_t)__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest) & 0xFFu;
       if (i < 4) lo |= b << (8 * i);
       else hi |= b << (8 * (i - 4));

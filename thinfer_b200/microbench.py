@@ -1,7 +1,7 @@
 """Times one NVFP4 linear shape through the C ABI (also the command the ncu captures run).
 
     python -m thinfer_b200.microbench --m 4352 --n 3072 --k 12288 [--act 1] [--iters 20]
-                                      [--no-quant] [--flush-l2]
+                                      [--no-quant] [--flush-l2] [--out-nvfp4]
 
 Prints one JSON line: average GEMM and activation-quantiser launch times (CUDA events on the
 library's compute stream), TFLOP/s and the algorithmic bytes. Inputs are seeded random
@@ -55,7 +55,7 @@ def random_weight(be, n, k, gen, sigma=0.02, bias=True):
     return Nvfp4Weight(n, k, codes, devs, float(g.value), b, None)
 
 
-def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0):
+def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0, out_nvfp4=False):
     import torch
 
     from . import Backend
@@ -71,6 +71,10 @@ def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0
     a = be.allocate(m * k * 2)
     _tview(be, a, torch.bfloat16, (m, k)).copy_(torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16))
     out = be.allocate(m * n * 2)
+    q_out = None
+    if out_nvfp4:  # the epilogue also emits the result as the next linear's NVFP4 operand
+        from .backend import device_scales_bytes
+        q_out = (be.allocate(m * n // 2), be.allocate(device_scales_bytes(m, n)), 0.0009765625)
     torch.cuda.synchronize()
     _, _, ga = sc.act_quant(a, m, k, 0.0, device_layout=True)[0:3]
     stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
@@ -85,7 +89,7 @@ def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0
         if quant or it == 0:
             sc.act_quant_shared(a, m, k, ga)
         e[1].record(stream)
-        sc.linear(None, m, W, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED)
+        sc.linear(None, m, W, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED, out_nvfp4=q_out)
         e[2].record(stream)
         be.submit(60000)
         torch.cuda.synchronize()
@@ -95,7 +99,7 @@ def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0
     flops = 2.0 * m * n * k
     gemm_ms, quant_ms = float(np.mean(tg)), float(np.mean(tq))
     res = {
-        "m": m, "n": n, "k": k, "act": act, "iters": iters, "flush_l2": bool(flush_l2),
+        "m": m, "n": n, "k": k, "act": act, "out_nvfp4": bool(out_nvfp4), "iters": iters, "flush_l2": bool(flush_l2),
         "gemm_ms": gemm_ms, "gemm_ms_min": float(np.min(tg)), "quant_ms": quant_ms if quant else None,
         "gemm_tflops": flops / (gemm_ms * 1e-3) / 1e12,
         "linear_tflops": flops / ((gemm_ms + (quant_ms if quant else 0.0)) * 1e-3) / 1e12,
@@ -118,8 +122,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-quant", action="store_true")
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--out-nvfp4", action="store_true")
     args = ap.parse_args()
-    print(json.dumps(run(args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2)))
+    print(json.dumps(run(args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
+                         out_nvfp4=args.out_nvfp4)))
 
 
 if __name__ == "__main__":
