@@ -42,22 +42,26 @@ __global__ void global_scale_kernel(const uint32_t* amax_bits, float* g) {
 }
 
 // ---- block quantiser --------------------------------------------------------------------------
-// One 16-element block per (thread, round); a warp covers 128 consecutive blocks of the block grid
-// in 4 rounds (lane l takes block base + 32*round + l), and issues the loads of all four rounds
-// before any arithmetic so that four 32-byte reads per thread are in flight. With the device scale
-// layout the grid is PADDED (rows up to a multiple of 128, blocks up to k_atoms*4), each aligned
-// group of 4 lanes owns one 4-byte scale word (row r, blocks 4i..4i+3), assembled with shuffles;
-// padding words are written as zero. g_ptr (device: {g, 1/(6g)}) wins over g_val when not null.
+// One 16-element block per (thread, round): in a round a warp takes 32 consecutive blocks of the
+// block grid (1 KB of bf16). The grid is persistent (at most 6 CTAs of 8 warps per SM, 40
+// registers): warp w handles rounds w, w + W, w + 2W, ... and issues the loads of its next round
+// before the arithmetic of the current one, so a thread always has 64-128 bytes in flight and
+// there is no half-empty last wave. With the device scale layout the block grid is PADDED (rows up
+// to a multiple of 128, blocks up to k_atoms*4), each aligned group of 4 lanes owns one 4-byte
+// scale word (row r, blocks 4i..4i+3), assembled with shuffles; padding words are written as zero.
+// g_ptr (device: {g, 1/(6g)}) wins over g_val when not null. The launcher guarantees
+// rows_grid*nb_grid < 2^32.
 template <typename T, bool kDeviceLayout>
-__global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32_t k, const float* __restrict__ g_ptr,
-                                float g_val, float inv_t_val, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                                uint32_t k_atoms) {
-  constexpr int kRounds = 4;
+__global__ void __launch_bounds__(256, 6)
+    quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32_t k, const float* __restrict__ g_ptr, float g_val,
+                    float inv_t_val, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t k_atoms) {
+  constexpr int kVec = sizeof(T) == 2 ? 2 : 4;  // 16-byte loads per block
   const uint32_t nb = k >> 4;
   const uint32_t nb_grid = kDeviceLayout ? k_atoms * 4u : nb;
   const uint32_t rows_grid = kDeviceLayout ? ((rows + 127u) & ~127u) : rows;
-  const uint64_t total = uint64_t(rows_grid) * nb_grid;
-  const uint64_t warp_base = (uint64_t(blockIdx.x) * blockDim.x + (threadIdx.x & ~31u)) * kRounds;
+  const uint32_t total = rows_grid * nb_grid;
+  const uint32_t n_rounds = (total + 31u) >> 5;  // the padded grid is a multiple of 32 blocks
+  const uint32_t warps_total = gridDim.x * (blockDim.x >> 5);
   const uint32_t lane = threadIdx.x & 31u;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // launched with programmatic dependent launch: see internal.h
@@ -66,56 +70,61 @@ __global__ void quantize_kernel(const T* __restrict__ src, uint32_t rows, uint32
   __shared__ float inv_d_lut[128];
   fill_inv_scale_lut(inv_d_lut, g, threadIdx.x, blockDim.x);
   __syncthreads();
-  if (warp_base >= total) return;  // warp-uniform
 
-  uint32_t r[kRounds], b[kRounds];
-  bool valid[kRounds];
-  uint4 raw[kRounds][sizeof(T) == 2 ? 2 : 4];
+  uint32_t wr = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  uint32_t r = 0, b = 0;
+  bool valid = false;
+  uint4 cur[kVec];
+  auto fetch = [&](uint32_t round, uint32_t& rr, uint32_t& bb, bool& ok, uint4(&raw)[kVec]) {
+    const uint32_t t = round * 32u + lane;
+    rr = t / nb_grid;
+    bb = t - rr * nb_grid;
+    ok = round < n_rounds && t < total && rr < rows && bb < nb;
+    if (ok) {
+      const uint4* p4 = reinterpret_cast<const uint4*>(src + uint64_t(rr) * k + uint64_t(bb) * 16u);
 #pragma unroll
-  for (int j = 0; j < kRounds; ++j) {
-    const uint64_t t = warp_base + uint64_t(j) * 32u + lane;
-    r[j] = uint32_t(t / nb_grid);
-    b[j] = uint32_t(t % nb_grid);
-    valid[j] = t < total && r[j] < rows && b[j] < nb;
-    if (valid[j]) {
-      const uint4* p4 = reinterpret_cast<const uint4*>(src + uint64_t(r[j]) * k + uint64_t(b[j]) * 16u);
-#pragma unroll
-      for (int i = 0; i < int(sizeof(T) == 2 ? 2 : 4); ++i) raw[j][i] = __ldg(p4 + i);
+      for (int i = 0; i < kVec; ++i) raw[i] = __ldg(p4 + i);
     }
-  }
-#pragma unroll
-  for (int j = 0; j < kRounds; ++j) {
+  };
+  if (wr < n_rounds) fetch(wr, r, b, valid, cur);
+  while (wr < n_rounds) {  // warp-uniform
+    uint32_t r_n = 0, b_n = 0;
+    bool valid_n = false;
+    uint4 nxt[kVec];
+    fetch(wr + warps_total, r_n, b_n, valid_n, nxt);
     uint32_t sc = 0;
-    if (valid[j]) {
-      float x[16];
+    if (valid) {
+      uint32_t lo, hi;
       if constexpr (sizeof(T) == 2) {
-        const uint32_t w[8] = {raw[j][0].x, raw[j][0].y, raw[j][0].z, raw[j][0].w, raw[j][1].x, raw[j][1].y, raw[j][1].z, raw[j][1].w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          x[2 * i] = __uint_as_float(w[i] << 16);
-          x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
+        const uint32_t w[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
+        sc = quant_block16_bf16(w, inv_d_lut, inv_t, lo, hi);
       } else {
+        float x[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          x[4 * i] = __uint_as_float(raw[j][i].x);
-          x[4 * i + 1] = __uint_as_float(raw[j][i].y);
-          x[4 * i + 2] = __uint_as_float(raw[j][i].z);
-          x[4 * i + 3] = __uint_as_float(raw[j][i].w);
+          x[4 * i] = __uint_as_float(cur[i].x);
+          x[4 * i + 1] = __uint_as_float(cur[i].y);
+          x[4 * i + 2] = __uint_as_float(cur[i].z);
+          x[4 * i + 3] = __uint_as_float(cur[i].w);
         }
+        sc = quant_block16(x, inv_d_lut, inv_t, lo, hi);
       }
-      uint32_t lo, hi;
-      sc = quant_block16(x, inv_d_lut, inv_t, lo, hi);
-      *reinterpret_cast<uint2*>(codes + uint64_t(r[j]) * (k >> 1) + uint64_t(b[j]) * 8u) = make_uint2(lo, hi);
+      *reinterpret_cast<uint2*>(codes + uint64_t(r) * (k >> 1) + uint64_t(b) * 8u) = make_uint2(lo, hi);
     }
-    if (kDeviceLayout) {  // the padded grid is a multiple of 128 blocks: every lane of the warp is in range here
-      uint32_t w = sc << (8u * (b[j] & 3u));
+    if (kDeviceLayout) {  // every lane of a round of the padded grid is in range: the shuffles are warp-wide
+      uint32_t w = sc << (8u * (b & 3u));
       w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
       w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-      if ((b[j] & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(r[j], b[j], k_atoms)) = w;
-    } else if (valid[j]) {
-      scales[uint64_t(r[j]) * nb + b[j]] = uint8_t(sc);
+      if ((b & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(r, b, k_atoms)) = w;
+    } else if (valid) {
+      scales[uint64_t(r) * nb + b] = uint8_t(sc);
     }
+    wr += warps_total;
+    r = r_n;
+    b = b_n;
+    valid = valid_n;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) cur[i] = nxt[i];
   }
 }
 
@@ -151,7 +160,15 @@ cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t 
   const float inv_t_val = 1.0f / (6.0f * g_val);  // same f32 operations as the device and the oracle
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
-  unsigned blocks = unsigned((threads + 1023) / 1024);  // 256 threads x 4 rounds per block
+  if (threads >= (uint64_t(1) << 32)) return cudaErrorInvalidValue;  // the kernel indexes blocks with 32 bits
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  // persistent: 8 warps per CTA, one 32-block round per warp and iteration, at most 6 CTAs per SM
+  unsigned blocks = unsigned(std::min<uint64_t>((threads + 255) / 256, uint64_t(sms) * 6));
   // Keep the SMs in the same L1/shared-memory split as the GEMMs that run before and after (they take
   // the whole 227 KB as shared memory): a kernel that prefers L1 makes every following GEMM launch wait
   // for the split to be switched back.
