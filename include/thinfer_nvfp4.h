@@ -152,7 +152,8 @@ enum {
   /* The epilogue also quantises its bf16-rounded result to NVFP4 (same bits as tnf_quantize_act
    * on out_bf16 would give), ready to be the A operand of tnf_gemm_nvfp4: MLP up -> GELU -> down
    * (thinfer-models/src/qwen_image/dit.rs:745-754) without the act_quant dispatch between.
-   * Requires n, n_offset and ldo to be multiples of 64. */
+   * Requires n, n_offset and ldo to be multiples of 64; not combinable with gate_bf16 / residual_bf16
+   * or TNF_LINEAR_SCATTER_PEERS. */
   TNF_LINEAR_OUT_NVFP4 = 4u,
   TNF_LINEAR_NO_BF16_OUT = 8u     /* with OUT_NVFP4: skip the bf16 store (out_bf16 may have len 0) */
 };

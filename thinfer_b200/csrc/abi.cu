@@ -240,9 +240,9 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.store_bf16 = store_bf16 ? 1u : 0u;
   if (q_out) {
     if (a->n % 64 != 0 || a->n_offset % 64 != 0 || ldo % 64 != 0 || !(a->out_global > 0.0f) ||
-        (a->flags & TNF_LINEAR_SCATTER_PEERS)) {
+        (a->flags & TNF_LINEAR_SCATTER_PEERS) || a->gate_bf16.len) {
       set_error("TNF_LINEAR_OUT_NVFP4 needs n, n_offset and ldo multiples of 64 (n=%u, n_offset=%u, ldo=%u), "
-                "out_global > 0 and no peer scatter", a->n, a->n_offset, ldo);
+                "out_global > 0, no peer scatter and no gated residual", a->n, a->n_offset, ldo);
       return TNF_ERR_INVALID_ARGUMENT;
     }
     // the NVFP4 copy is the [m, ldo] operand of the next linear; this call fills columns n_offset .. n_offset + n

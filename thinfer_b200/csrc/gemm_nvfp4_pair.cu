@@ -114,14 +114,14 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool 
 
 // One warp's 32 rows x 64 columns: accumulator registers -> bf16 rows in the swizzled staging
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
-template <bool kGelu, bool kChain, bool kGate>
+template <bool kGelu, bool kChain, bool kGate, bool kQuant>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
                                                    uint8_t* buf_gen, const uint4* bias_smem, const float* lut, int lane) {
   const bool row_ok = row < p.m;
   // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes. Each 16-byte group of codes
   // is stored as soon as it is complete, so only four code words are live beside the accumulators
   // (holding all eight spilled, and the spill reloads, not the math, cost ~30 us on the MLP-up shape).
-  const bool q_on = p.q_codes != nullptr && row_ok && ncol0 < p.n;  // n % 64 == 0: the whole group is in range
+  const bool q_on = kQuant && row_ok && ncol0 < p.n;  // n % 64 == 0: the whole group is in range
   const uint32_t qcol = p.n_offset + ncol0;  // the copy is an [m, ldo] operand; this launch fills n_offset .. n_offset + n
   uint32_t cw[4], sw = 0;
   uint4 prev = make_uint4(0, 0, 0, 0);
@@ -144,7 +144,7 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
       if (p.bias) b4 = bias_smem[j];  // staged per tile (zero past n); broadcast read
       const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4, g4[jj], s4[jj]);
       *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
-      if (p.q_codes) {  // uniform: quantise the bf16-ROUNDED values, 16 columns at a time
+      if (kQuant) {  // quantise the bf16-ROUNDED values, 16 columns at a time
         if (jj & 1) {
           const uint32_t w[8] = {prev.x, prev.y, prev.z, prev.w, o.x, o.y, o.z, o.w};
           uint32_t lo, hi;
@@ -167,14 +167,19 @@ __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint
                                                        uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const uint4* bias_smem,
                                                        const float* lut, int lane) {
   switch (mode) {
-    case 0: epilogue_pair_math<false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 1: epilogue_pair_math<true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 2: epilogue_pair_math<false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 3: epilogue_pair_math<true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 4: epilogue_pair_math<false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 5: epilogue_pair_math<true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 6: epilogue_pair_math<false, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    default: epilogue_pair_math<true, true, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 0: epilogue_pair_math<false, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 1: epilogue_pair_math<true, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 2: epilogue_pair_math<false, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 3: epilogue_pair_math<true, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 4: epilogue_pair_math<false, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 5: epilogue_pair_math<true, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 6: epilogue_pair_math<false, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 7: epilogue_pair_math<true, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    // with an NVFP4 copy of the output (the host refuses the combination with a gated residual)
+    case 8: epilogue_pair_math<false, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 9: epilogue_pair_math<true, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    case 10: epilogue_pair_math<false, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+    default: epilogue_pair_math<true, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
   }
 }
 
@@ -353,7 +358,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     const uint32_t acc_free_leader = mapa_cluster(bar_acc_free, 0);
     uint32_t it = 0;
     bool ok = true;
-    const uint32_t mode = (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.gate ? 4u : 0u);
+    const uint32_t mode = (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.q_codes ? 8u : (p.gate ? 4u : 0u));
     for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
       const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
       const uint32_t row0 = tm2 * 256u + rank * 128u + q * 32u;

@@ -72,26 +72,38 @@ __global__ void __launch_bounds__(256, 6)
   __syncthreads();
 
   uint32_t wr = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // (row, block) of this lane in round wr; later rounds step by a fixed (rows, blocks) stride, so
+  // the loop needs no division
+  const uint32_t stride = warps_total * 32u;
+  const uint32_t step_r = stride / nb_grid, step_b = stride - step_r * nb_grid;
+  uint32_t t_n = wr * 32u + lane;
+  uint32_t r_n = t_n / nb_grid, b_n = t_n - r_n * nb_grid;
   uint32_t r = 0, b = 0;
   bool valid = false;
   uint4 cur[kVec];
-  auto fetch = [&](uint32_t round, uint32_t& rr, uint32_t& bb, bool& ok, uint4(&raw)[kVec]) {
-    const uint32_t t = round * 32u + lane;
-    rr = t / nb_grid;
-    bb = t - rr * nb_grid;
-    ok = round < n_rounds && t < total && rr < rows && bb < nb;
+  auto fetch = [&](uint32_t& rr, uint32_t& bb, bool& ok, uint4(&raw)[kVec]) {  // loads round (t_n, r_n, b_n), then steps it
+    rr = r_n;
+    bb = b_n;
+    ok = t_n < total && r_n < rows && b_n < nb;
     if (ok) {
-      const uint4* p4 = reinterpret_cast<const uint4*>(src + uint64_t(rr) * k + uint64_t(bb) * 16u);
+      const uint4* p4 = reinterpret_cast<const uint4*>(src + uint64_t(r_n) * k + uint64_t(b_n) * 16u);
 #pragma unroll
       for (int i = 0; i < kVec; ++i) raw[i] = __ldg(p4 + i);
     }
+    t_n = (t_n < total) ? t_n + stride : total;  // saturates: no wrap-around past the last round
+    r_n += step_r;
+    b_n += step_b;
+    if (b_n >= nb_grid) {
+      b_n -= nb_grid;
+      ++r_n;
+    }
   };
-  if (wr < n_rounds) fetch(wr, r, b, valid, cur);
+  if (wr < n_rounds) fetch(r, b, valid, cur);
   while (wr < n_rounds) {  // warp-uniform
-    uint32_t r_n = 0, b_n = 0;
+    uint32_t r_x = 0, b_x = 0;
     bool valid_n = false;
     uint4 nxt[kVec];
-    fetch(wr + warps_total, r_n, b_n, valid_n, nxt);
+    fetch(r_x, b_x, valid_n, nxt);
     uint32_t sc = 0;
     if (valid) {
       uint32_t lo, hi;
@@ -120,8 +132,8 @@ __global__ void __launch_bounds__(256, 6)
       scales[uint64_t(r) * nb + b] = uint8_t(sc);
     }
     wr += warps_total;
-    r = r_n;
-    b = b_n;
+    r = r_x;
+    b = b_x;
     valid = valid_n;
 #pragma unroll
     for (int i = 0; i < kVec; ++i) cur[i] = nxt[i];
@@ -160,7 +172,7 @@ cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t 
   const float inv_t_val = 1.0f / (6.0f * g_val);  // same f32 operations as the device and the oracle
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
-  if (threads >= (uint64_t(1) << 32)) return cudaErrorInvalidValue;  // the kernel indexes blocks with 32 bits
+  if (threads >= (uint64_t(1) << 32) - (uint64_t(1) << 20)) return cudaErrorInvalidValue;  // the kernel indexes blocks with 32 bits (one stride of headroom)
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
