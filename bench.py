@@ -53,21 +53,66 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons sampled while the timed region runs: NVML from a thread every
+    10 ms (read-only queries), or `nvidia-smi -lms 200` when the NVML binding is missing."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
+        self.p = self.f = self.thread = None
+        self.samples, self.reason_bits, self.max_mhz, self._stop = [], 0, None, False
+        try:
+            import threading
+
+            import pynvml as N
+            N.nvmlInit()
+            self.N = N
+            self.h = N.nvmlDeviceGetHandleByIndex(self._physical_index(gpu_index))
+            self.max_mhz = float(N.nvmlDeviceGetMaxClockInfo(self.h, N.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # no binding, no driver library: fall back to the command-line tool
+            self.thread = None
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                        "-lms", "200", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             pass
 
+    @staticmethod
+    def _physical_index(i: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        ids = [v for v in vis.split(",") if v.strip() != ""]
+        return int(ids[i]) if i < len(ids) and ids[i].strip().isdigit() else i
+
+    def _run(self):
+        N = self.N
+        while not self._stop:
+            try:
+                mhz = float(N.nvmlDeviceGetClockInfo(self.h, N.NVML_CLOCK_SM))
+                try:
+                    bits = int(N.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    bits = int(N.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                self.samples.append(mhz)
+                self.reason_bits |= bits
+            except Exception:
+                pass
+            time.sleep(0.01)
+
     def stop(self) -> dict:
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(1.0)
+            names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+            reasons = sorted(nm for bit, nm in names.items() if self.reason_bits & bit)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"]}
+            return {"sm_mhz": float(np.median(self.samples)), "sm_min_mhz": float(min(self.samples)), "sm_max_mhz": self.max_mhz,
+                    "reasons": reasons, "samples": len(self.samples), "source": "nvml, 10 ms period, timed region only"}
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.25)
@@ -90,7 +135,8 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         busy = sorted(sm)[len(sm) // 2:]  # upper half = samples under load
-        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi, 200 ms period"}
 
 
 # --------------------------------------------------------------------------------------------
@@ -316,8 +362,8 @@ def run_single_gpu(args):
         "per_shape": {QWEN_LINEARS[j][0]: {"ms": float(np.mean(v)),
                                             "tflops": 2.0 * M * QWEN_LINEARS[j][1] * QWEN_LINEARS[j][2] / (np.mean(v) * 1e-3) / 1e12}
                       for j, v in sorted(per_shape.items())},
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
-        # profiles/nvfp4_gemm_pair_qkv_and_down.md (qkv 52.9 MB, down 60.0 MB; algorithmic 103.7 / 78.1 MB)
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures of the pair
+        # kernel (qkv 52.9 MB, down 60.0 MB; algorithmic 103.7 / 78.1 MB)
         "traffic": 56.4e6, "traffic_note": "mean of the two captured shapes; below the algorithmic bytes (outputs stay in L2)",
     }
 

@@ -250,7 +250,10 @@ def run_multi_gpu(args):
             "clocks": clocks,
             "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_finite": finite},
-            "gpu_launches": args.steps * 4, "breakdown_ms": breakdown,
+            # this library's kernels per step: activation quantiser + GEMM per band and linear (the down projection of
+            # push / nvfp4 takes the gathered NVFP4 operand: no quantiser), pack / unpack / interleave kernels
+            "gpu_launches": args.steps * {"push": 3 * bands + 3, "nvfp4": 9, "nccl": 8, "fused": 4, "copy": 4 * bands}[args.gather],
+            "breakdown_ms": breakdown,
             "m_split_no_collective": {"ms_per_step": ms_msplit, "value": flops / (ms_msplit * 1e-3) / 1e12, "unit": "TFLOP/s",
                                       "note": "same FFN pair with ROWS split over the ranks (full weights per rank, no exchange): "
                                               "the partition this path shards on naturally; reported beside the mandated N-split"},
