@@ -160,6 +160,25 @@ enum {
 
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);
 
+/* LayerNorm (no affine) + AdaLN modulation + activation quantiser in one pass: the two
+ * dispatches in front of every block linear, op_layernorm (thinfer-core/src/ops/layernorm.rs:95-125)
+ * and op_modulate = x * (scale + mod_bias) + shift (thinfer-core/src/ops/bcast_modulate.rs:93-102;
+ * call sites thinfer-models/src/qwen_image/dit.rs:521-532,757-768), followed by tnf_quantize_act
+ * with a given per-tensor scale. The modulated row is rounded to bf16 once (parity_mode 1: also
+ * after the LayerNorm, as the reference's two dispatches do) and quantised from those bits, so
+ * out_codes / out_scales (DEVICE layout) hold what tnf_quantize_act would make of out_bf16; they
+ * feed tnf_gemm_nvfp4. scale_bf16 / shift_bf16: [k] bf16, both or neither (len 0 = LayerNorm only);
+ * out_bf16: [m, k] or len 0 to skip the bf16 store. k % 16 == 0, k <= 16384, out_global > 0. */
+typedef struct {
+  uint32_t m, k;
+  float eps;       /* 1e-6 at the reference's call sites */
+  float mod_bias;  /* 1.0 folds the "1 +" of AdaLN */
+  tnf_buf x_bf16, scale_bf16, shift_bf16, out_bf16, out_codes, out_scales;
+  float out_global;
+  uint32_t parity_mode; /* 0 fused, 1 chain */
+} tnf_norm_quant_args;
+int32_t tnf_norm_modulate_quantize(tnf_ctx* ctx, const tnf_norm_quant_args* args);
+
 /* Same linear, for callers that must not allocate device memory (a fixed memory plan, a
  * latency-critical thread, a host that forbids allocation after start-up). It has no counterpart
  * in the reference. The quantised activations go to a 16 MiB array built into the library

@@ -57,6 +57,9 @@ def _load():
         "ref_dequantize_row_q4_0": (None, [vp, i64, vp]),
         "ref_act_quant_i8": (None, [vp, i64, i64, vp, vp]),
         "ref_matmul_i8": (None, [vp, vp, vp, vp, vp, i64, i64, i64, vp]),
+        "ref_layernorm": (None, [vp, C.c_int, i64, i64, f32, vp]),
+        "ref_bcast_modulate": (None, [vp, vp, vp, C.c_int, i64, i64, f32, vp]),
+        "ref_norm_modulate_bf16": (None, [vp, vp, vp, i64, i64, f32, f32, C.c_int, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -289,4 +292,33 @@ def ref_matmul_i8(a, a_scale, a_zero, b, b_scale):
     out = np.empty((m, n), np.float32)
     _lib.ref_matmul_i8(_p(a), _p(_c(a_scale, np.float32)), _p(_c(a_zero, np.float32)), _p(b),
                        _p(_c(b_scale, np.float32)), m, n, k, _p(out))
+    return out
+
+
+def ref_layernorm(x, eps: float):
+    """Row LayerNorm without affine (thinfer-core/src/ops/layernorm.rs); f32 in -> f32 out, uint16 (bf16 bits) in -> bf16 bits out."""
+    bf16 = x.dtype == np.uint16
+    x = _c(x, np.uint16 if bf16 else np.float32)
+    out = np.empty_like(x)
+    _lib.ref_layernorm(_p(x), int(bf16), x.shape[0], x.shape[1], eps, _p(out))
+    return out
+
+
+def ref_bcast_modulate(x, s, t, bias: float = 1.0):
+    """out = x * (s + bias) + t with s, t broadcast over rows (thinfer-core/src/ops/bcast_modulate.rs)."""
+    bf16 = x.dtype == np.uint16
+    dt = np.uint16 if bf16 else np.float32
+    x, s, t = _c(x, dt), _c(s, dt), _c(t, dt)
+    out = np.empty_like(x)
+    _lib.ref_bcast_modulate(_p(x), _p(s), _p(t), int(bf16), x.size, s.size, bias, _p(out))
+    return out
+
+
+def norm_modulate(x_bf16, scale_bf16=None, shift_bf16=None, eps: float = 1e-6, bias: float = 1.0, chain: bool = False):
+    """LayerNorm + modulate fused on bf16 rows (the two reference dispatches; chain=True keeps their bf16 rounding between)."""
+    x = _c(x_bf16, np.uint16)
+    s = None if scale_bf16 is None else _c(scale_bf16, np.uint16)
+    t = None if shift_bf16 is None else _c(shift_bf16, np.uint16)
+    out = np.empty_like(x)
+    _lib.ref_norm_modulate_bf16(_p(x), _p(s), _p(t), x.shape[0], x.shape[1], eps, bias, int(chain), _p(out))
     return out

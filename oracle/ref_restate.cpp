@@ -187,4 +187,81 @@ void ref_matmul_i8(const int8_t* a, const float* a_scale, const float* a_zero, c
         }
 }
 
+// thinfer-core/src/ops/layernorm.rs:58-82 (f32 activations) and :95-125 (packed bf16): no affine,
+// one row at a time, both sums SEQUENTIAL in f32 (mean first, then the squared deviations), then
+// (x - mean) * inverseSqrt(sum_sq / dim + eps). bf16 = 1 reads bf16 bits and rounds the result to
+// bf16 (RNE) like the packed kernel's pack_bf16x2; bf16 = 0 is the f32 kernel.
+static inline float rs_bf16_f32(uint16_t h) { uint32_t u = uint32_t(h) << 16; float f; std::memcpy(&f, &u, 4); return f; }
+static inline uint16_t rs_bf16_rne(float f) {
+    uint32_t u; std::memcpy(&u, &f, 4);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return uint16_t((u >> 16) | 0x40);
+    return uint16_t((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+void ref_layernorm(const void* x, int bf16, int64_t rows, int64_t dim, float eps, void* out) {
+    const float* xf = static_cast<const float*>(x);
+    const uint16_t* xh = static_cast<const uint16_t*>(x);
+    for (int64_t r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        for (int64_t i = 0; i < dim; ++i) sum = sum + (bf16 ? rs_bf16_f32(xh[r * dim + i]) : xf[r * dim + i]);
+        float mean = sum / float(dim);
+        float sum_sq = 0.0f;
+        for (int64_t i = 0; i < dim; ++i) {
+            float d = (bf16 ? rs_bf16_f32(xh[r * dim + i]) : xf[r * dim + i]) - mean;
+            sum_sq = sum_sq + d * d;
+        }
+        float inv = 1.0f / std::sqrt(sum_sq / float(dim) + eps);
+        for (int64_t i = 0; i < dim; ++i) {
+            float v = ((bf16 ? rs_bf16_f32(xh[r * dim + i]) : xf[r * dim + i]) - mean) * inv;
+            if (bf16) static_cast<uint16_t*>(out)[r * dim + i] = rs_bf16_rne(v);
+            else static_cast<float*>(out)[r * dim + i] = v;
+        }
+    }
+}
+
+// thinfer-core/src/ops/bcast_modulate.rs:1-3,93-102: out[i] = x[i] * (s[i % C] + bias) + t[i % C];
+// AdaLN modulation norm(x) * (1 + scale) + shift with bias = 1.
+void ref_bcast_modulate(const void* x, const void* s, const void* t, int bf16, int64_t n, int64_t c, float bias, void* out) {
+    for (int64_t i = 0; i < n; ++i) {
+        float xv, sv, tv;
+        if (bf16) {
+            xv = rs_bf16_f32(static_cast<const uint16_t*>(x)[i]);
+            sv = rs_bf16_f32(static_cast<const uint16_t*>(s)[i % c]);
+            tv = rs_bf16_f32(static_cast<const uint16_t*>(t)[i % c]);
+        } else {
+            xv = static_cast<const float*>(x)[i];
+            sv = static_cast<const float*>(s)[i % c];
+            tv = static_cast<const float*>(t)[i % c];
+        }
+        float v = xv * (sv + bias) + tv;
+        if (bf16) static_cast<uint16_t*>(out)[i] = rs_bf16_rne(v);
+        else static_cast<float*>(out)[i] = v;
+    }
+}
+
+// The fused form of the two dispatches above (what the device kernel computes): LayerNorm then
+// modulate on one row, bf16 in, bf16 out. chain = 1 rounds the LayerNorm result to bf16 before the
+// modulation, as the reference's two dispatches do; chain = 0 keeps it in f32. s == null skips the
+// modulation (out = bf16(LayerNorm(x))).
+void ref_norm_modulate_bf16(const uint16_t* x, const uint16_t* s, const uint16_t* t, int64_t rows, int64_t dim, float eps,
+                            float bias, int chain, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        for (int64_t i = 0; i < dim; ++i) sum = sum + rs_bf16_f32(x[r * dim + i]);
+        float mean = sum / float(dim);
+        float sum_sq = 0.0f;
+        for (int64_t i = 0; i < dim; ++i) {
+            float d = rs_bf16_f32(x[r * dim + i]) - mean;
+            sum_sq = sum_sq + d * d;
+        }
+        float inv = 1.0f / std::sqrt(sum_sq / float(dim) + eps);
+        for (int64_t i = 0; i < dim; ++i) {
+            float v = (rs_bf16_f32(x[r * dim + i]) - mean) * inv;
+            if (chain) v = rs_bf16_f32(rs_bf16_rne(v));
+            if (s) v = v * (rs_bf16_f32(s[i]) + bias) + rs_bf16_f32(t[i]);
+            out[r * dim + i] = rs_bf16_rne(v);
+        }
+    }
+}
+
 }  // extern "C"

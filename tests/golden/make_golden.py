@@ -4,7 +4,8 @@ checkout for part 1); the .npz files are committed so that tests never read the 
 Part 1 — reference_fixtures.npz: the cases of the reference's committed conformance
 fixtures (thinfer-conformance/fixtures/{fp32,bf16w,bf16p}.safetensors, spec in
 fixtures/spec.json) that touch the linear path: matmul_basic, bcast_add (bias),
-bcast_fma (gated residual), gelu_mul_basic (tanh-GELU gate). Copied as data, bit for bit;
+bcast_fma (gated residual), gelu_mul_basic (tanh-GELU gate), layernorm_basic and bcast_modulate
+(the two steps in front of every block linear). Copied as data, bit for bit;
 bf16 tensors are stored as uint16 bit patterns.
 
 Part 2 — nvfp4_golden.npz: small seeded NVFP4 cases produced by this repo's CPU oracle
@@ -19,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 
 REF_FIXTURES = "/root/reference/projects/thinfer-conformance/fixtures"
-CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic"]
+CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic", "layernorm_basic", "bcast_modulate"]
 
 
 def part1():

@@ -53,6 +53,47 @@ def test_gated_residual_fixture_bf16p(golden_ref):
     assert np.array_equal(got, out)
 
 
+@pytest.mark.parametrize("variant", ["fp32", "bf16w", "bf16p"])
+def test_layernorm_fixture(golden_ref, variant):
+    """layernorm_basic (eps 1e-6, thinfer-conformance/fixtures/spec.json): the restated two-pass LayerNorm."""
+    x, out = golden_ref[f"{variant}/layernorm_basic/x"], golden_ref[f"{variant}/layernorm_basic/out"]
+    got = O.ref_layernorm(x, 1e-6)
+    if variant == "bf16p":
+        g, e = O.bf16_to_f32(got), O.bf16_to_f32(out)
+        # torch's reduction order differs from the kernel's sequential sums: at most one bf16 step apart
+        assert (np.abs(g - e) <= 2.0 ** -7 * np.abs(e) + TOL).all() and (got == out).mean() >= 0.9
+    elif variant == "bf16w":  # f32 in, output narrowed through bf16
+        assert (np.abs(got - out) <= 2.0 ** -7 * np.abs(out) + TOL).all()
+    else:
+        assert np.abs(got - out).max() <= TOL
+
+
+@pytest.mark.parametrize("variant", ["fp32", "bf16w", "bf16p"])
+def test_bcast_modulate_fixture(golden_ref, variant):
+    """bcast_modulate (bias 1.0): out = x * (s + 1) + t."""
+    x, s, t, out = (golden_ref[f"{variant}/bcast_modulate/{k}"] for k in "x s t out".split())
+    got = O.ref_bcast_modulate(x, s, t, 1.0)
+    if variant == "bf16p":
+        g, e = O.bf16_to_f32(got), O.bf16_to_f32(out)
+        assert (np.abs(g - e) <= 2.0 ** -7 * np.abs(e) + TOL).all() and (got == out).mean() >= 0.9
+    elif variant == "bf16w":
+        assert (np.abs(got - out) <= 2.0 ** -7 * np.abs(out) + TOL).all()
+    else:
+        assert np.abs(got - out).max() <= TOL
+
+
+def test_norm_modulate_fused_equals_the_two_dispatches():
+    """The fused oracle routine in chain mode is the two restated dispatches back to back, bit for bit."""
+    x = O.f32_to_bf16(O.gaussian(37 * 96, 5).reshape(37, 96) * np.float32(3.0) + np.float32(0.5))
+    s = O.f32_to_bf16(O.gaussian(96, 6) * np.float32(0.3))
+    t = O.f32_to_bf16(O.gaussian(96, 7) * np.float32(0.2))
+    two = O.ref_bcast_modulate(O.ref_layernorm(x, 1e-6), s, t, 1.0)
+    assert np.array_equal(O.norm_modulate(x, s, t, 1e-6, 1.0, chain=True), two)
+    fused = O.bf16_to_f32(O.norm_modulate(x, s, t, 1e-6, 1.0, chain=False))
+    assert rel_fro(fused, O.bf16_to_f32(two)) <= 4e-3  # one bf16 rounding less
+    assert np.array_equal(O.norm_modulate(x, None, None, 1e-6), O.ref_layernorm(x, 1e-6))
+
+
 def test_gelu_fixture(golden_ref):
     a, b, out = (golden_ref[f"fp32/gelu_mul_basic/{k}"] for k in "a b out".split())
     # fixture = gelu_tanh(a) * b ; take the oracle's GELU through its epilogue (bf16 out)

@@ -35,6 +35,14 @@ class LinearArgs(C.Structure):
     ]
 
 
+class NormQuantArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_uint32), ("k", C.c_uint32), ("eps", C.c_float), ("mod_bias", C.c_float),
+        ("x_bf16", Buf), ("scale_bf16", Buf), ("shift_bf16", Buf), ("out_bf16", Buf), ("out_codes", Buf), ("out_scales", Buf),
+        ("out_global", C.c_float), ("parity_mode", C.c_uint32),
+    ]
+
+
 class StackLinear(C.Structure):
     _fields_ = [("n", C.c_uint32), ("k", C.c_uint32), ("act", C.c_uint32), ("has_bias", C.c_uint32),
                 ("input", C.c_uint32), ("stream_id", C.c_uint32)]
@@ -64,6 +72,7 @@ SIGNATURES = {
     "tnf_quantize_act": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float, C.c_int32, Buf, Buf, C.POINTER(C.c_float)]),
     "tnf_linear_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
     "tnf_linear_nvfp4_noalloc": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_norm_modulate_quantize": (C.c_int32, [_ctx, C.POINTER(NormQuantArgs)]),
     "tnf_noalloc_scratch_bytes": (C.c_uint64, []),
     "tnf_quantize_act_shared": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float]),
     "tnf_gemm_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs), Buf, Buf]),

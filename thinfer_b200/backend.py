@@ -273,6 +273,16 @@ class BatchScope:
         args.n_offset, args.ldo, args.flags = n_offset, ldo, flags
         return args
 
+    def norm_modulate_quant(self, x_bf16: Buf, m: int, k: int, out_global: float, out_codes: Buf, out_scales_device: Buf,
+                            scale: Optional[Buf] = None, shift: Optional[Buf] = None, out_bf16: Optional[Buf] = None,
+                            eps: float = 1e-6, mod_bias: float = 1.0, chain: bool = False) -> None:
+        """op_layernorm + op_modulate + act_quant of the reference's block in one launch
+        (thinfer-models/src/qwen_image/dit.rs:521-532); the NVFP4 copy feeds ``matmul``."""
+        none = Buf(0, 0, 0)
+        args = L.NormQuantArgs(m, k, eps, mod_bias, x_bf16, scale or none, shift or none, out_bf16 or none, out_codes,
+                               out_scales_device, out_global, int(chain))
+        _check(self.be.lib.tnf_norm_modulate_quantize(self.be._ctx, C.byref(args)))
+
     def linear(self, a_bf16: Optional[Buf], m: int, w: Nvfp4Weight, a_global: float, out: Optional[Buf],
                act: int = L.ACT_NONE, gate: Optional[Buf] = None, residual: Optional[Buf] = None, chain: bool = False,
                n_offset: int = 0, ldo: int = 0, flags: int = 0, bias=None, out_nvfp4=None) -> None:

@@ -63,8 +63,11 @@ __device__ __forceinline__ uint32_t quant_block16(const float (&x)[16], const fl
 // The same block from 8 packed bf16 pairs (element 2i in the low half of w[i]): the block maximum is
 // taken on the packed values (exact: a maximum of bf16 magnitudes, NaNs dropped like fmaxf drops
 // them), which halves the instructions and the live registers of the f32 form. Same bits out.
-__device__ __forceinline__ uint32_t quant_block16_bf16(const uint32_t (&w)[8], const float* inv_d_lut, float inv_t,
-                                                       uint32_t& lo, uint32_t& hi) {
+// kDirect: no table, 1/(decode(sc) * g) is computed for this one block with the table's two operations
+// (a kernel whose threads quantise a single block each gains nothing from filling a table).
+template <bool kDirect>
+__device__ __forceinline__ uint32_t quant_block16_bf16_impl(const uint32_t (&w)[8], const float* inv_d_lut, float g, float inv_t,
+                                                            uint32_t& lo, uint32_t& hi) {
   __nv_bfloat162 m2[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -83,7 +86,7 @@ __device__ __forceinline__ uint32_t quant_block16_bf16(const uint32_t (&w)[8], c
   lo = 0;
   hi = 0;
   if (sc != 0) {
-    const float inv_d = inv_d_lut[sc];
+    const float inv_d = kDirect ? __fdiv_rn(1.0f, __fmul_rn(e4m3_decode_dev(sc), g)) : inv_d_lut[sc];
     float y[16];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -94,6 +97,15 @@ __device__ __forceinline__ uint32_t quant_block16_bf16(const uint32_t (&w)[8], c
     hi = e2m1x8(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
   }
   return sc;
+}
+
+__device__ __forceinline__ uint32_t quant_block16_bf16(const uint32_t (&w)[8], const float* inv_d_lut, float inv_t,
+                                                       uint32_t& lo, uint32_t& hi) {
+  return quant_block16_bf16_impl<false>(w, inv_d_lut, 0.0f, inv_t, lo, hi);
+}
+__device__ __forceinline__ uint32_t quant_block16_bf16_direct(const uint32_t (&w)[8], float g, float inv_t, uint32_t& lo,
+                                                              uint32_t& hi) {
+  return quant_block16_bf16_impl<true>(w, nullptr, g, inv_t, lo, hi);
 }
 
 __device__ __forceinline__ uint64_t sf_device_offset(uint32_t r, uint32_t b, uint32_t k_atoms) {

@@ -112,10 +112,48 @@ def run(m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, device=0
     return res
 
 
+def run_norm_quant(m, k, iters=20, warmup=3, device=0):
+    """Times the fused LayerNorm + modulate + quantiser launch on [m, k] bf16 rows (no bf16 output)."""
+    import torch
+
+    from . import Backend
+    from .backend import device_scales_bytes
+
+    be = Backend(device)
+    sc = be.scope()
+    dev = f"cuda:{device}"
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321)
+    x = be.allocate(m * k * 2)
+    _tview(be, x, torch.bfloat16, (m, k)).copy_(torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16))
+    s, t = be.allocate(k * 2), be.allocate(k * 2)
+    _tview(be, s, torch.bfloat16, (k,)).copy_((torch.randn(k, device=dev, generator=gen) * 0.3).to(torch.bfloat16))
+    _tview(be, t, torch.bfloat16, (k,)).copy_((torch.randn(k, device=dev, generator=gen) * 0.2).to(torch.bfloat16))
+    codes, scales = be.allocate(m * k // 2), be.allocate(device_scales_bytes(m, k))
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    ts = []
+    for it in range(warmup + iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        sc.norm_modulate_quant(x, m, k, 0.002, codes, scales, scale=s, shift=t)
+        e1.record(stream)
+        be.submit(60000)
+        torch.cuda.synchronize()
+        if it >= warmup:
+            ts.append(e0.elapsed_time(e1))
+    ms = float(np.mean(ts))
+    nbytes = 2 * m * k + m * k // 2 + m * k // 16 + 4 * k
+    be.close()
+    return {"op": "norm_modulate_quant", "m": m, "k": k, "ms": ms, "ms_min": float(np.min(ts)), "min_bytes": nbytes,
+            "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, required=True)
-    ap.add_argument("--n", type=int, required=True)
+    ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, required=True)
     ap.add_argument("--act", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
@@ -123,7 +161,11 @@ def main():
     ap.add_argument("--no-quant", action="store_true")
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--out-nvfp4", action="store_true")
+    ap.add_argument("--norm-quant", action="store_true", help="time tnf_norm_modulate_quantize on [m, k] instead of a linear")
     args = ap.parse_args()
+    if args.norm_quant:
+        print(json.dumps(run_norm_quant(args.m, args.k, args.iters, args.warmup)))
+        return
     print(json.dumps(run(args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
                          out_nvfp4=args.out_nvfp4)))
 
