@@ -167,7 +167,25 @@ def cpu_sample(steps: int = 1, warmup: int = 0, workload: str = "qwen"):
     for _ in range(steps):
         one()
     dt = (time.perf_counter() - t0) / steps
+    # two more figures on the same host cores: configs[0] (256 x 3072 x 3072 with bias) alone, best of 3, and the
+    # bit-exact activation quantiser on a [4352, 3072] bf16 matrix
+    c1 = next(op for op, (name, k, n, _) in zip(ops, shapes) if (k, n) == (HIDDEN, HIDDEN)) if workload == "qwen" else None
+    c1_ms = None
+    if c1 is not None:
+        best = float("inf")
+        for _ in range(3):
+            t1 = time.perf_counter()
+            O.linear(c1[0], c1[1], c1[2], c1[3], c1[4], bias=c1[5], act=0)
+            best = min(best, time.perf_counter() - t1)
+        c1_ms = best * 1e3
+    qa = O.f32_to_bf16(O.gaussian(QWEN_M * HIDDEN, 0xA0FF).reshape(QWEN_M, HIDDEN))
+    qg = O.global_scale(O.amax_bf16(qa))
+    O.quantize_act(qa[:256], qg)
+    t1 = time.perf_counter()
+    O.quantize_act(qa, qg)
+    q_gbs = qa.nbytes * (1.0 + 0.28125) / (time.perf_counter() - t1) / 1e9
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+            "c1_256x3072x3072_ms": c1_ms, "quantiser_gbs": q_gbs,
             "sample": f"{len(shapes)} linears of one layer at {rows} rows ({flops / 1e9:.1f} GFLOP per step), "
                       f"activation quantiser + dequantise + f32 GEMM + epilogue, OpenMP over {O.num_threads()} threads",
             "ms_per_sample_step": dt * 1e3}
@@ -184,7 +202,7 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_sample_step"],
         "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "nvfp4",
         "data": "synthetic", "config": workload_config(args.gpus),
-        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample", "c1_256x3072x3072_ms", "quantiser_gbs")},
         "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no NVFP4 path and its GPU path needs a graphics API; this arm times the CPU "
                 "restatement of its dequantise-then-f32-GEMM linear on a bounded sample of the workload",

@@ -5,7 +5,7 @@
 // trip of the [rows, dim] activation: op_layernorm (thinfer-core/src/ops/layernorm.rs:95-125,
 // called at thinfer-models/src/qwen_image/dit.rs:521,757) and op_modulate = x * (1 + scale) + shift
 // (thinfer-core/src/ops/bcast_modulate.rs:93-102, dit.rs:523-532,759-768); the NVFP4 path then adds
-// the activation quantiser. Here one CTA owns one row: a thread holds one 16-element block in
+// the activation quantiser. Here a CTA works on one row at a time: a thread holds one 16-element block in
 // registers, the row statistics are two block reductions (mean first, then the squared deviations,
 // like the reference's two loops), the modulated value is rounded to bf16 exactly once (twice in
 // chain mode, which keeps the reference's rounding between its two dispatches) and quantised from
@@ -15,6 +15,8 @@
 // compared with the CPU restatement under a tolerance, the NVFP4 copy bit for bit against the
 // quantiser applied to this kernel's own bf16 output.
 #include <cuda_runtime.h>
+
+#include <algorithm>
 
 #include "context.h"
 #include "internal.h"
@@ -30,108 +32,119 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// sum over the CTA, the same value in every thread; `red` holds one float per warp
+// sum over the CTA, the same value in every thread; `red` holds one float per warp. One barrier per
+// call: the caller alternates between buffers so that a buffer is rewritten only two calls later,
+// after every thread has passed the barrier of the call in between.
 __device__ __forceinline__ float block_sum(float v, float* red, uint32_t warp, uint32_t lane, uint32_t n_warps) {
   v = warp_sum(v);
-  __syncthreads();  // the previous use of `red` is over
   if (lane == 0) red[warp] = v;
   __syncthreads();
-  float t = 0.0f;
-  for (uint32_t w = 0; w < n_warps; ++w) t += red[w];  // fixed order, broadcast reads
-  return t;
+  return warp_sum(lane < n_warps ? red[lane] : 0.0f);  // fixed tree order
 }
 
 __device__ __forceinline__ float bf16_round_f32(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// blockDim.x = nb_grid rounded up to a warp; thread t owns block t of the row (blocks past dim/16
-// are padding of the device scale layout and produce zero scale bytes).
+// blockDim.x = nb_grid rounded up to a warp; thread t owns block t of a row (blocks past dim/16
+// are padding of the device scale layout and produce zero scale bytes). The grid is persistent:
+// a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ... and loads its next row before the
+// reductions of the current one, so the load latency of a row hides under the previous row's work.
 template <bool kChain>
 __global__ void __launch_bounds__(1024, 1)
     norm_modulate_quant_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ scale,
                                const uint16_t* __restrict__ shift, float mod_bias, float eps, uint32_t rows, uint32_t dim,
                                uint32_t nb_grid, float g, float inv_t, uint16_t* __restrict__ out_bf16,
                                uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t k_atoms) {
-  __shared__ float red[32];
-  const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, n_warps = blockDim.x >> 5;
+  __shared__ float red[4][32];
+  __shared__ float inv_d_lut[128];
+  const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, n_warps = blockDim.x >> 5;
   const uint32_t nb = dim >> 4;
   const bool active = tid < nb;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // launched with programmatic dependent launch: see internal.h
-  float v[16];
-  if (active) {
-    const uint4* p4 = reinterpret_cast<const uint4*>(x + uint64_t(row) * dim + uint64_t(tid) * 16u);
-    const uint4 a = __ldg(p4), b = __ldg(p4 + 1);
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  fill_inv_scale_lut(inv_d_lut, g, tid, blockDim.x);  // once per CTA; the first block_sum barrier publishes it
+  const float inv_dim = __fdiv_rn(1.0f, float(dim));
+  uint32_t par = 0;
+  uint4 nxt[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+  auto fetch = [&](uint32_t r) {
+    if (active && r < rows) {
+      const uint4* p4 = reinterpret_cast<const uint4*>(x + uint64_t(r) * dim + uint64_t(tid) * 16u);
+      nxt[0] = __ldg(p4);
+      nxt[1] = __ldg(p4 + 1);
     }
-  } else {
+  };
+  fetch(blockIdx.x);
+  for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {  // CTA-uniform
+    const uint32_t xw[8] = {nxt[0].x, nxt[0].y, nxt[0].z, nxt[0].w, nxt[1].x, nxt[1].y, nxt[1].z, nxt[1].w};
+    fetch(row + gridDim.x);
+    float v[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = 0.0f;
-  }
-  float s = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) s += v[i];
-  const float mean = __fdiv_rn(block_sum(s, red, warp, lane, n_warps), float(dim));
-  float ss = 0.0f;
-  if (active) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float d = __fsub_rn(v[i], mean);
-      ss = __fmaf_rn(d, d, ss);
+    for (int i = 0; i < 8; ++i) {  // inactive threads hold zeros
+      v[2 * i] = active ? __uint_as_float(xw[i] << 16) : 0.0f;
+      v[2 * i + 1] = active ? __uint_as_float(xw[i] & 0xFFFF0000u) : 0.0f;
     }
-  }
-  const float var = __fdiv_rn(block_sum(ss, red, warp, lane, n_warps), float(dim));
-  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
-
-  uint32_t sc = 0;
-  if (active) {
-    uint4 s4[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, t4[2] = {s4[0], s4[0]};
-    if (scale) {
-      const uint4* sp = reinterpret_cast<const uint4*>(scale + uint64_t(tid) * 16u);
-      const uint4* tp = reinterpret_cast<const uint4*>(shift + uint64_t(tid) * 16u);
-      s4[0] = __ldg(sp);
-      s4[1] = __ldg(sp + 1);
-      t4[0] = __ldg(tp);
-      t4[1] = __ldg(tp + 1);
-    }
-    const uint32_t sw[8] = {s4[0].x, s4[0].y, s4[0].z, s4[0].w, s4[1].x, s4[1].y, s4[1].z, s4[1].w};
-    const uint32_t tw[8] = {t4[0].x, t4[0].y, t4[0].z, t4[0].w, t4[1].x, t4[1].y, t4[1].z, t4[1].w};
-    uint32_t w[8];
+    float s = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float y[2];
+    for (int i = 0; i < 16; ++i) s += v[i];
+    const float mean = block_sum(s, red[par], warp, lane, n_warps) * inv_dim;
+    float ss = 0.0f;
+    if (active) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float n = __fmul_rn(__fsub_rn(v[2 * i + e], mean), inv);
-        if (kChain) n = bf16_round_f32(n);
-        if (scale) {
-          const float sv = __uint_as_float(e ? (sw[i] & 0xFFFF0000u) : (sw[i] << 16));
-          const float tv = __uint_as_float(e ? (tw[i] & 0xFFFF0000u) : (tw[i] << 16));
-          n = __fadd_rn(__fmul_rn(n, __fadd_rn(sv, mod_bias)), tv);  // x * (s + bias) + t, separately rounded
-        }
-        y[e] = n;
+      for (int i = 0; i < 16; ++i) {
+        const float d = __fsub_rn(v[i], mean);
+        ss = __fmaf_rn(d, d, ss);
       }
-      const __nv_bfloat162 pk = __floats2bfloat162_rn(y[0], y[1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&pk);
     }
-    if (out_bf16) {
-      uint4* o4 = reinterpret_cast<uint4*>(out_bf16 + uint64_t(row) * dim + uint64_t(tid) * 16u);
-      o4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      o4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    const float var = block_sum(ss, red[par + 1], warp, lane, n_warps) * inv_dim;
+    const float inv = __frsqrt_rn(var + eps);
+    par ^= 2u;
+
+    uint32_t sc = 0;
+    if (active) {
+      uint4 s4[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, t4[2] = {s4[0], s4[0]};
+      if (scale) {  // 64 bytes per thread, the same for every row: L1 hits after the first
+        const uint4* sp = reinterpret_cast<const uint4*>(scale + uint64_t(tid) * 16u);
+        const uint4* tp = reinterpret_cast<const uint4*>(shift + uint64_t(tid) * 16u);
+        s4[0] = __ldg(sp);
+        s4[1] = __ldg(sp + 1);
+        t4[0] = __ldg(tp);
+        t4[1] = __ldg(tp + 1);
+      }
+      const uint32_t sw[8] = {s4[0].x, s4[0].y, s4[0].z, s4[0].w, s4[1].x, s4[1].y, s4[1].z, s4[1].w};
+      const uint32_t tw[8] = {t4[0].x, t4[0].y, t4[0].z, t4[0].w, t4[1].x, t4[1].y, t4[1].z, t4[1].w};
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float y[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float n = __fmul_rn(__fsub_rn(v[2 * i + e], mean), inv);
+          if (kChain) n = bf16_round_f32(n);
+          if (scale) {
+            const float sv = __uint_as_float(e ? (sw[i] & 0xFFFF0000u) : (sw[i] << 16));
+            const float tv = __uint_as_float(e ? (tw[i] & 0xFFFF0000u) : (tw[i] << 16));
+            n = __fadd_rn(__fmul_rn(n, __fadd_rn(sv, mod_bias)), tv);  // x * (s + bias) + t, separately rounded
+          }
+          y[e] = n;
+        }
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(y[0], y[1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      if (out_bf16) {
+        uint4* o4 = reinterpret_cast<uint4*>(out_bf16 + uint64_t(row) * dim + uint64_t(tid) * 16u);
+        o4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        o4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      uint32_t lo, hi;
+      sc = quant_block16_bf16(w, inv_d_lut, inv_t, lo, hi);
+      *reinterpret_cast<uint2*>(codes + uint64_t(row) * (dim >> 1) + uint64_t(tid) * 8u) = make_uint2(lo, hi);
     }
-    uint32_t lo, hi;
-    sc = quant_block16_bf16_direct(w, g, inv_t, lo, hi);
-    *reinterpret_cast<uint2*>(codes + uint64_t(row) * (dim >> 1) + uint64_t(tid) * 8u) = make_uint2(lo, hi);
-  }
-  if (tid < nb_grid) {  // nb_grid is a multiple of 4: whole quads of lanes get here together
-    uint32_t wv = sc << (8u * (tid & 3u));
-    const uint32_t quad = 0xFu << (lane & ~3u);
-    wv |= __shfl_xor_sync(quad, wv, 1);
-    wv |= __shfl_xor_sync(quad, wv, 2);
-    if ((tid & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(row, tid, k_atoms)) = wv;
+    if (tid < nb_grid) {  // nb_grid is a multiple of 4: whole quads of lanes get here together
+      uint32_t wv = sc << (8u * (tid & 3u));
+      const uint32_t quad = 0xFu << (lane & ~3u);
+      wv |= __shfl_xor_sync(quad, wv, 1);
+      wv |= __shfl_xor_sync(quad, wv, 2);
+      if ((tid & 3u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_device_offset(row, tid, k_atoms)) = wv;
+    }
   }
 }
 
@@ -189,9 +202,12 @@ extern "C" int32_t tnf_norm_modulate_quantize(tnf_ctx* ctx, const tnf_norm_quant
     if (e != cudaSuccess) return cuda_fail(e, "out_scales clear");
   }
   const uint32_t threads = (nb_grid + 31u) & ~31u;
+  // persistent grid: as many CTAs as stay resident (about 1024 threads per SM at this kernel's register count)
+  const uint32_t per_sm = std::max(1u, 1024u / threads);
+  const uint32_t blocks = std::min<uint64_t>(a->m, uint64_t(ctx->sm_count) * per_sm);
   const float inv_t = 1.0f / (6.0f * a->out_global);  // same f32 operations as the quantiser and the oracle
   auto launch = [&](auto kernel) {
-    return launch_pdl(kernel, dim3(a->m), dim3(threads), 0, ctx->compute, reinterpret_cast<const uint16_t*>(x),
+    return launch_pdl(kernel, dim3(blocks), dim3(threads), 0, ctx->compute, reinterpret_cast<const uint16_t*>(x),
                       reinterpret_cast<const uint16_t*>(sc), reinterpret_cast<const uint16_t*>(sh), a->mod_bias, a->eps, a->m,
                       a->k, nb_grid, a->out_global, inv_t, reinterpret_cast<uint16_t*>(out), codes, scales, k_atoms);
   };
