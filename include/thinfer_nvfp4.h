@@ -212,6 +212,13 @@ int32_t tnf_stream_upload(tnf_ctx* ctx, uint64_t host_id, uint64_t host_off, uin
                           uint64_t dst_off, uint64_t n, uint64_t* event);
 /* Compute stream waits for an upload event; the host does not block. */
 int32_t tnf_wait_event(tnf_ctx* ctx, uint64_t event);
+/* Asynchronous read-back into a pinned arena (the reference's read_buffer is awaited, not blocking:
+ * thinfer-core/src/backend/mod.rs:180-185): once the work queued so far on the compute stream is
+ * done, the copy stream copies src -> host; *event identifies completion. tnf_event_sync blocks
+ * the HOST on an event (and retires it); tnf_wait_event makes the compute stream wait for it. */
+int32_t tnf_stream_download(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uint64_t host_id, uint64_t host_off,
+                            uint64_t n, uint64_t* event);
+int32_t tnf_event_sync(tnf_ctx* ctx, uint64_t event);
 /* Copy stream waits until everything launched so far on the compute stream is done
  * (a ring slot may be overwritten only after its last reader). */
 int32_t tnf_copy_after_compute(tnf_ctx* ctx);

@@ -111,3 +111,33 @@ def test_stack_budget_below_ring_reserve_is_refused(backend):
         st.build(weight_budget=1024, ring_slots=2)
     assert backend.mem_snapshot()["live_weights"] == before  # nothing was allocated
     st.close()
+
+
+@pytest.mark.gpu
+def test_stream_upload_download_round_trip(backend):
+    """Pinned arena -> device on the copy stream, a compute-stream copy in between, device -> pinned arena
+    with tnf_stream_download; tnf_event_sync makes the host wait for exactly that read-back."""
+    import ctypes as C
+
+    from thinfer_b200.backend import UnknownBuffer, _check
+    from thinfer_b200.residency import HostArena
+
+    be = backend
+    n = 1 << 20
+    src, dst = HostArena(be, n), HostArena(be, n)
+    src.np[:] = (np.arange(n, dtype=np.uint32) * 2654435761 >> 24).astype(np.uint8)
+    dst.np[:] = 0
+    a, b = be.allocate(n), be.allocate(n)
+    ev = C.c_uint64()
+    _check(be.lib.tnf_stream_upload(be._ctx, src.id, 0, a.id, 0, n, C.byref(ev)))
+    _check(be.lib.tnf_wait_event(be._ctx, ev.value))
+    _check(be.lib.tnf_copy(be._ctx, a.id, 0, b.id, 0, n))
+    _check(be.lib.tnf_stream_download(be._ctx, b.id, 4096, dst.id, 4096, n - 4096, C.byref(ev)))
+    _check(be.lib.tnf_event_sync(be._ctx, ev.value))
+    assert np.array_equal(dst.np[4096:], src.np[4096:]) and not dst.np[:4096].any()
+    with pytest.raises(UnknownBuffer):
+        _check(be.lib.tnf_event_sync(be._ctx, ev.value))  # an event is retired by its first wait
+    be.free(a)
+    be.free(b)
+    src.release()
+    dst.release()

@@ -81,6 +81,8 @@ SIGNATURES = {
     "tnf_host_release": (C.c_int32, [_ctx, C.c_uint64]),
     "tnf_stream_upload": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _u64p]),
     "tnf_wait_event": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_stream_download": (C.c_int32, [_ctx, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _u64p]),
+    "tnf_event_sync": (C.c_int32, [_ctx, C.c_uint64]),
     "tnf_copy_after_compute": (C.c_int32, [_ctx]),
     "tnf_stack_record_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
     "tnf_stack_create": (C.c_int32, [_ctx, C.c_uint32, C.c_uint32, C.POINTER(StackLinear), C.c_uint32, _u32p,

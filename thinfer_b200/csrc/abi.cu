@@ -799,6 +799,75 @@ int32_t tnf_wait_event(tnf_ctx* ctx, uint64_t event) {
   return TNF_OK;
 }
 
+int32_t tnf_stream_download(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uint64_t host_id, uint64_t host_off,
+                            uint64_t n, uint64_t* event) {
+  TNF_CHECK_CTX(ctx);
+  uint8_t* d = nullptr;
+  int32_t st = raw_range(ctx, src_id, src_off, n, "tnf_stream_download src", &d);
+  if (st != TNF_OK) return st;
+  uint8_t* h = nullptr;
+  cudaEvent_t order = nullptr, done = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->hosts.find(host_id);
+    if (it == ctx->hosts.end()) {
+      set_error("tnf_stream_download: unknown host arena %llu", (unsigned long long)host_id);
+      return TNF_ERR_UNKNOWN_BUFFER;
+    }
+    if (host_off > it->second.bytes || n > it->second.bytes - host_off) {
+      set_error("tnf_stream_download: host range [%llu, +%llu) outside arena of %llu bytes",
+                (unsigned long long)host_off, (unsigned long long)n, (unsigned long long)it->second.bytes);
+      return TNF_ERR_INVALID_ARGUMENT;
+    }
+    h = static_cast<uint8_t*>(it->second.ptr) + host_off;
+    for (cudaEvent_t* e : {&order, &done}) {
+      if (!ctx->event_pool.empty()) {
+        *e = ctx->event_pool.back();
+        ctx->event_pool.pop_back();
+      }
+    }
+  }
+  if (!order) TNF_CUDA(cudaEventCreateWithFlags(&order, cudaEventDisableTiming), "cudaEventCreate");
+  if (!done) TNF_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate");
+  // the copy starts when everything launched so far on the compute stream (the producer of src) is done
+  TNF_CUDA(cudaEventRecord(order, ctx->compute), "cudaEventRecord");
+  TNF_CUDA(cudaStreamWaitEvent(ctx->copy, order, 0), "cudaStreamWaitEvent");
+  if (n) TNF_CUDA(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, ctx->copy), "tnf_stream_download copy");
+  TNF_CUDA(cudaEventRecord(done, ctx->copy), "cudaEventRecord");
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  ctx->event_pool.push_back(order);
+  if (event) {
+    uint64_t id = ctx->next_id++;
+    ctx->events[id] = done;
+    *event = id;
+  } else {
+    ctx->event_pool.push_back(done);
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_event_sync(tnf_ctx* ctx, uint64_t event) {
+  TNF_CHECK_CTX(ctx);
+  cudaEvent_t ev;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    auto it = ctx->events.find(event);
+    if (it == ctx->events.end()) {
+      set_error("tnf_event_sync: unknown event %llu", (unsigned long long)event);
+      return TNF_ERR_UNKNOWN_BUFFER;
+    }
+    ev = it->second;
+    ctx->events.erase(it);
+  }
+  cudaError_t e = cudaEventSynchronize(ev);
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->event_pool.push_back(ev);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventSynchronize");
+  return TNF_OK;
+}
+
 int32_t tnf_copy_after_compute(tnf_ctx* ctx) {
   TNF_CHECK_CTX(ctx);
   cudaEvent_t ev = nullptr;
