@@ -265,6 +265,37 @@ int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* aux
 int32_t tnf_stack_stats(tnf_stack* st, uint64_t out[6]);
 int32_t tnf_stack_destroy(tnf_stack* st);
 
+/* ---- container: GGUF-v3 header parser + tensor catalog ------------------------------- */
+
+/* parse_header / catalog_from of the reference (thinfer-core/src/format/gguf.rs:122-250), host
+ * only. tnf_gguf_parse reads a header from the first `len` bytes of a file: TNF_OK and a handle,
+ * or TNF_GGUF_NEED_MORE with *need_at = the absolute offset it had to reach (read at least that
+ * many bytes and call again: no whole-file load), or TNF_ERR_INVALID_ARGUMENT with the reference's
+ * error variant in tnf_last_error() ("BadMagic(0x..)", "UnsupportedVersion(2)", "Oversized {..}",
+ * "BadValueType(..)", "BadBool(..)", "BadUtf8", "BadAlignment(..)", "AlignmentTooLarge(..)",
+ * "BadDimCount(..)"). tnf_gguf_info: out = {version, alignment, tensor-data offset, tensor count}.
+ * tnf_gguf_tensor: catalog entry `index` (header order): dims OUTER-first (GGUF stores them
+ * innermost-first), absolute file offset, size = distance to the next tensor in offset order
+ * (the last one is bounded by file_size, or by its type's own size when file_size is 0). */
+typedef struct tnf_gguf tnf_gguf;
+#define TNF_GGUF_NEED_MORE 1
+/* Added to ggml's type table: one linear as the streaming residency consumes it
+ * (tnf_stack_record_offsets), GGUF dims [K, N]. "NVF4" in ASCII. */
+#define TNF_GGML_TYPE_NVFP4_RECORD 0x4E564634u
+typedef struct {
+  const char* name; /* owned by the handle */
+  uint32_t n_dims;
+  uint64_t dims[8];
+  uint32_t ggml_type;
+  uint64_t offset, size;
+  uint64_t on_disk_bytes; /* from dims and type; 0 for a type this build does not size */
+} tnf_gguf_tensor_info;
+int32_t tnf_gguf_parse(const void* buf, uint64_t len, tnf_gguf** out, uint64_t* need_at);
+int32_t tnf_gguf_free(tnf_gguf* h);
+int32_t tnf_gguf_info(const tnf_gguf* h, uint64_t out[4]);
+int32_t tnf_gguf_tensor(const tnf_gguf* h, uint64_t index, uint64_t file_size, tnf_gguf_tensor_info* out);
+const char* tnf_ggml_type_label(uint32_t ggml_type);
+
 /* ---- multi-GPU (no reference counterpart: the reference is single-device) ------------ */
 
 /* Join an NCCL communicator of `world` ranks. unique_id is the 128-byte ncclUniqueId

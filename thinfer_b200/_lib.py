@@ -43,6 +43,15 @@ class NormQuantArgs(C.Structure):
     ]
 
 
+class GgufTensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 8), ("ggml_type", C.c_uint32),
+                ("offset", C.c_uint64), ("size", C.c_uint64), ("on_disk_bytes", C.c_uint64)]
+
+
+GGUF_NEED_MORE = 1
+GGML_TYPE_NVFP4_RECORD = 0x4E564634
+
+
 class StackLinear(C.Structure):
     _fields_ = [("n", C.c_uint32), ("k", C.c_uint32), ("act", C.c_uint32), ("has_bias", C.c_uint32),
                 ("input", C.c_uint32), ("stream_id", C.c_uint32)]
@@ -91,6 +100,11 @@ SIGNATURES = {
     "tnf_stack_step": (C.c_int32, [C.c_void_p, _u64p, _u64p, _u64p, C.c_float]),
     "tnf_stack_stats": (C.c_int32, [C.c_void_p, _u64p]),
     "tnf_stack_destroy": (C.c_int32, [C.c_void_p]),
+    "tnf_gguf_parse": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p), _u64p]),
+    "tnf_gguf_free": (C.c_int32, [C.c_void_p]),
+    "tnf_gguf_info": (C.c_int32, [C.c_void_p, _u64p]),
+    "tnf_gguf_tensor": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(GgufTensorInfo)]),
+    "tnf_ggml_type_label": (C.c_char_p, [C.c_uint32]),
     "tnf_comm_unique_id": (C.c_int32, [C.c_void_p]),
     "tnf_comm_init": (C.c_int32, [_ctx, C.c_int32, C.c_int32, C.c_void_p]),
     "tnf_all_gather_cols": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
