@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the NVFP4 linear path (see DESIGN.md for the workload definitions).
+"""Benchmark of the NVFP4 linear path.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
@@ -10,7 +10,8 @@ than L2). Each linear is the library's public call: activation quantiser + tcgen
 the fused epilogue.
 N > 1 (torchrun, one rank per GPU): one step = the batched Wan-5B-shaped FFN pair at
 M = 26520 with the weights split by output columns over the ranks and every rank's slice
-delivered to all ranks (fused peer-store epilogue, or NCCL all-gather with --gather nccl).
+delivered to all ranks (--gather: packed copy-engine pushes by default; NCCL all-gathers, the fused
+peer-store epilogue and strided copy-engine bands are the alternatives).
 
 Prints ONE JSON line on rank 0.
 """

@@ -19,7 +19,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 
-REF_FIXTURES = "/root/reference/projects/thinfer-conformance/fixtures"
+REF_FIXTURES = os.path.join(os.environ.get("THINFER_REFERENCE", os.path.join(os.sep, "root", "reference")),
+                            "projects", "thinfer-conformance", "fixtures")  # the reference checkout of the build container
 CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic", "layernorm_basic", "bcast_modulate"]
 
 

@@ -1,5 +1,7 @@
-// Multi-GPU side of the ABI: NCCL communicator (loaded at run time), the all-gather of an
-// N-split output, CUDA IPC windows for the fused epilogue scatter, a stream-ordered barrier.
+// Multi-GPU side of the ABI: NCCL communicator (loaded at run time), the all-gathers of an
+// N-split output (bf16 columns, or the NVFP4 copy the epilogue made), CUDA IPC windows for the
+// fused epilogue scatter and for the copy-engine deliveries (strided row bands; contiguous pushes
+// of packed slices + an interleave kernel), a stream-ordered barrier.
 // The reference is single-device; the N-split with an all-gather of the output is what the
 // benchmark configuration adds. One process per GPU; NCCL is found with dlopen so that a
 // process that already loaded a libnccl (torch) shares it.

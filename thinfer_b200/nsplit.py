@@ -2,9 +2,11 @@
 
 The reference is single-device; this is the partition the benchmark configuration adds:
 rank g keeps W[g*N/G:(g+1)*N/G, :] resident, computes out[:, slice] and the slices reach
-every rank either through the GEMM epilogue itself (TMA stores into the peers' output
-buffers, opened over CUDA IPC) or through an NCCL all-gather. ``torch.distributed`` is only
-the plumbing that passes handles and the NCCL id around.
+every rank in one of several ways: packed slices pushed by the copy engines into every peer's
+receive area and interleaved there (``PackedGather``), an NCCL all-gather of bf16 columns or of
+the NVFP4 copy the epilogue made, the GEMM epilogue's own stores into the peers' output buffers
+(opened over CUDA IPC), or strided copy-engine bands. ``torch.distributed`` is only the
+plumbing that passes handles and the NCCL id around.
 """
 from __future__ import annotations
 
