@@ -148,6 +148,11 @@ def cpu_sample(steps: int = 1, warmup: int = 0, workload: str = "qwen"):
     import oracle as O
 
     rows = 256
+    # all host cores this process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
+    try:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        O.set_num_threads(os.cpu_count() or 1)
     shapes = QWEN_LINEARS if workload == "qwen" else [("up", HIDDEN, WAN_FFN, 1), ("down", WAN_FFN, HIDDEN, 0)]
     ops = []
     for i, (name, k, n, act) in enumerate(shapes):
@@ -399,32 +404,8 @@ def run_single_gpu(args):
     x_stage = [be.allocate(nbytes) for _ in range(2)]
     out_stage = [be.allocate(nbytes) for _ in range(2)]
     final = xs[layers % 2]
-    lib, ctx = be.lib, be._ctx
-
     def e2e_run(n_steps):
-        up_ev, down_ev = [None, None], [None, None]
-        ev = C.c_uint64()
-        _check(lib.tnf_stream_upload(ctx, host_in[0]["id"], 0, x_stage[0].id, 0, nbytes, C.byref(ev)))
-        up_ev[0] = ev.value
-        for i in range(n_steps):
-            s = i % 2
-            _check(lib.tnf_wait_event(ctx, up_ev[s]))                       # compute waits for this step's input
-            _check(lib.tnf_copy(ctx, x_stage[s].id, 0, xs[0].id, 0, nbytes))
-            if i + 1 < n_steps:                                             # next input: the copy stream first waits for
-                _check(lib.tnf_copy_after_compute(ctx))                     # the copy that last read that staging buffer
-                ev = C.c_uint64()
-                _check(lib.tnf_stream_upload(ctx, host_in[1 - s]["id"], 0, x_stage[1 - s].id, 0, nbytes, C.byref(ev)))
-                up_ev[1 - s] = ev.value
-            step()
-            if down_ev[s] is not None:                                      # this output buffer's previous download is over
-                _check(lib.tnf_wait_event(ctx, down_ev[s]))
-            _check(lib.tnf_copy(ctx, final.id, 0, out_stage[s].id, 0, nbytes))
-            ev = C.c_uint64()
-            _check(lib.tnf_stream_download(ctx, out_stage[s].id, 0, host_out[s]["id"], 0, nbytes, C.byref(ev)))
-            down_ev[s] = ev.value
-        for e in down_ev:
-            if e is not None:
-                _check(lib.tnf_event_sync(ctx, e))                          # the host holds every result
+        e2e_pipelined(be, step, xs[0], final, nbytes, nbytes, host_in, host_out, x_stage, out_stage, n_steps)
 
     e2e_run(2)
     be.submit()
@@ -460,6 +441,38 @@ def run_single_gpu(args):
     }
     print(json.dumps(line))
     be.close()
+
+
+def e2e_pipelined(be, step, x_buf, out_buf, in_bytes, out_bytes, host_in, host_out, x_stage, out_stage, n_steps):
+    """`n_steps` steps, each with its input from pinned host memory and its result back to pinned host memory.
+    Serving-style double buffering: while step i computes, the copy stream uploads the input of step i+1 into the
+    other staging buffer and downloads the result of step i-1. Returns when the host holds every result."""
+    from thinfer_b200.backend import _check
+
+    lib, ctx = be.lib, be._ctx
+    up_ev, down_ev = [None, None], [None, None]
+    ev = C.c_uint64()
+    _check(lib.tnf_stream_upload(ctx, host_in[0]["id"], 0, x_stage[0].id, 0, in_bytes, C.byref(ev)))
+    up_ev[0] = ev.value
+    for i in range(n_steps):
+        s = i % 2
+        _check(lib.tnf_wait_event(ctx, up_ev[s]))                       # compute waits for this step's input
+        _check(lib.tnf_copy(ctx, x_stage[s].id, 0, x_buf.id, 0, in_bytes))
+        if i + 1 < n_steps:                                             # next input: the copy stream first waits for
+            _check(lib.tnf_copy_after_compute(ctx))                     # the copy that last read that staging buffer
+            ev = C.c_uint64()
+            _check(lib.tnf_stream_upload(ctx, host_in[1 - s]["id"], 0, x_stage[1 - s].id, 0, in_bytes, C.byref(ev)))
+            up_ev[1 - s] = ev.value
+        step()
+        if down_ev[s] is not None:                                      # this output buffer's previous download is over
+            _check(lib.tnf_wait_event(ctx, down_ev[s]))
+        _check(lib.tnf_copy(ctx, out_buf.id, 0, out_stage[s].id, 0, out_bytes))
+        ev = C.c_uint64()
+        _check(lib.tnf_stream_download(ctx, out_stage[s].id, 0, host_out[s]["id"], 0, out_bytes, C.byref(ev)))
+        down_ev[s] = ev.value
+    for e in down_ev:
+        if e is not None:
+            _check(lib.tnf_event_sync(ctx, e))                          # the host holds every result
 
 
 def _calibrate(be, sc, src, m, k):

@@ -214,7 +214,8 @@ int32_t tnf_stream_upload(tnf_ctx* ctx, uint64_t host_id, uint64_t host_off, uin
 int32_t tnf_wait_event(tnf_ctx* ctx, uint64_t event);
 /* Asynchronous read-back into a pinned arena (the reference's read_buffer is awaited, not blocking:
  * thinfer-core/src/backend/mod.rs:180-185): once the work queued so far on the compute stream is
- * done, the copy stream copies src -> host; *event identifies completion. tnf_event_sync blocks
+ * done, a read-back stream (separate from the upload stream: the link is full duplex) copies
+ * src -> host; *event identifies completion. tnf_event_sync blocks
  * the HOST on an event (and retires it); tnf_wait_event makes the compute stream wait for it. */
 int32_t tnf_stream_download(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uint64_t host_id, uint64_t host_off,
                             uint64_t n, uint64_t* event);
@@ -332,16 +333,19 @@ int32_t tnf_scatter_rows(tnf_ctx* ctx, int32_t set, tnf_buf out_bf16, uint32_t r
  * copy stream copies src to byte dst_offset of every window of `set` (each peer's receive area,
  * which the caller sized; ring order, so every rank receives from one sender at a time) and to
  * self_dst, this rank's slot of its own receive area (len 0 to skip). Contiguous peer copies run
- * at link rate where the strided ones of tnf_scatter_rows do not. Then tnf_compute_after_copy,
- * tnf_comm_barrier, and tnf_interleave_cols to lay the slices side by side. */
+ * at link rate where the strided ones of tnf_scatter_rows do not. The pushes run on streams of
+ * their own (not behind uploads or read-backs queued on the copy stream). Then
+ * tnf_compute_after_push (the compute stream waits for the pushes queued so far, and only for
+ * them), tnf_comm_barrier, and tnf_interleave_cols to lay the slices side by side. */
 int32_t tnf_push_peers(tnf_ctx* ctx, int32_t set, tnf_buf src, uint64_t dst_offset, tnf_buf self_dst);
+int32_t tnf_compute_after_push(tnf_ctx* ctx);
 /* out[r*out_row_bytes + w*local_row_bytes + c] = gathered[w*rank_stride + r*src_row_bytes + c] for
  * w < world, r < rows, c < local_row_bytes: the receive area's per-rank blocks become the column
  * slices of one row-major matrix (bf16 rows, NVFP4 code rows, or 128-row blocks of device-layout
  * scales, whose rows may carry padding atoms). All byte counts are multiples of 16. */
 int32_t tnf_interleave_cols(tnf_ctx* ctx, tnf_buf gathered, uint64_t rank_stride, uint32_t src_row_bytes, uint32_t world,
                             tnf_buf out, uint32_t out_row_bytes, uint32_t rows, uint32_t local_row_bytes);
-/* Compute stream waits for everything queued so far on the copy stream. */
+/* Compute stream waits for everything queued so far on the copy stream and for the pushes. */
 int32_t tnf_compute_after_copy(tnf_ctx* ctx);
 /* Stream-ordered barrier across the communicator (after a scatter epilogue). */
 int32_t tnf_comm_barrier(tnf_ctx* ctx);

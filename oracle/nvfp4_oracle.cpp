@@ -137,6 +137,15 @@ int orc_num_threads() {
 #endif
 }
 
+// A launcher may have pinned OMP_NUM_THREADS to 1 for its workers; the timed CPU leg sets the count itself.
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 uint16_t orc_bf16_rne(float x) { return bf16_rne(x); }
 float orc_bf16_to_f32(uint16_t h) { return bf16_f32(h); }
 uint8_t orc_e4m3_encode(float x) { return e4m3_encode(x); }

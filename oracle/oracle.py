@@ -28,6 +28,7 @@ def _load():
     i64, f32, vp = C.c_int64, C.c_float, C.c_void_p
     sig = {
         "orc_num_threads": (C.c_int, []),
+        "orc_set_num_threads": (None, [C.c_int]),
         "orc_bf16_rne": (C.c_uint16, [f32]),
         "orc_e4m3_encode": (C.c_uint8, [f32]),
         "orc_e4m3_decode": (f32, [C.c_uint8]),
@@ -80,6 +81,11 @@ def _c(a, dt):
 
 def num_threads() -> int:
     return int(_lib.orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following calls (torchrun exports OMP_NUM_THREADS=1 to its workers)."""
+    _lib.orc_set_num_threads(int(n))
 
 
 # ---- scalar conversions -------------------------------------------------------------

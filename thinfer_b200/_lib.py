@@ -115,6 +115,7 @@ SIGNATURES = {
     "tnf_push_peers": (C.c_int32, [_ctx, C.c_int32, Buf, C.c_uint64, Buf]),
     "tnf_interleave_cols": (C.c_int32, [_ctx, Buf, C.c_uint64, C.c_uint32, C.c_uint32, Buf, C.c_uint32, C.c_uint32, C.c_uint32]),
     "tnf_compute_after_copy": (C.c_int32, [_ctx]),
+    "tnf_compute_after_push": (C.c_int32, [_ctx]),
     "tnf_comm_barrier": (C.c_int32, [_ctx]),
 }
 

@@ -351,6 +351,7 @@ int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out) {
   ctx->budget = vram_budget_bytes;
   TNF_CUDA(cudaStreamCreateWithFlags(&ctx->compute, cudaStreamNonBlocking), "cudaStreamCreate");
   TNF_CUDA(cudaStreamCreateWithFlags(&ctx->copy, cudaStreamNonBlocking), "cudaStreamCreate");
+  TNF_CUDA(cudaStreamCreateWithFlags(&ctx->readback, cudaStreamNonBlocking), "cudaStreamCreate");
   TNF_CUDA(cudaMalloc(&ctx->dwords, 256 + 16384), "cudaMalloc(status words)");
   TNF_CUDA(cudaMemset(ctx->dwords, 0, 256 + 16384), "cudaMemset(status words)");
   *out = ctx;
@@ -372,6 +373,7 @@ int32_t tnf_destroy(tnf_ctx* ctx) {
   cudaFree(ctx->dwords);
   cudaStreamDestroy(ctx->compute);
   cudaStreamDestroy(ctx->copy);
+  cudaStreamDestroy(ctx->readback);
   for (int i = 0; i < 8; ++i) {
     if (ctx->push[i]) cudaStreamDestroy(ctx->push[i]);
     if (ctx->push_done[i]) cudaEventDestroy(ctx->push_done[i]);
@@ -475,9 +477,13 @@ int32_t tnf_streams(tnf_ctx* ctx, void** compute_stream, void** copy_stream) {
 
 int32_t tnf_sync(tnf_ctx* ctx, uint32_t timeout_ms) {
   TNF_CHECK_CTX(ctx);
-  cudaStream_t streams[2] = {ctx->compute, ctx->copy};
+  cudaStream_t streams[11] = {ctx->compute, ctx->copy, ctx->readback};
+  int n_streams = 3;
+  for (int i = 0; i < 8; ++i)
+    if (ctx->push[i]) streams[n_streams++] = ctx->push[i];
   auto t0 = std::chrono::steady_clock::now();
-  for (cudaStream_t s : streams) {
+  for (int si = 0; si < n_streams; ++si) {
+    cudaStream_t s = streams[si];
     if (timeout_ms == 0) {
       TNF_CUDA(cudaStreamSynchronize(s), "tnf_sync");
     } else {
@@ -723,6 +729,7 @@ int32_t tnf_host_ptr(tnf_ctx* ctx, uint64_t host_id, void** ptr, uint64_t* bytes
 int32_t tnf_host_release(tnf_ctx* ctx, uint64_t host_id) {
   TNF_CHECK_CTX(ctx);
   TNF_CUDA(cudaStreamSynchronize(ctx->copy), "tnf_host_release sync");
+  TNF_CUDA(cudaStreamSynchronize(ctx->readback), "tnf_host_release sync");
   std::lock_guard<std::mutex> lk(ctx->mu);
   auto it = ctx->hosts.find(host_id);
   if (it == ctx->hosts.end()) {
@@ -831,9 +838,9 @@ int32_t tnf_stream_download(tnf_ctx* ctx, uint64_t src_id, uint64_t src_off, uin
   if (!done) TNF_CUDA(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate");
   // the copy starts when everything launched so far on the compute stream (the producer of src) is done
   TNF_CUDA(cudaEventRecord(order, ctx->compute), "cudaEventRecord");
-  TNF_CUDA(cudaStreamWaitEvent(ctx->copy, order, 0), "cudaStreamWaitEvent");
-  if (n) TNF_CUDA(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, ctx->copy), "tnf_stream_download copy");
-  TNF_CUDA(cudaEventRecord(done, ctx->copy), "cudaEventRecord");
+  TNF_CUDA(cudaStreamWaitEvent(ctx->readback, order, 0), "cudaStreamWaitEvent");
+  if (n) TNF_CUDA(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, ctx->readback), "tnf_stream_download copy");
+  TNF_CUDA(cudaEventRecord(done, ctx->readback), "cudaEventRecord");
   std::lock_guard<std::mutex> lk(ctx->mu);
   ctx->event_pool.push_back(order);
   if (event) {

@@ -380,10 +380,28 @@ int32_t tnf_push_peers(tnf_ctx* ctx, int32_t set, tnf_buf src, uint64_t dst_offs
     e = cudaMemcpyAsync(own, from, src.len, cudaMemcpyDeviceToDevice, ctx->push[np % lanes]);
     if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: own copy");
   }
+  // the pushes stay on their own streams (host uploads and read-backs queued on the copy stream neither wait for
+  // them nor delay them); tnf_compute_after_push / tnf_compute_after_copy / tnf_sync join them
   for (int i = 0; i < lanes; ++i) {
     e = cudaEventRecord(ctx->push_done[i], ctx->push[i]);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy, ctx->push_done[i], 0);
-    if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: join");
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_push_peers: record");
+    ctx->push_pending[i] = true;
+  }
+  return TNF_OK;
+}
+
+int32_t tnf_compute_after_push(tnf_ctx* ctx) {
+  if (!ctx) {
+    set_error("null context");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  for (int i = 0; i < 8; ++i) {
+    if (!ctx->push_pending[i]) continue;
+    e = cudaStreamWaitEvent(ctx->compute, ctx->push_done[i], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "tnf_compute_after_push");
+    ctx->push_pending[i] = false;
   }
   return TNF_OK;
 }
@@ -427,6 +445,8 @@ int32_t tnf_compute_after_copy(tnf_ctx* ctx) {
   }
   cudaError_t e = cudaSetDevice(ctx->device);
   if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  int32_t st = tnf_compute_after_push(ctx);  // the copy-engine work of tnf_push_peers counts too
+  if (st != TNF_OK) return st;
   cudaEvent_t ev = nullptr;
   {
     std::lock_guard<std::mutex> lk(ctx->mu);

@@ -31,8 +31,10 @@ struct tnf_ctx {
   int sm_count = 148;
   uint64_t budget = 0;
   cudaStream_t compute = nullptr, copy = nullptr;
+  cudaStream_t readback = nullptr;  // device -> host copies of tnf_stream_download: full duplex beside the uploads on `copy`
   cudaStream_t push[8] = {};  // lanes of tnf_push_peers, made on first use
   cudaEvent_t push_done[8] = {};
+  bool push_pending[8] = {};  // a push was recorded on lane i and nothing has waited for it yet
   std::mutex mu;
   uint64_t next_id = 1;
   std::unordered_map<uint64_t, tnf_buffer_rec> bufs;

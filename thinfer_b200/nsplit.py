@@ -66,6 +66,10 @@ class NSplitGroup:
         """Compute stream waits for the pushes queued so far; follow with ``barrier``."""
         _check(self.be.lib.tnf_compute_after_copy(self.be._ctx))
 
+    def wait_pushes(self) -> None:
+        """Compute stream waits for the ``push_peers`` copies queued so far (not for host uploads or read-backs)."""
+        _check(self.be.lib.tnf_compute_after_push(self.be._ctx))
+
     def barrier(self) -> None:
         """Stream-ordered: later work on the compute stream starts after every rank got here."""
         _check(self.be.lib.tnf_comm_barrier(self.be._ctx))
@@ -133,7 +137,7 @@ class PackedGather:
         interleave the slots into the full output."""
         g, lib, ctx = self.grp, self.grp.be.lib, self.grp.be._ctx
         if sync:
-            g.wait_scatter()
+            g.wait_pushes()
             g.barrier()
         _check(lib.tnf_interleave_cols(ctx, self.recv, self.slot, self.row_bytes, g.world, out, self.row_bytes * g.world,
                                        self.m, self.row_bytes))
