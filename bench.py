@@ -10,7 +10,8 @@ than L2). Each linear is the library's public call: activation quantiser + tcgen
 the fused epilogue.
 N > 1 (torchrun, one rank per GPU): one step = the batched Wan-5B-shaped FFN pair at
 M = 26520 with the weights split by output columns over the ranks and every rank's slice
-delivered to all ranks (--gather: packed copy-engine pushes by default; NCCL all-gathers, the fused
+delivered to all ranks (--gather: packed copy-engine pushes up to 4 ranks and an NCCL all-gather of the NVFP4
+copy beyond by default; bf16 all-gather, the fused
 peer-store epilogue and strided copy-engine bands are the alternatives).
 
 Prints ONE JSON line on rank 0.
@@ -622,7 +623,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=60, help="layers in the single-GPU stack (60 = the named workload)")
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl", "nvfp4", "push"],
-                    help="N>1: how slices reach every rank (auto = push: packed NVFP4/bf16 slices, contiguous copy-engine pushes)")
+                    help="N>1: how slices reach every rank (auto: push = packed NVFP4/bf16 slices by contiguous copy-engine pushes up to 4 ranks, nvfp4 = the same bytes by NCCL all-gather beyond)")
     ap.add_argument("--bands", type=int, default=2, help="N>1 with --gather push/copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="stack", choices=["stack", "stream"],

@@ -52,9 +52,9 @@ def run_multi_gpu(args):
     grp = NSplitGroup(be, rank, world)
     M = WAN_M
     if args.gather == "auto":
-        # measured ms/step at 2 / 4 / 8 ranks: push 1.12 / 1.09 / 1.23-1.32, nvfp4 (NCCL) 1.32 / 1.09 / 1.29,
-        # fused 1.20 / 4.3 / -, nccl (bf16) 2.2 / 2.15 / 2.12, copy (strided) 1.34 / 2.27 / 4.35
-        args.gather = "push"
+        # measured ms/step at 2 / 4 / 8 ranks: push 1.04-1.17 / 1.05-1.13 / 1.19-2.27 (noisy with 7 peers), nvfp4 (NCCL)
+        # 1.32 / 1.09 / 0.98-1.29, fused 1.20 / 4.3 / -, nccl (bf16) 2.2 / 2.15 / 2.12, copy (strided) 1.34 / 2.27 / 4.35
+        args.gather = "push" if world <= 4 else "nvfp4"
     gen = torch.Generator(device=dev)
     gen.manual_seed(0xC5)  # same seed on every rank: identical full tensors, each rank keeps its slice
 
