@@ -32,7 +32,7 @@ def run_multi_gpu(args):
     import torch.distributed as dist
 
     import thinfer_b200 as T
-    from bench import (ClockSampler, HIDDEN, NOMINAL_FP4_TFLOPS, WAN_FFN, WAN_M, as_torch, cpu_sample, make_weight,
+    from bench import (ClockSampler, HIDDEN, NOMINAL_FP4_TFLOPS, WAN_FFN, WAN_M, as_torch, make_weight,
                        measured_peaks, workload_config)
     from thinfer_b200 import _lib as L
     from thinfer_b200.nsplit import NSplitGroup, column_partition

@@ -11,7 +11,7 @@ plumbing that passes handles and the NCCL id around.
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Sequence, Tuple
+from typing import List, Tuple
 
 from . import _lib as L
 from .backend import Backend, Buf, _check
