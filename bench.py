@@ -14,6 +14,16 @@ delivered to all ranks (--gather: packed copy-engine pushes up to 4 ranks and an
 copy beyond by default; bf16 all-gather, the fused
 peer-store epilogue and strided copy-engine bands are the alternatives).
 
+The N = 1 line also carries, measured after the headline's timed region: `parity` (a 256-row sample of the
+timed step's own outputs against the CPU oracle), `shapes` (the other BASELINE shapes as single launches: configs[0],
+configs[2], the M = 1 modulation linear, and the configs[4] FFN pair on one GPU, which is the same-workload
+reference of the N > 1 lines) and `stream` (configs[3] streamed from pinned host memory under 6 GiB).
+
+    python bench.py --workload linear --m M --n N --k K [--act 1] [--out-nvfp4] [--iters I] [--flush-l2]
+    python bench.py --workload norm-quant --m M --k K
+
+time one launch shape (what the ncu captures under profiles/ run).
+
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -43,6 +53,17 @@ QWEN_LINEARS = [  # (name, k, n, act)
 WAN_M = 26520
 WAN_FFN = 14336
 NOMINAL_FP4_TFLOPS = 9000.0  # NVIDIA's dense FP4 figure for B200 (context only)
+
+
+def captured_traffic():
+    """DRAM bytes per launch of the dominant kernel, from the committed summary of its ncu captures."""
+    p = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    if not os.path.exists(p):
+        return None, "no committed capture"
+    d = json.load(open(p))
+    per = d["nvfp4_gemm_pair_kernel"]["dram_bytes_per_launch"]
+    # one launch of each block linear per layer: the average launch moves the mean of the four
+    return float(np.mean([per[k] for k in ("qkv", "out", "up", "down")])), d["nvfp4_gemm_pair_kernel"]["source"]
 
 
 def measured_peaks():
@@ -270,6 +291,226 @@ def make_weight(be, T, L, gen, n, k, sigma=0.02, with_bias=True):
     return T.Nvfp4Weight(n, k, codes, devs, float(g.value), bias, None)
 
 
+
+# --------------------------------------------------------------------------------------------
+# single launch shapes (also what the ncu captures under profiles/ run)
+# --------------------------------------------------------------------------------------------
+def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, out_nvfp4=False, seed=1234):
+    """Average launch times of one linear shape through the C ABI: the activation quantiser and the GEMM with its
+    fused epilogue, CUDA events on the library's compute stream. With flush_l2 a 256 MB buffer is overwritten
+    between iterations (untimed) so that a small problem is read from HBM every time."""
+    import torch
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+    from thinfer_b200.backend import device_scales_bytes
+
+    sc = be.scope()
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    W = make_weight(be, T, L, gen, n, k)
+    a = be.allocate(max(m * k * 2, 256))
+    as_torch(be, a, torch.bfloat16, (max(m * k, 128),))[: m * k].copy_(torch.randn(m * k, device=dev, generator=gen).to(torch.bfloat16))
+    out = be.allocate(max(m * n * 2, 256))
+    q_out = None
+    if out_nvfp4:  # the epilogue also emits the result as the next linear's NVFP4 operand
+        q_out = (be.allocate(m * n // 2), be.allocate(device_scales_bytes(m, n)), 0.0009765625)
+    torch.cuda.synchronize()
+    c_, s_, ga = sc.act_quant(a, m, k, 0.0, device_layout=True)
+    be.free(c_)
+    be.free(s_)
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush_l2 else None
+    tq, tg = [], []
+    for it in range(warmup + iters):
+        if flush is not None:
+            flush.fill_(it & 0xFF)
+            torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record(stream)
+        if quant or it == 0:
+            sc.act_quant_shared(a, m, k, ga)
+        e[1].record(stream)
+        sc.linear(None, m, W, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED, out_nvfp4=q_out)
+        e[2].record(stream)
+        be.submit(60000)
+        torch.cuda.synchronize()
+        if it >= warmup:
+            tq.append(e[0].elapsed_time(e[1]))
+            tg.append(e[1].elapsed_time(e[2]))
+    flops = 2.0 * m * n * k
+    gemm_ms, quant_ms = float(np.mean(tg)), float(np.mean(tq))
+    res = {
+        "m": m, "n": n, "k": k, "act": act, "out_nvfp4": bool(out_nvfp4), "iters": iters, "flush_l2": bool(flush_l2),
+        "gemm_ms": gemm_ms, "gemm_ms_min": float(np.min(tg)), "quant_ms": quant_ms if quant else None,
+        "gemm_tflops": flops / (gemm_ms * 1e-3) / 1e12,
+        "linear_tflops": flops / ((gemm_ms + (quant_ms if quant else 0.0)) * 1e-3) / 1e12,
+        "gemm_min_bytes": m * k // 2 + m * k // 16 + n * k // 2 + n * k // 16 + 2 * n + 2 * m * n,
+        "quant_min_bytes": 2 * m * k + m * k // 2 + m * k // 16,
+    }
+    res["gemm_gbs"] = res["gemm_min_bytes"] / (gemm_ms * 1e-3) / 1e9
+    if quant:
+        res["quant_gbs"] = res["quant_min_bytes"] / (quant_ms * 1e-3) / 1e9
+    for b in [a, out] + (list(q_out[:2]) if q_out else []):
+        be.free(b)
+    W.free(be)
+    return res
+
+
+def time_norm_quant(be, m, k, iters=20, warmup=3):
+    """Times the fused LayerNorm + modulate + quantiser launch on [m, k] bf16 rows (no bf16 output)."""
+    import torch
+    from thinfer_b200.backend import device_scales_bytes
+
+    sc = be.scope()
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321)
+    x = be.allocate(m * k * 2)
+    as_torch(be, x, torch.bfloat16, (m, k)).copy_(torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16))
+    s, t = be.allocate(k * 2), be.allocate(k * 2)
+    as_torch(be, s, torch.bfloat16, (k,)).copy_((torch.randn(k, device=dev, generator=gen) * 0.3).to(torch.bfloat16))
+    as_torch(be, t, torch.bfloat16, (k,)).copy_((torch.randn(k, device=dev, generator=gen) * 0.2).to(torch.bfloat16))
+    codes, scales = be.allocate(m * k // 2), be.allocate(device_scales_bytes(m, k))
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    ts = []
+    for it in range(warmup + iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        sc.norm_modulate_quant(x, m, k, 0.002, codes, scales, scale=s, shift=t)
+        e1.record(stream)
+        be.submit(60000)
+        torch.cuda.synchronize()
+        if it >= warmup:
+            ts.append(e0.elapsed_time(e1))
+    ms = float(np.mean(ts))
+    nbytes = 2 * m * k + m * k // 2 + m * k // 16 + 4 * k
+    return {"op": "norm_modulate_quant", "m": m, "k": k, "ms": ms, "ms_min": float(np.min(ts)), "min_bytes": nbytes,
+            "gbs": nbytes / (ms * 1e-3) / 1e9}
+
+
+def run_launch_workload(args):
+    import torch
+    import thinfer_b200 as T
+
+    torch.cuda.set_device(0)
+    be = T.Backend(0)
+    if args.workload == "norm-quant":
+        res = time_norm_quant(be, args.m, args.k, args.iters, args.warmup)
+    else:
+        res = time_linear(be, args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
+                          args.out_nvfp4)
+    be.close()
+    print(json.dumps(res))
+
+
+def time_ffn_pair(be, m, hidden, ffn, iters=10, warmup=3):
+    """The FFN pair (up + bias + GELU emitting the NVFP4 operand, down + bias) on one GPU, full weights: the
+    same work the N > 1 lines split over ranks, without any exchange."""
+    import torch
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+    from thinfer_b200.backend import device_scales_bytes
+
+    sc = be.scope()
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0xC5AA)
+    w_up, w_dn = make_weight(be, T, L, gen, ffn, hidden), make_weight(be, T, L, gen, hidden, ffn)
+    x, y = be.allocate(m * hidden * 2), be.allocate(m * hidden * 2)
+    as_torch(be, x, torch.bfloat16, (m, hidden)).copy_(torch.randn(m, hidden, device=dev, generator=gen).to(torch.bfloat16))
+    hc, hs = be.allocate(m * ffn // 2), be.allocate(device_scales_bytes(m, ffn))
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    ga_x, ga_h = 0.0018, 0.0009765625
+
+    def pair():
+        sc.linear(x, m, w_up, ga_x, None, act=1, out_nvfp4=(hc, hs, ga_h))
+        sc.matmul(hc, hs, m, w_dn, ga_h, y)
+
+    for _ in range(warmup):
+        pair()
+    be.submit()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(iters):
+        pair()
+    e1.record(stream)
+    be.submit()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    for b in (x, y, hc, hs):
+        be.free(b)
+    w_up.free(be)
+    w_dn.free(be)
+    return {"ms": ms, "tflops": 4.0 * m * hidden * ffn / (ms * 1e-3) / 1e12, "iters": iters}
+
+
+def other_shapes(be):
+    """The BASELINE shapes that are not the headline, as single launches (CUDA events, L2 flushed between
+    iterations for the small ones). Tensor-bound shapes report TFLOP/s against 4 x the measured sustained bf16
+    peak, the skinny ones GB/s of their minimum bytes against the measured copy bandwidth."""
+    peaks = measured_peaks()
+    fp4 = 4.0 * peaks["bf16_sustained"]
+    out = {}
+
+    def tensor(name, r):
+        out[name] = {"gemm_us": r["gemm_ms"] * 1e3, "quant_us": r["quant_ms"] * 1e3, "tflops": r["gemm_tflops"], "bound": "tensor",
+                     "frac": r["gemm_tflops"] / fp4}
+
+    def hbm(name, r):
+        out[name] = {"gemm_us": r["gemm_ms"] * 1e3, "quant_us": r["quant_ms"] * 1e3, "tflops": r["gemm_tflops"], "bound": "hbm",
+                     "min_bytes": r["gemm_min_bytes"], "gbs": r["gemm_gbs"], "frac": r["gemm_gbs"] / peaks["hbm_gbs"]}
+
+    hbm("c1_256x3072x3072_bias", time_linear(be, 256, 3072, 3072, iters=20, flush_l2=True))
+    hbm("mod_1x3072x18432", time_linear(be, 1, 18432, 3072, iters=20, flush_l2=True))
+    tensor("c3_up_6630x3072x14336_gelu", time_linear(be, 6630, 14336, 3072, act=1, iters=10))
+    tensor("c3_down_6630x14336x3072", time_linear(be, 6630, 3072, 14336, iters=10))
+    pair = time_ffn_pair(be, WAN_M, HIDDEN, WAN_FFN)
+    out["c5_ffn_pair_26520_one_gpu"] = {"ms": pair["ms"], "tflops": pair["tflops"], "bound": "tensor", "frac": pair["tflops"] / fp4,
+                                        "note": "the N > 1 lines split this work by output columns; this is their same-workload N = 1 time"}
+    out["peaks"] = {"fp4_tflops": fp4, "hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}
+    return out
+
+
+def sample_rows(m, per_slab=86):
+    """Row indices for the parity sample: the first rows, a slab around the middle, the last rows."""
+    mid = (m // 2) // 256 * 256 + 100
+    return np.concatenate([np.arange(per_slab), np.arange(mid, mid + per_slab - 1), np.arange(m - per_slab + 1, m)])
+
+
+def read_rows(be, buf, rows, row_bytes, dtype=np.uint16):
+    out, start, prev = [], int(rows[0]), int(rows[0])
+    for r in list(rows[1:]) + [None]:
+        if r is None or r != prev + 1:
+            out.append(be.read_buffer(buf, dtype, count=(prev + 1 - start) * row_bytes // np.dtype(dtype).itemsize,
+                                      offset=start * row_bytes))
+            start = r
+        prev = r
+    return np.concatenate(out)
+
+
+def weight_to_host(be, w):
+    """(codes [n,k/2], canonical scales [n,k/16], g, bias bits) of a resident weight, for the CPU oracle."""
+    n, k = w.n, w.k
+    codes = be.read_buffer(w.codes).reshape(n, k // 2)
+    dev = be.read_buffer(w.scales_device)
+    nb = k // 16
+    ka = ((k + 63) // 64 + 3) // 4 * 4
+    r, b = np.arange(n)[:, None], np.arange(nb)[None, :]
+    scales = dev[((r // 128) * ka + b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (b % 4)]
+    bias = be.read_buffer(w.bias, np.uint16, count=n) if w.bias is not None else None
+    return codes, scales, w.global_scale, bias
+
+
+def parity_entry(got_bits, want_bits):
+    g, e = _bf16_to_f32(got_bits).astype(np.float64), _bf16_to_f32(want_bits).astype(np.float64)
+    return {"rel_fro": float(np.linalg.norm(g - e) / max(np.linalg.norm(e), 1e-300)), "bit_equal": float((got_bits == want_bits).mean()),
+            "rows": int(got_bits.shape[0])}
+
+
 def run_single_gpu(args):
     import torch
     import thinfer_b200 as T
@@ -387,10 +628,38 @@ def run_single_gpu(args):
         "per_shape": {QWEN_LINEARS[j][0]: {"ms": float(np.mean(v)),
                                             "tflops": 2.0 * M * QWEN_LINEARS[j][1] * QWEN_LINEARS[j][2] / (np.mean(v) * 1e-3) / 1e12}
                       for j, v in sorted(per_shape.items())},
-        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures of the pair
-        # kernel (qkv 52.9 MB, down 60.0 MB; algorithmic 103.7 / 78.1 MB)
-        "traffic": 56.4e6, "traffic_note": "mean of the two captured shapes; below the algorithmic bytes (outputs stay in L2)",
     }
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch, read from the committed ncu summary (not measured
+    # by this run: ncu is never part of a bench run)
+    roofline["traffic"], roofline["traffic_note"] = captured_traffic()
+
+    # ---- parity of the timed step's own outputs (the only place this arm touches the oracle: as the checker) ----
+    # After the timed region the buffers hold the last layer's inputs and outputs of the last step. A 256-row sample
+    # (first, middle and last row tile) of each of that layer's four linears is recomputed by the CPU oracle from the
+    # device's own inputs and weights. MLP up stores no bf16 in the timed step, so that launch is repeated once with
+    # the bf16 store on (same kernel, same epilogue); down is checked on the H the device produced.
+    parity = None
+    if not args.no_cpu:
+        import oracle as O
+
+        li = layers - 1
+        rows = sample_rows(M)
+        io = layer_io(li)
+        host_w = [weight_to_host(be, w) for w in weights[li]]
+        sc.linear(io[2][0], M, weights[li][2], scales[li][2], h2, act=1, out_nvfp4=(h2c, h2s, scales[li][3]))
+        be.submit()
+        ins = [read_rows(be, io[0][0], rows, HIDDEN * 2).reshape(len(rows), HIDDEN),
+               read_rows(be, io[1][0], rows, HIDDEN * 2).reshape(len(rows), HIDDEN),
+               read_rows(be, io[2][0], rows, HIDDEN * 2).reshape(len(rows), HIDDEN),
+               read_rows(be, h2, rows, 12288 * 2).reshape(len(rows), 12288)]
+        outs_dev = [io[0][1], io[1][1], h2, io[3][1]]
+        parity = {"tolerance": 1e-3, "layer": li, "sample": "256 rows: first, middle and last row tile; oracle on the device's own inputs"}
+        for j, (name, k, n, act) in enumerate(QWEN_LINEARS):
+            wc, ws, gw, bias = host_w[j]
+            want = O.linear(ins[j], scales[li][j], wc, ws, gw, bias=bias, act=act)
+            got = read_rows(be, outs_dev[j], rows, n * 2).reshape(len(rows), n)
+            parity[name] = parity_entry(got, want)
+        parity["ok"] = all(parity[nm]["rel_fro"] <= 1e-3 for nm, *_ in QWEN_LINEARS)
 
     # ---- end to end through the public API with host buffers ----
     # Every step's input comes from pinned host memory and its result goes back to pinned host memory, both inside
@@ -433,15 +702,26 @@ def run_single_gpu(args):
         "config": dict(workload_config(1), layers=layers),
         "ms_per_dit_step": ms_step * 60.0 / layers,
         "frac_of_nominal_fp4": flops_step / (ms_step * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "parity": parity,
         "e2e": {"value": flops_step / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": M * HIDDEN * 2, "d2h_bytes_per_step": M * HIDDEN * 2, "output_ok": out_ok,
                 "note": "tnf_stream_upload / tnf_stream_download on the copy stream, double-buffered against the compute stream"},
         "gpu_launches": args.steps * layers * 7,  # per layer: 3 activation quantisers + 4 GEMMs
         "mem": be.mem_snapshot(),
     }
-    print(json.dumps(line))
     be.close()
+    del weights
+    torch.cuda.empty_cache()
+    if not args.headline_only:
+        be2 = T.Backend(0)
+        line["shapes"] = other_shapes(be2)
+        be2.close()
+        st_args = argparse.Namespace(**vars(args))
+        st_args.steps, st_args.warmup = max(args.steps, 5), 2
+        st = run_stream_bench(st_args, as_dict=True)
+        line["stream"] = {k: st[k] for k in ("ms_per_step", "steps", "tflops", "weights_bytes", "uploaded_per_step", "h2d_gbs",
+                                              "h2d_peak_gbs_measured", "roofline", "vram_true_peak", "vram_budget", "config")}
+    print(json.dumps(line))
 
 
 def e2e_pipelined(be, step, x_buf, out_buf, in_bytes, out_bytes, host_in, host_out, x_stage, out_stage, n_steps):
@@ -506,7 +786,7 @@ def _bf16_to_f32(h):
     return (h.astype(np.uint32) << 16).view(np.float32)
 
 
-def run_stream_bench(args):
+def run_stream_bench(args, as_dict=False):
     """BASELINE configs[3], streamed variant: the dual-stream Qwen-Image-shaped stack (img M=4096, txt M=256,
     two M=1 modulation linears; 60 layers, 11.46 GB of NVFP4 records in pinned host memory) under a 6 GiB
     VRAM budget. Reports ms per step, achieved H2D GB/s against a measured pinned-copy peak, and the overlap."""
@@ -612,6 +892,8 @@ def run_stream_bench(args):
                      "traffic": stats["uploaded_last_step"]},
         "vram_true_peak": peak["true_peak"], "vram_budget": 6 * GiB, "clocks": clocks, "setup_s": setup_s,
     }
+    if as_dict:
+        return line
     print(json.dumps(line))
 
 
@@ -626,8 +908,18 @@ def main():
                     help="N>1: how slices reach every rank (auto: push = packed NVFP4/bf16 slices by contiguous copy-engine pushes up to 4 ranks, nvfp4 = the same bytes by NCCL all-gather beyond)")
     ap.add_argument("--bands", type=int, default=2, help="N>1 with --gather push/copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="stack", choices=["stack", "stream"],
-                    help="N=1: 'stack' = resident 60-layer block-linear stack (default); 'stream' = streamed variant under 6 GiB")
+    ap.add_argument("--workload", default="stack", choices=["stack", "stream", "linear", "norm-quant"],
+                    help="N=1: 'stack' = resident 60-layer block-linear stack (default); 'stream' = streamed variant under 6 GiB; "
+                         "'linear' / 'norm-quant' = one launch shape (--m --n --k)")
+    ap.add_argument("--headline-only", action="store_true", help="N=1 stack: skip the `shapes` and `stream` sections")
+    ap.add_argument("--m", type=int, default=4352)
+    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--act", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-quant", action="store_true", help="linear: quantise the activations once, time the GEMM alone afterwards")
+    ap.add_argument("--flush-l2", action="store_true", help="linear: overwrite a 256 MB buffer between iterations")
+    ap.add_argument("--out-nvfp4", action="store_true", help="linear: the epilogue also emits the NVFP4 copy of the output")
     ap.add_argument("--ring-slots", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -639,6 +931,8 @@ def main():
         run_multi_gpu(args)
     elif args.workload == "stream":
         run_stream_bench(args)
+    elif args.workload in ("linear", "norm-quant"):
+        run_launch_workload(args)
     else:
         run_single_gpu(args)
 

@@ -93,6 +93,19 @@ int32_t tnf_sync(tnf_ctx* ctx, uint32_t timeout_ms);
  * workspace, live staging, peak weights, peak workspace, peak staging, true concurrent
  * peak, bytes streamed host->device since creation}. */
 int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]);
+/* Upper bound, in SM cycles, of every device-side wait of the kernels launched afterwards (a wait on a
+ * loaded stage, a freed stage, a finished or drained accumulator). A wait that runs out makes its kernel
+ * return normally with the status word set, and the next tnf_sync returns TNF_ERR_TIMEOUT: the analogue of a
+ * submit whose error surfaces at the awaited future (thinfer-core/src/backend/wgpu.rs:948,1063-1068) instead
+ * of a lost device. 0 restores the default (4e9 cycles, about two seconds). */
+int32_t tnf_set_device_wait_limit(tnf_ctx* ctx, uint64_t sm_cycles);
+/* Failure-detection self-test (the reference's counterpart is the submit-error path above, exercised
+ * in its tests by a failing dispatch): launches the CTA-pair GEMM on a small zeroed problem with its
+ * loader switched off, so that nothing is in flight and the first device-side wait runs out after the
+ * context's wait limit. Blocks until the kernel has returned. The call itself returns TNF_OK; the
+ * NEXT tnf_sync must return TNF_ERR_TIMEOUT, and the context stays usable afterwards. Set a short
+ * limit first (tnf_set_device_wait_limit), or the call takes about two seconds. */
+int32_t tnf_selftest_stalled_wait(tnf_ctx* ctx);
 /* The context's CUDA streams (cudaStream_t as void*), for event timing by the caller. */
 int32_t tnf_streams(tnf_ctx* ctx, void** compute_stream, void** copy_stream);
 

@@ -44,8 +44,10 @@ def _linear_both_ways(be, m, n, k, seed, act):
 
 
 def test_noalloc_matches_regular_entry_point_twice(backend):
-    # a larger problem first, then a smaller ragged one: the second call finds stale bytes in the array
-    for (m, n, k, seed, act) in [(1000, 520, 1024, 1, 1), (200, 264, 320, 2, 0), (100, 128, 64, 3, 0)]:
+    # a larger problem first, then smaller ragged ones: later calls find stale bytes in the array. The first shape
+    # has 32 tiles of 256 x 256 and runs the CTA-pair kernel (tensor maps built on the host stack), the others the
+    # single-CTA kernel.
+    for (m, n, k, seed, act) in [(2048, 1024, 256, 4, 1), (1000, 520, 1024, 1, 1), (200, 264, 320, 2, 0), (100, 128, 64, 3, 0)]:
         ref, new, want = _linear_both_ways(backend, m, n, k, seed, act)
         assert not np.isnan(O.bf16_to_f32(new)).any()
         assert np.array_equal(new, ref)

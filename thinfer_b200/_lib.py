@@ -75,6 +75,8 @@ SIGNATURES = {
     "tnf_sync": (C.c_int32, [_ctx, C.c_uint32]),
     "tnf_mem_snapshot": (C.c_int32, [_ctx, _u64p]),
     "tnf_streams": (C.c_int32, [_ctx, _vpp, _vpp]),
+    "tnf_set_device_wait_limit": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_selftest_stalled_wait": (C.c_int32, [_ctx]),
     "tnf_quantize_weight": (C.c_int32, [_ctx, Buf, C.c_int32, C.c_uint32, C.c_uint32, Buf, Buf, C.POINTER(C.c_float)]),
     "tnf_device_scales_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32]),
     "tnf_prepare_scales": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, Buf]),

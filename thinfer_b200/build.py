@@ -31,7 +31,20 @@ def stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+DIAG_OUT = os.path.join(HERE, "libthinfer_nvfp4_diag.so")
+
+
+def build(force: bool = False, verbose: bool = False, diag: bool = False) -> str:
+    """Builds the library. ``diag=True`` builds the diagnostic variant instead (clock64 traces, "skip
+    this part" switches and kernel-selection overrides read from TNF_GEMM_* environment variables) as
+    libthinfer_nvfp4_diag.so; point THINFER_B200_LIB at it to use it. The default library has none of that."""
+    if diag:
+        cmd = [NVCC, *FLAGS, "-DTNF_GEMM_DIAG", "-o", DIAG_OUT, *sources(), "-ldl"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError("nvcc failed building libthinfer_nvfp4_diag.so")
+        return DIAG_OUT
     if not (force or stale()):
         return OUT
     cmd = [NVCC, *FLAGS, "-o", OUT, *sources(), "-ldl"]
@@ -47,4 +60,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force=True, verbose="-v" in sys.argv))
+    print(build(force=True, verbose="-v" in sys.argv, diag="--diag" in sys.argv))

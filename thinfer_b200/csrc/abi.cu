@@ -152,14 +152,19 @@ int make_tensor_map(CUtensorMap* out, const MapSpec& sp) {
   return TNF_OK;
 }
 
-const CUtensorMap* get_map(tnf_ctx* ctx, const MapSpec& spec) {
+// The map is copied out under the lock: a pointer into the cache could be invalidated by the next lookup's
+// eviction or by another thread's tnf_free before the launch copies it.
+bool get_map(tnf_ctx* ctx, const MapSpec& spec, CUtensorMap* out) {
   std::lock_guard<std::mutex> lk(ctx->mu);
   auto it = ctx->maps.find(spec);
-  if (it != ctx->maps.end()) return &it->second;
-  CUtensorMap m;
-  if (make_tensor_map(&m, spec) != TNF_OK) return nullptr;
-  if (ctx->maps.size() > 8192) ctx->maps.clear();
-  return &(ctx->maps[spec] = m);
+  if (it != ctx->maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  if (make_tensor_map(out, spec) != TNF_OK) return false;
+  if (ctx->maps.size() >= 8192) ctx->maps.erase(ctx->maps.begin());  // bounded cache: drop one entry, never all
+  ctx->maps[spec] = *out;
+  return true;
 }
 
 // packed E2M1 codes viewed as bytes [rows, k/2]: box {128 bytes, box_rows}, 128-byte swizzle
@@ -182,6 +187,7 @@ static MapSpec out_spec(const void* base, uint32_t m, uint32_t n, uint32_t ldo) 
 static int32_t ensure_scratch(tnf_ctx* ctx, uint32_t m, uint32_t k) {
   uint64_t need_codes = uint64_t(m) * (k / 2), need_scales = sf_device_bytes(m, k);
   std::lock_guard<std::mutex> lk(ctx->mu);
+  if (need_codes > ctx->scratch_codes_bytes || need_scales > ctx->scratch_scales_bytes) ctx->scratch_m = ctx->scratch_k = 0;
   if (need_codes > ctx->scratch_codes_bytes) {
     if (ctx->scratch_codes_id) free_locked(ctx, ctx->scratch_codes_id);
     ctx->scratch_codes_id = 0;
@@ -253,8 +259,14 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
     p.q_global = a->out_global;
     p.q_inv_t = 1.0f / (6.0f * a->out_global);
     p.q_k_atoms = sf_k_atoms(ldo);
-    if ((ldo / 64) % 4 != 0)  // K-padding atoms of the next operand must hold benign (zero) scales
-      TNF_CUDA(cudaMemsetAsync(p.q_scales, 0, sf_device_bytes(a->m, ldo), ctx->compute), "out_scales clear");
+    // The scale layout pads K to whole groups of four 512-byte atoms; the padding atoms of the next operand must
+    // hold benign (zero) scales. Only those atoms are cleared (atoms ldo/64 .. k_atoms-1 of every 128-row block),
+    // so an earlier window call's scales in the same buffer stay intact.
+    const uint32_t used_atoms = ldo / 64;
+    if (used_atoms < p.q_k_atoms)
+      TNF_CUDA(cudaMemset2DAsync(p.q_scales + uint64_t(used_atoms) * 512u, uint64_t(p.q_k_atoms) * 512u, 0,
+                                 uint64_t(p.q_k_atoms - used_atoms) * 512u, (a->m + 127u) / 128u, ctx->compute),
+               "out_scales padding clear");
   }
   p.m = a->m; p.n = a->n; p.k = a->k;
   p.k_atoms = sf_k_atoms(a->k);
@@ -287,29 +299,28 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.act = a->act;
   p.chain = a->parity_mode;
   p.status = ctx->dwords;
+  p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
+  CUtensorMap ma, mw;
   if (q_out || gemm_use_pair(a->m, a->n, a->k)) {
     const uint32_t kb = gemm_pair_kblocks();
-    const CUtensorMap* ma = get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb));
-    const CUtensorMap* mw = get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb));
-    const CUtensorMap* msa = get_map(ctx, scales_spec(a_scales, a->m, a->k, kb));
-    const CUtensorMap* msb = get_map(ctx, scales_spec(w_scales, a->n, a->k, kb));
-    if (!ma || !mw || !msa || !msb) return TNF_ERR_INVALID_ARGUMENT;
-    CUtensorMap outs[kMaxPeers];
+    CUtensorMap msa, msb, outs[kMaxPeers];
+    if (!get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb), &ma) || !get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb), &mw) ||
+        !get_map(ctx, scales_spec(a_scales, a->m, a->k, kb), &msa) || !get_map(ctx, scales_spec(w_scales, a->n, a->k, kb), &msb))
+      return TNF_ERR_INVALID_ARGUMENT;
     for (uint32_t d = 0; d < p.n_out; ++d) {
       // without a bf16 destination the map is never used; any valid one fills the slot
-      const CUtensorMap* mo = store_bf16 ? get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo)) : ma;
-      if (!mo) return TNF_ERR_INVALID_ARGUMENT;
-      outs[d] = *mo;
+      if (!store_bf16) outs[d] = ma;
+      else if (!get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo), &outs[d])) return TNF_ERR_INVALID_ARGUMENT;
     }
     for (uint32_t d = p.n_out; d < kMaxPeers; ++d) outs[d] = outs[0];
-    TNF_CUDA(launch_gemm_nvfp4_pair(*ma, *mw, *msa, *msb, outs, p, ctx->sm_count, ctx->compute), "nvfp4 pair gemm launch");
+    TNF_CUDA(launch_gemm_nvfp4_pair(ma, mw, msa, msb, outs, p, ctx->sm_count, ctx->compute), "nvfp4 pair gemm launch");
     return TNF_OK;
   }
-  const CUtensorMap* ma = get_map(ctx, codes_spec(a_codes, a->m, a->k, 128));
-  const CUtensorMap* mw = get_map(ctx, codes_spec(w_codes, a->n, a->k, gemm_tile_n(a->m, a->n)));
-  if (!ma || !mw) return TNF_ERR_INVALID_ARGUMENT;
-  TNF_CUDA(launch_gemm_nvfp4(*ma, *mw, p, ctx->sm_count, ctx->compute), "nvfp4 gemm launch");
+  if (!get_map(ctx, codes_spec(a_codes, a->m, a->k, 128), &ma) ||
+      !get_map(ctx, codes_spec(w_codes, a->n, a->k, gemm_tile_n(a->m, a->n)), &mw))
+    return TNF_ERR_INVALID_ARGUMENT;
+  TNF_CUDA(launch_gemm_nvfp4(ma, mw, p, ctx->sm_count, ctx->compute), "nvfp4 gemm launch");
   return TNF_OK;
 }
 
@@ -527,11 +538,73 @@ int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]) {
   return TNF_OK;
 }
 
-// Diagnostic (not part of the ABI header): copies the clock64 stamps recorded with TNF_GEMM_DIAG bit 16.
+#ifdef TNF_GEMM_DIAG
+// Diagnostic builds only (not part of the ABI): copies the clock64 stamps recorded with TNF_GEMM_DIAG bit 16.
 int32_t tnf_debug_trace(tnf_ctx* ctx, unsigned long long* dst_2048) {
   TNF_CHECK_CTX(ctx);
   TNF_CUDA(cudaMemcpy(dst_2048, ctx->dwords + 64, 16384, cudaMemcpyDeviceToHost), "trace read");
   return TNF_OK;
+}
+#endif
+
+int32_t tnf_set_device_wait_limit(tnf_ctx* ctx, uint64_t sm_cycles) {
+  if (!ctx) {
+    set_error("null context");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  ctx->wait_limit_cycles = sm_cycles ? (long long)std::min<uint64_t>(sm_cycles, uint64_t(1) << 40) : kDefaultWaitLimitCycles;
+  return TNF_OK;
+}
+
+int32_t tnf_selftest_stalled_wait(tnf_ctx* ctx) {
+  TNF_CHECK_CTX(ctx);
+  // A 512 x 512 x 512 problem on zeroed operands through the CTA-pair kernel with its producer switched off: no
+  // copy and no MMA is ever in flight, the MMA warp's first wait on a loaded stage gives up after the context's
+  // wait limit, every role falls through to the tear-down and the kernel returns normally with the status word set.
+  const uint32_t m = 512, n = 512, k = 512;
+  const uint64_t codes = uint64_t(m) * (k / 2), scales = sf_device_bytes(m, k), outb = uint64_t(m) * n * 2;
+  uint64_t id = 0;
+  uint8_t* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int32_t st = alloc_locked(ctx, 2 * codes + 2 * scales + outb, TNF_CAT_WORKSPACE, &id);
+    if (st != TNF_OK) return st;
+    base = static_cast<uint8_t*>(ctx->bufs[id].ptr);
+  }
+  cudaError_t e = cudaMemsetAsync(base, 0, 2 * codes + 2 * scales + outb, ctx->compute);
+  GemmParams p{};
+  p.m = m; p.n = n; p.k = k;
+  p.k_atoms = sf_k_atoms(k);
+  p.alpha = 1.0f;
+  p.sfa = base + 2 * codes;
+  p.sfb = base + 2 * codes + scales;
+  p.out[0] = reinterpret_cast<uint16_t*>(base + 2 * codes + 2 * scales);
+  p.n_out = 1;
+  p.ldo = n;
+  p.store_bf16 = 1;
+  p.status = ctx->dwords;
+  p.wait_limit = ctx->wait_limit_cycles;
+  p.stall = 1;
+  p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
+  CUtensorMap ma, mw, msa, msb, outs[kMaxPeers];
+  const uint32_t kb = gemm_pair_kblocks();
+  bool ok = e == cudaSuccess && make_tensor_map(&ma, pair_codes_spec(base, m, k, kb)) == TNF_OK &&
+            make_tensor_map(&mw, pair_codes_spec(base + codes, n, k, kb)) == TNF_OK &&
+            make_tensor_map(&msa, scales_spec(p.sfa, m, k, kb)) == TNF_OK &&
+            make_tensor_map(&msb, scales_spec(p.sfb, n, k, kb)) == TNF_OK &&
+            make_tensor_map(&outs[0], out_spec(p.out[0], m, n, n)) == TNF_OK;
+  if (ok) {
+    for (int d = 1; d < kMaxPeers; ++d) outs[d] = outs[0];
+    e = launch_gemm_nvfp4_pair(ma, mw, msa, msb, outs, p, ctx->sm_count, ctx->compute);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->compute);
+  }
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    free_locked(ctx, id);
+  }
+  if (!ok) return e != cudaSuccess ? cuda_fail(e, "tnf_selftest_stalled_wait set-up") : TNF_ERR_INVALID_ARGUMENT;
+  if (e != cudaSuccess) return cuda_fail(e, "tnf_selftest_stalled_wait");
+  return TNF_OK;  // the outcome is the status word: the next tnf_sync returns TNF_ERR_TIMEOUT
 }
 
 // ---- quantisers ----------------------------------------------------------------------------------
@@ -630,6 +703,8 @@ int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32
   if (!a) return st;
   st = ensure_scratch(ctx, m, k);
   if (st != TNF_OK) return st;
+  ctx->scratch_m = m;
+  ctx->scratch_k = k;
   return quantize_act_impl(ctx, a, m, k, global_scale, true, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
                            static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr);
 }
@@ -654,12 +729,17 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
     if (!src) return st;
     st = ensure_scratch(ctx, a->m, a->k);
     if (st != TNF_OK) return st;
+    ctx->scratch_m = a->m;
+    ctx->scratch_k = a->k;
     st = quantize_act_impl(ctx, src, a->m, a->k, a->a_global, true,
                            static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
                            static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr);
     if (st != TNF_OK) return st;
-  } else if (uint64_t(a->m) * (a->k / 2) > ctx->scratch_codes_bytes) {
-    set_error("TNF_LINEAR_A_PREQUANTIZED: tnf_quantize_act_shared has not been called for m=%u k=%u", a->m, a->k);
+  } else if (ctx->scratch_m != a->m || ctx->scratch_k != a->k) {
+    // the scratch is tagged with the shape it was last filled for: a pre-quantised call for any other shape would
+    // multiply stale codes (the scale layout depends on m and k), so it is refused
+    set_error("TNF_LINEAR_A_PREQUANTIZED: the shared scratch holds the quantised activations of m=%u k=%u, not m=%u k=%u "
+              "(call tnf_quantize_act_shared first)", ctx->scratch_m, ctx->scratch_k, a->m, a->k);
     return TNF_ERR_INVALID_ARGUMENT;
   }
   return run_gemm(ctx, a, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),

@@ -46,6 +46,8 @@ struct tnf_ctx {
   // scratch for on-the-fly activation quantisation (workspace category)
   uint64_t scratch_codes_id = 0, scratch_scales_id = 0;
   uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;
+  uint32_t scratch_m = 0, scratch_k = 0;  // shape the scratch was last filled for (0 = never)
+  long long wait_limit_cycles = tnf::kDefaultWaitLimitCycles;  // bound of every device-side mbarrier wait
   // small device words: [0] kernel status, [1] amax bits, [2] global scale (f32)
   uint32_t* dwords = nullptr;
   std::map<tnf::MapSpec, CUtensorMap> maps;
@@ -69,5 +71,5 @@ int32_t cuda_fail(cudaError_t e, const char* what);
 uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need_bytes, const char* name, int32_t* status);
 int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id);
 int32_t free_locked(tnf_ctx* ctx, uint64_t id);
-const CUtensorMap* get_map(tnf_ctx* ctx, const MapSpec& spec);
+bool get_map(tnf_ctx* ctx, const MapSpec& spec, CUtensorMap* out);  // copies the (cached) map out under the lock
 }  // namespace tnf

@@ -22,6 +22,7 @@
 #include <cstdint>
 #include <cstdlib>
 
+#include "epilogue.cuh"
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -51,12 +52,6 @@ struct TileCfg {
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 };
 
-__device__ __forceinline__ float gelu_tanh_dev(float x) {
-  // 0.5*x*(1+tanh(u)) == x / (1 + exp(-2u)), u = sqrt(2/pi)*(x + 0.044715 x^3)
-  float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  return x / (1.0f + __expf(-2.0f * u));
-}
-__device__ __forceinline__ float bf16_round_dev(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
 
 template <int BN>
@@ -86,9 +81,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t num_tiles = p.tiles_m * p.tiles_n;
-  const bool ktr = (p.diag & 16u) && blockIdx.x == 0;
+  const bool ktr = kDiag && (p.diag & 16u) && blockIdx.x == 0;
 
   const uint32_t num_k_tiles = (p.k + kBlockK - 1) / kBlockK;
+  const long long wait_limit = p.wait_limit > 0 ? p.wait_limit : kDefaultWaitLimitCycles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -127,13 +123,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint8_t* sfa_src = p.sfa + uint64_t(tm) * p.k_atoms * 512u;
         const uint8_t* sfb_src = p.sfb + uint64_t(n0 >> 7) * p.k_atoms * 512u;
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout, wait_limit)) {
             ok = false;
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
           if (elect_one()) {
-          if (p.diag & 8u) {
+          if (kDiag && (p.diag & 8u)) {
             mbar_arrive_expect_tx(full, Cfg::kSfaBytes + Cfg::kSfbBytes);
           } else {
             mbar_arrive_expect_tx(full, Cfg::kStageBytes);
@@ -160,14 +156,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const uint32_t n0 = (tile / p.tiles_m) * BN;
         const uint32_t sfb_shift = (n0 & 127u) >> 5;  // TMEM column shift when the tile starts inside a 128-row scale block
-        if (!mbar_wait_warp(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusAccEmptyTimeout)) {
+        if (!mbar_wait_warp(bar_acc_empty + 8 * acc, acc_phase ^ 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + Cfg::kAccCol0 + acc * BN;
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
             ok = false;
             break;
           }
@@ -176,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (elect_one()) {
           const uint32_t a_addr = sA + stage * Cfg::kABytes, b_addr = sB + stage * Cfg::kBBytes;
           const uint32_t sfa_addr = sSfa + stage * Cfg::kSfaBytes, sfb_addr = sSfb + stage * Cfg::kSfbBytes;
-          if (!(p.diag & 2u) || kt == 0)
+          if (!(kDiag && (p.diag & 2u)) || kt == 0)
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfaCol + kb * 4, make_desc_sf(sfa_addr + kb * 512));
@@ -185,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + j * 4,
                                    make_desc_sf(sfb_addr + j * 2048 + kb * 512));
           }
-          if (!(p.diag & 4u))
+          if (!(kDiag && (p.diag & 4u)))
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             tc_mma_nvfp4(d_tmem, make_desc_sw128(a_addr + kb * 32), make_desc_sw128(b_addr + kb * 32), idesc,
@@ -212,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       const uint32_t row = tm * kBlockM + quarter * 32 + lane;
       const uint32_t n0 = tn * BN;
-      if (!mbar_wait_bounded(bar_acc_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout)) {
+      if (!mbar_wait_bounded(bar_acc_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
         ok = false;
         break;
       }
@@ -249,14 +245,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 float x = __uint_as_float(r[v8 * 8 + h * 2 + e]) * p.alpha;
-                if (p.chain) x = bf16_round_dev(x);
+                if (p.chain) x = bf16r(x);
                 if (p.bias) {
                   x += bf16_bits_to_f32(e ? (bw[h] >> 16) : (bw[h] & 0xFFFFu));
-                  if (p.chain) x = bf16_round_dev(x);
+                  if (p.chain) x = bf16r(x);
                 }
                 if (p.act == 1u) {
-                  x = gelu_tanh_dev(x);
-                  if (p.chain) x = bf16_round_dev(x);
+                  x = p.chain ? gelu_tanh_exact(x) : gelu_tanh_fast(x);  // same two forms as the pair kernel
+                  if (p.chain) x = bf16r(x);
                 }
                 if (p.gate) {
                   float g = bf16_bits_to_f32(e ? (gw[h] >> 16) : (gw[h] & 0xFFFFu));
@@ -269,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               ow[h] = *reinterpret_cast<uint32_t*>(&pk);
             }
             const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-            if (!(p.diag & 1u) || o4.x == 0x12345678u)
+            if (!(kDiag && (p.diag & 1u)) || o4.x == 0x12345678u)
               for (uint32_t d = 0; d < p.n_out; ++d)
                 *reinterpret_cast<uint4*>(p.out[d] + out_off + v8 * 8) = o4;
           }
@@ -295,6 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 static uint32_t env_u32(const char* name, uint32_t dflt) {
+  if (!kDiag) return dflt;  // the default build reads no environment variable
   const char* v = getenv(name);
   return v ? uint32_t(strtoul(v, nullptr, 0)) : dflt;
 }
@@ -310,11 +307,10 @@ template <int BN>
 static cudaError_t launch_bn(const CUtensorMap& map_a, const CUtensorMap& map_w, GemmParams p, int sm_count,
                              cudaStream_t s) {
   using Cfg = TileCfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  if (once.first_use() >= 0) {  // the shared-memory opt-in is a per-device attribute of the function
     cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   static uint32_t diag = env_u32("TNF_GEMM_DIAG", 0);
   p.diag = diag;

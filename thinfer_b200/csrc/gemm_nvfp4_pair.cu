@@ -25,6 +25,7 @@
 #include <cstdint>
 #include <cstdlib>
 
+#include "epilogue.cuh"
 #include "internal.h"
 #include "ptx.cuh"
 #include "quant_dev.cuh"
@@ -71,18 +72,6 @@ struct PairOutMaps {
   CUtensorMap m[kMaxPeers];
 };
 
-__device__ __forceinline__ float gelu_tanh_fast(float x) {
-  // 0.5*x*(1+tanh(u)), u = sqrt(2/pi)*(x + 0.044715 x^3); tanh.approx (rel. error ~2^-11)
-  float u = x * (0.7978845608028654f + 0.035677408136300125f * x * x);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-  float hx = 0.5f * x;
-  return fmaf(hx, t, hx);
-}
-__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
-
 // 8 accumulator columns -> 8 bf16 (one 16-byte chunk of the staging row)
 template <bool kGelu, bool kChain, bool kGate>
 __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool has_bias, uint4 b4, uint4 g4, uint4 s4) {
@@ -100,7 +89,7 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool 
         if (kChain) x = bf16r(x);
       }
       if (kGelu) {
-        x = gelu_tanh_fast(x);
+        x = gelu_tanh<kChain>(x);
         if (kChain) x = bf16r(x);
       }
       if (kGate) x = fmaf(e ? bf16_hi(gw[h]) : bf16_lo(gw[h]), x, e ? bf16_hi(sw[h]) : bf16_lo(sw[h]));
@@ -216,11 +205,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
-  const bool ktr = (p.diag & 16u) && blockIdx.x == 0 && threadIdx.x == 0;
+  const bool ktr = kDiag && (p.diag & 16u) && blockIdx.x == 0 && threadIdx.x == 0;
   if (ktr) p.trace[1200] = clock64();
   const uint32_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const uint32_t tiles_m2 = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
   const uint32_t num_k_tiles = (p.k + kStageK - 1u) / kStageK;
+  const long long wait_limit = p.wait_limit > 0 ? p.wait_limit : kDefaultWaitLimitCycles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -263,14 +253,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         const int32_t sfa_row0 = int32_t((tm2 * 2u + rank) * p.k_atoms * 4u);
         const int32_t sfb_row0 = int32_t((uint32_t(n0) >> 7) * p.k_atoms * 4u);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout)) {
+          if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusProducerTimeout, wait_limit)) {
             ok = false;
             break;
           }
-          const bool tr = (p.diag & 16u) && rank == 0 && pair_id == 0 && titer < 256u;
-          const bool skip_ab = (p.diag & 8u) != 0u;
+          const bool tr = kDiag && (p.diag & 16u) && rank == 0 && pair_id == 0 && titer < 256u;
+          const bool skip_ab = kDiag && (p.diag & 8u) != 0u;
           const uint32_t full = mapa_cluster(bar_full + 8 * stage, 0);  // the leader's barrier counts both CTAs' bytes
-          if (elect_one()) {
+          // p.stall (wait self-test): nothing is loaded and no bytes are expected, so the MMA warp's first wait on a
+          // loaded stage runs out, raises the abort flag and every role leaves through the tear-down
+          if (!p.stall && elect_one()) {
             if (tr) p.trace[titer * 4 + 0] = clock64();
             if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * kStageBytes);
             if (!skip_ab) {
@@ -296,10 +288,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       uint32_t stage = 0, phase = 0, it = 0, titer = 0;
       bool ok = true;
       for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
-        const bool ttr = (p.diag & 16u) && pair_id == 0 && it < 16u && lane == 0;
+        const bool ttr = kDiag && (p.diag & 16u) && pair_id == 0 && it < 16u && lane == 0;
         if (ttr) p.trace[1024 + it * 8 + 0] = clock64();
         if (it > 0) {  // the previous tile's epilogues (both CTAs) have read the overlapping columns
-          if (!mbar_wait_warp(bar_acc_free, (it - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout)) {
+          if (!mbar_wait_warp(bar_acc_free, (it - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) {
             ok = false;
             break;
           }
@@ -308,12 +300,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (ttr) p.trace[1024 + it * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + (it & 1u) * kAccStride;
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout)) {
+          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const bool tr = (p.diag & 16u) && pair_id == 0 && titer < 256u;
+          const bool tr = kDiag && (p.diag & 16u) && pair_id == 0 && titer < 256u;
           if (elect_one()) {
           if (tr) p.trace[titer * 4 + 2] = clock64();
           const uint32_t a_addr = sA + stage * kABytes, b_addr = sB + stage * kBBytes;
@@ -322,14 +314,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
           // do not wait for the previous stage's MMAs to finish reading theirs
           const uint32_t sf_slot = Cfg::kSfSlots == 2 ? (kt & 1u) : 0u;
           const uint32_t t_sfa = tmem_base + kSfaCol + sf_slot * (KB * 4), t_sfb = tmem_base + kSfbCol + sf_slot * (KB * 8);
-          if (!(p.diag & 2u) || kt == 0)
+          if (!(kDiag && (p.diag & 2u)) || kt == 0)
 #pragma unroll
           for (int kb = 0; kb < KB; ++kb) {
             tc_cp_32x128b_warpx4_pair(t_sfa + kb * 4, make_desc_sf(sfa_addr + kb * 512));
             tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8, make_desc_sf(sfb_addr + kb * 512));
             tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8 + 4, make_desc_sf(sfb_addr + 512 * KB + kb * 512));
           }
-          if (!(p.diag & 4u))
+          if (!(kDiag && (p.diag & 4u)))
 #pragma unroll
           for (int kb = 0; kb < KB; ++kb)
             tc_mma_nvfp4_pair(d_tmem, make_desc_operand<KB>(a_addr + kb * 32), make_desc_operand<KB>(b_addr + kb * 32), idesc,
@@ -382,9 +374,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (n0 + g0 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g0 * 64u));
         if (n0 + g1 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g1 * 64u));
       }
-      const bool ttr = (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == 2;
+      const bool ttr = kDiag && (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == 2;
       if (ttr) p.trace[1024 + it * 8 + 3] = clock64();
-      if (!mbar_wait_bounded(bar_acc_full, it & 1u, abort_flag, kStatusEpilogueTimeout)) {
+      if (!mbar_wait_bounded(bar_acc_full, it & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
         ok = false;
         break;
       }
@@ -427,13 +419,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {
-          if (!(p.diag & 1u) && p.store_bf16) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
+          if (!(kDiag && (p.diag & 1u)) && p.store_bf16) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
           bulk_commit_group();
         }
         // Peer windows: coalesced 16-byte stores straight from the staging rows (8 lanes cover one
         // 128-byte row segment, a warp instruction writes 4 rows). TMA stores to peer memory reached
         // only ~160 GB/s per GPU with three peers; plain vector stores are what NVLink packs well.
-        if (p.n_out > 1u && !(p.diag & 1u)) {
+        if (p.n_out > 1u && !(kDiag && (p.diag & 1u))) {
           const uint32_t chunk = lane & 7u, col = ncol0 + chunk * 8u;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -469,13 +461,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
 }
 
 static uint32_t env_u32_pair(const char* name, uint32_t dflt) {
+  if (!kDiag) return dflt;  // the default build reads no environment variable
   const char* v = getenv(name);
   return v ? uint32_t(strtoul(v, nullptr, 0)) : dflt;
 }
 
 bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
   (void)k;
-  static uint32_t force = env_u32_pair("TNF_GEMM_KERNEL", 0);  // tuning knob: 1 = always 1-CTA, 2 = always pair
+  static uint32_t force = env_u32_pair("TNF_GEMM_KERNEL", 0);  // diagnostic builds: 1 = always 1-CTA, 2 = always pair
   if (force == 1) return false;
   if (force == 2) return true;
   // a pair works on a 256x256 tile; with few tiles (skinny M) the 1-CTA kernel's 128x128 tiles fill more SMs
@@ -483,7 +476,7 @@ bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
 }
 
 uint32_t gemm_pair_kblocks() {
-  static uint32_t v = env_u32_pair("TNF_GEMM_STAGE_K", 256) == 128 ? 2u : 4u;  // tuning knob: K elements per stage
+  static uint32_t v = env_u32_pair("TNF_GEMM_STAGE_K", 256) == 128 ? 2u : 4u;  // diagnostic builds: K elements per stage
   return v;
 }
 
@@ -492,9 +485,12 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p_in,
                                   int sm_count, cudaStream_t s) {
   using Cfg = PairCfg<KB>;
-  static bool attr_set = false;
-  static int max_pairs = 0;
-  if (!attr_set) {
+  static PerDeviceOnce once;
+  static int max_pairs[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (once.first_use() >= 0) {  // the shared-memory opt-in is a per-device attribute of the function
     cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -507,8 +503,7 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
       cudaGetLastError();
       clusters = sm_count / 2;
     }
-    max_pairs = std::min(clusters, sm_count / 2);
-    attr_set = true;
+    max_pairs[dev] = std::min(clusters, sm_count / 2);
   }
   GemmParams p = p_in;
   static uint32_t diag = env_u32_pair("TNF_GEMM_DIAG", 0);
@@ -517,7 +512,7 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
   p.tiles_n = (p.n + 255u) / 256u;
   const uint32_t tiles = p.tiles_m * p.tiles_n;
   if (tiles == 0) return cudaSuccess;
-  const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs));
+  const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs[dev] > 0 ? max_pairs[dev] : sm_count / 2));
   PairOutMaps om;
   for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
   return launch_pdl(nvfp4_gemm_pair_kernel<KB>, dim3(pairs * 2), dim3(pair::kThreads), Cfg::kSmemBytes, s, map_a, map_w, map_sfa,

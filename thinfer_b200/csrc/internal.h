@@ -35,6 +35,33 @@ inline uint64_t sf_device_bytes(uint32_t rows, uint32_t k) {
 }
 
 constexpr int kMaxPeers = 8;
+constexpr int kMaxDevices = 64;
+
+// Diagnostic variant of the library (clock64 traces, "skip this part" switches, kernel-selection
+// overrides from the environment): compiled only with -DTNF_GEMM_DIAG. In the default build every
+// `if (kDiag && ...)` below is removed by the compiler and the library reads no environment variable.
+#ifdef TNF_GEMM_DIAG
+constexpr bool kDiag = true;
+#else
+constexpr bool kDiag = false;
+#endif
+
+// Function attributes (dynamic shared memory opt-in, carve-out) belong to a device, not to the
+// process: launchers keep one of these per kernel and set the attributes on first use per device.
+struct PerDeviceOnce {
+  bool done[kMaxDevices] = {};
+  // index of the current device, or -1 when it has been seen before (or cannot be tracked)
+  int first_use() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;  // untracked: set every time
+    if (done[dev]) return -1;
+    done[dev] = true;
+    return dev;
+  }
+};
+
+// Default upper bound of a device-side mbarrier wait, in SM cycles (about two seconds).
+constexpr long long kDefaultWaitLimitCycles = 4000000000ll;
 
 // Device-side status word values (first failure wins).
 enum : uint32_t {
@@ -65,7 +92,9 @@ struct GemmParams {
   uint32_t q_k_atoms;          // sf_k_atoms(n)
   uint32_t store_bf16;         // 0: skip the bf16 store
   uint32_t* status;            // device status word
-  uint32_t diag;               // diagnostic bits from TNF_GEMM_DIAG (0 in normal use): 1 no output stores,
+  long long wait_limit;        // SM cycles after which a device-side wait gives up (0 = kDefaultWaitLimitCycles)
+  uint32_t stall;              // self-test: the producer issues no loads, so the first wait on a loaded stage runs out
+  uint32_t diag;               // diagnostic builds only (kDiag), bits from TNF_GEMM_DIAG: 1 no output stores,
                                // 2 scale copies only on the first K tile, 4 no MMA, 8 no operand loads,
                                // 16 record clock64 stamps of the first K tiles of pair 0 into `trace`
   unsigned long long* trace;   // 4 stamps per K tile (diag bit 16), 256 K tiles

@@ -131,6 +131,7 @@ int32_t tnf_linear_nvfp4_noalloc(tnf_ctx* ctx, const tnf_linear_args* a) {
   p.chain = a->parity_mode;
   p.store_bf16 = 1;
   p.status = ctx->dwords;
+  p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
 
   ce = launch_quantize(src, TNF_DTYPE_BF16, a->m, a->k, nullptr, a->a_global, a_codes, a_scales, true, ctx->compute);

@@ -66,8 +66,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
 
 // Warp-wide form: every lane polls, the outcome is made warp-uniform with a vote so that the
 // caller's control flow (and the address arithmetic after it) stays uniform.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t why) {
-  bool ok = mbar_wait_bounded(bar, parity, abort_flag, why);
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint32_t why,
+                                               long long limit_cycles = 4000000000ll) {
+  bool ok = mbar_wait_bounded(bar, parity, abort_flag, why, limit_cycles);
   return __all_sync(0xFFFFFFFFu, ok) != 0;
 }
 // One lane of a converged warp.

@@ -173,24 +173,24 @@ cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t 
   uint64_t threads = device_layout ? uint64_t((rows + 127u) & ~127u) * (k_atoms * 4u) : uint64_t(rows) * (k >> 4);
   if (threads == 0) return cudaSuccess;
   if (threads >= (uint64_t(1) << 32) - (uint64_t(1) << 20)) return cudaErrorInvalidValue;  // the kernel indexes blocks with 32 bits (one stride of headroom)
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-  }
+  static int sms_of[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (sms_of[dev] == 0 && (cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms_of[dev] <= 0))
+    sms_of[dev] = 148;
+  const int sms = sms_of[dev];
   // persistent: 8 warps per CTA, one 32-block round per warp and iteration, at most 6 CTAs per SM
   unsigned blocks = unsigned(std::min<uint64_t>((threads + 255) / 256, uint64_t(sms) * 6));
   // Keep the SMs in the same L1/shared-memory split as the GEMMs that run before and after (they take
   // the whole 227 KB as shared memory): a kernel that prefers L1 makes every following GEMM launch wait
   // for the split to be switched back.
-  static bool carveout_set = false;
-  if (!carveout_set) {
+  static PerDeviceOnce carveout;
+  if (carveout.first_use() >= 0) {  // a per-device attribute of each function
     cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(quantize_kernel<__nv_bfloat16, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(quantize_kernel<float, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(quantize_kernel<float, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    carveout_set = true;
   }
   if (dtype == 1) {
     auto* p = (const __nv_bfloat16*)src;
