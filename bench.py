@@ -738,7 +738,7 @@ def e2e_pipelined(be, step, x_buf, out_buf, in_bytes, out_bytes, host_in, host_o
     for i in range(n_steps):
         s = i % 2
         _check(lib.tnf_wait_event(ctx, up_ev[s]))                       # compute waits for this step's input
-        _check(lib.tnf_copy(ctx, x_stage[s].id, 0, x_buf.id, 0, in_bytes))
+        _check(lib.tnf_copy(ctx, x_stage[s].id, 0, x_buf.id, x_buf.offset, in_bytes))
         if i + 1 < n_steps:                                             # next input: the copy stream first waits for
             _check(lib.tnf_copy_after_compute(ctx))                     # the copy that last read that staging buffer
             ev = C.c_uint64()
@@ -747,7 +747,7 @@ def e2e_pipelined(be, step, x_buf, out_buf, in_bytes, out_bytes, host_in, host_o
         step()
         if down_ev[s] is not None:                                      # this output buffer's previous download is over
             _check(lib.tnf_wait_event(ctx, down_ev[s]))
-        _check(lib.tnf_copy(ctx, out_buf.id, 0, out_stage[s].id, 0, out_bytes))
+        _check(lib.tnf_copy(ctx, out_buf.id, out_buf.offset, out_stage[s].id, 0, out_bytes))
         ev = C.c_uint64()
         _check(lib.tnf_stream_download(ctx, out_stage[s].id, 0, host_out[s]["id"], 0, out_bytes, C.byref(ev)))
         down_ev[s] = ev.value
@@ -904,8 +904,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=60, help="layers in the single-GPU stack (60 = the named workload)")
-    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy", "nccl", "nvfp4", "push"],
-                    help="N>1: how slices reach every rank (auto: push = packed NVFP4/bf16 slices by contiguous copy-engine pushes up to 4 ranks, nvfp4 = the same bytes by NCCL all-gather beyond)")
+    ap.add_argument("--gather", default="auto", choices=["auto", "multimem", "fused", "copy", "nccl", "nvfp4", "push"],
+                    help="N>1: how slices reach every rank (auto: multimem = the producing kernels' epilogues store through the "
+                         "NVSwitch multicast alias; without multicast support, push = packed slices by copy-engine pushes up to 4 "
+                         "ranks and nvfp4 = the same bytes by NCCL all-gather beyond)")
     ap.add_argument("--bands", type=int, default=2, help="N>1 with --gather push/copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="stack", choices=["stack", "stream", "linear", "norm-quant"],

@@ -168,7 +168,13 @@ enum {
    * Requires n, n_offset and ldo to be multiples of 64; not combinable with gate_bf16 / residual_bf16
    * or TNF_LINEAR_SCATTER_PEERS. */
   TNF_LINEAR_OUT_NVFP4 = 4u,
-  TNF_LINEAR_NO_BF16_OUT = 8u     /* with OUT_NVFP4: skip the bf16 store (out_bf16 may have len 0) */
+  TNF_LINEAR_NO_BF16_OUT = 8u,    /* with OUT_NVFP4: skip the bf16 store (out_bf16 may have len 0) */
+  /* The outputs of this call (out_bf16, and out_codes / out_scales with OUT_NVFP4) live in buffers
+   * registered with tnf_import_symmetric: the epilogue stores them through the NVSwitch multicast
+   * alias (multimem.st), so every rank of the group receives this rank's column window at the same
+   * offsets while the GEMM is still running: the all-gather of an N-split output, fused into the
+   * kernel that produces it. Follow with a barrier across the ranks before the result is read. */
+  TNF_LINEAR_MULTICAST_OUT = 16u
 };
 
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);
@@ -362,6 +368,18 @@ int32_t tnf_interleave_cols(tnf_ctx* ctx, tnf_buf gathered, uint64_t rank_stride
 int32_t tnf_compute_after_copy(tnf_ctx* ctx);
 /* Stream-ordered barrier across the communicator (after a scatter epilogue). */
 int32_t tnf_comm_barrier(tnf_ctx* ctx);
+/* Registers a device range this library did not allocate as a buffer: `local_ptr` is this rank's copy
+ * of a symmetric allocation (same size and layout on every rank of the node) and `multicast_ptr`
+ * the NVSwitch multicast alias of the same range (0 if the platform has none; the multicast
+ * features then refuse the buffer). The range is charged to `category` but never freed here:
+ * tnf_free only forgets it. The reference is single-device and has no counterpart; the nearest
+ * idea is Backend::allocate_in (thinfer-core/src/backend/mod.rs:94-122) for memory owned elsewhere. */
+int32_t tnf_import_symmetric(tnf_ctx* ctx, void* local_ptr, void* multicast_ptr, uint64_t bytes, int32_t category,
+                             uint64_t* id);
+/* Copies `n` bytes of `src` to offset `dst_off` of the symmetric buffer `dst_id` on EVERY rank
+ * (this one included) with multicast stores; n, offsets 16-byte multiples. Asynchronous on the
+ * compute stream. Used to hand every rank this rank's row block of a quantised activation. */
+int32_t tnf_multicast_copy(tnf_ctx* ctx, tnf_buf src, uint64_t dst_id, uint64_t dst_off, uint64_t n);
 
 #ifdef __cplusplus
 }

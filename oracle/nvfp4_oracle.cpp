@@ -355,4 +355,17 @@ void orc_linear(const uint16_t* a, int64_t m, int64_t k, float g_a, int quantize
     orc_epilogue(acc.data(), m, n, scale, bias, act, gate, residual, chain, out);
 }
 
+// The same linear on an activation operand that is ALREADY NVFP4 (canonical codes [m,k/2] and scales
+// [m,k/16] with per-tensor scale g_a): what tnf_gemm_nvfp4 computes when the producing GEMM's epilogue
+// emitted its output quantised.
+void orc_linear_q(const uint8_t* a_codes, const uint8_t* a_scales, int64_t m, int64_t k, float g_a,
+                  const uint8_t* w_codes, const uint8_t* w_scales, float g_w, int64_t n, const uint16_t* bias,
+                  int act, const uint16_t* gate, const uint16_t* residual, int chain, uint16_t* out) {
+    std::vector<float> af(size_t(m) * k), wf(size_t(n) * k), acc(size_t(m) * n);
+    orc_dequant(a_codes, a_scales, 1.0f, m, k, af.data());
+    orc_dequant(w_codes, w_scales, 1.0f, n, k, wf.data());
+    orc_gemm_f32(af.data(), wf.data(), m, n, k, acc.data());
+    orc_epilogue(acc.data(), m, n, g_a * g_w, bias, act, gate, residual, chain, out);
+}
+
 }  // extern "C"

@@ -21,8 +21,11 @@ def build(force: bool = False) -> str:
 
 
 def _load():
-    if not os.path.exists(_SO):
-        build()
+    try:
+        build()  # recompiles when a source is newer than the library
+    except (OSError, subprocess.CalledProcessError):
+        if not os.path.exists(_SO):  # no compiler here: a prebuilt library is used as it is
+            raise
     lib = C.CDLL(_SO)
     f32p, u16p, u8p, i8p = (C.POINTER(t) for t in (C.c_float, C.c_uint16, C.c_uint8, C.c_int8))
     i64, f32, vp = C.c_int64, C.c_float, C.c_void_p
@@ -48,6 +51,7 @@ def _load():
         "orc_gemm_f64": (None, [vp, vp, i64, i64, i64, vp]),
         "orc_epilogue": (None, [vp, i64, i64, f32, vp, C.c_int, vp, vp, C.c_int, vp]),
         "orc_linear": (None, [vp, i64, i64, f32, C.c_int, vp, vp, f32, i64, vp, C.c_int, vp, vp, C.c_int, vp, vp]),
+        "orc_linear_q": (None, [vp, vp, i64, i64, f32, vp, vp, f32, i64, vp, C.c_int, vp, vp, C.c_int, vp]),
         "ref_f16_from_f32": (C.c_uint16, [f32]),
         "ref_f16_to_f32": (f32, [C.c_uint16]),
         "ref_lcg_fill": (None, [vp, i64, C.POINTER(C.c_uint64), f32]),
@@ -222,6 +226,21 @@ def linear(a_bf16, g_a, w_codes, w_scales, g_w, bias=None, act=0, gate=None, res
     _lib.orc_linear(_p(a), m, k, g_a, int(quantize_a), _p(w_codes), _p(w_scales), g_w, n, _p(bias),
                     act, _p(gate), _p(residual), int(chain), _p(out), _p(acc))
     return (out, acc) if return_acc else out
+
+
+def linear_q(a_codes, a_scales, g_a, w_codes, w_scales, g_w, bias=None, act=0, gate=None, residual=None, chain=False):
+    """The linear on an activation operand that is already NVFP4 (canonical layouts); bf16 bits [m, n]."""
+    a_codes, a_scales = _c(a_codes, np.uint8), _c(a_scales, np.uint8)
+    w_codes, w_scales = _c(w_codes, np.uint8), _c(w_scales, np.uint8)
+    m, k = a_codes.shape[0], a_codes.shape[1] * 2
+    n = w_codes.shape[0]
+    out = np.empty((m, n), np.uint16)
+    bias = None if bias is None else _c(bias, np.uint16)
+    gate = None if gate is None else _c(gate, np.uint16)
+    residual = None if residual is None else _c(residual, np.uint16)
+    _lib.orc_linear_q(_p(a_codes), _p(a_scales), m, k, g_a, _p(w_codes), _p(w_scales), g_w, n, _p(bias), act, _p(gate),
+                      _p(residual), int(chain), _p(out))
+    return out
 
 
 # ---- restated reference routines (pinned by the reference's own unit tests) ----------

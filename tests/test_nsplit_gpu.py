@@ -122,6 +122,110 @@ def _worker(rank, world, port, ret):
     dist.destroy_process_group()
 
 
+def _worker_multicast(rank, world, port, ret):
+    """The FFN pair with the all-gathers fused into the producing kernels (multicast stores through NVSwitch).
+    Slices are large enough for the CTA-pair kernel to run several tiles per pair. Every rank must end with the
+    bits the unsplit pair leaves on one GPU: H codes and scales, and y."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    import oracle as O
+    import thinfer_b200 as T
+    from thinfer_b200._lib import Buf
+    from thinfer_b200.backend import device_scales_bytes
+    from thinfer_b200.nsplit import MulticastFfn, NSplitGroup, column_partition, row_partition
+
+    m, hidden, ffn = 2350, 512, 4608  # ragged rows; per-rank slices of 2304 and 256 columns
+    x = O.f32_to_bf16(O.gaussian(m * hidden, 11).reshape(m, hidden))
+    w1 = (O.gaussian(ffn * hidden, 12) * np.float32(0.03)).reshape(ffn, hidden)
+    w2 = (O.gaussian(hidden * ffn, 13) * np.float32(0.03)).reshape(hidden, ffn)
+    b1 = O.f32_to_bf16(O.gaussian(ffn, 14) * np.float32(0.01))
+    b2 = O.f32_to_bf16(O.gaussian(hidden, 15) * np.float32(0.01))
+    w1c, w1s, g1 = O.quantize_weight(w1)
+    w2c, w2s, g2 = O.quantize_weight(w2)
+    ga_x, ga_h = O.global_scale(O.amax_bf16(x)), 0.0009765625
+    be = T.Backend(rank)
+    grp = NSplitGroup(be, rank, world)
+    uo, uw = column_partition(ffn, world)[rank]
+    do, dw = column_partition(hidden, world)[rank]
+    W1 = T.Nvfp4Weight.from_packed(be, w1c[uo:uo + uw], w1s[uo:uo + uw], g1, b1[uo:uo + uw])
+    W2 = T.Nvfp4Weight.from_packed(be, w2c[do:do + dw], w2s[do:do + dw], g2, b2[do:do + dw])
+    ok = True
+    try:
+        pair = MulticastFfn(grp, m, hidden, ffn, W1, W2, ga_x, ga_h)
+    except RuntimeError:
+        pair = None  # no multicast alias on this platform: nothing to test (every rank sees the same)
+    if pair is not None:
+        r0, rows = row_partition(m, world)[rank]
+        xb = be.upload(x[r0:r0 + rows])
+        for _ in range(2):  # twice: the second pass overwrites what the first delivered
+            pair.step(Buf(xb.id, 0, rows * hidden * 2))
+        be.submit(30000)
+        dist.barrier()
+        # the unsplit pair on this GPU
+        whole1 = T.Nvfp4Weight.from_packed(be, w1c, w1s, g1, b1)
+        whole2 = T.Nvfp4Weight.from_packed(be, w2c, w2s, g2, b2)
+        xf = be.upload(x)
+        qc, qs = be.allocate(m * ffn // 2), be.allocate(device_scales_bytes(m, ffn))
+        be.write_buffer(qs, np.zeros(qs.len, np.uint8))
+        yb = be.allocate(m * hidden * 2)
+        sc = be.scope()
+        sc.linear(xf, m, whole1, ga_x, None, act=1, out_nvfp4=(qc, qs, ga_h))
+        sc.matmul(qc, qs, m, whole2, ga_h, yb)
+        be.submit(30000)
+        ok = ok and np.array_equal(be.read_buffer(pair.hq_c.buf), be.read_buffer(qc))
+        ok = ok and np.array_equal(be.read_buffer(pair.hq_s.buf), be.read_buffer(qs))
+        y_got, y_one = be.read_buffer(pair.y.buf, np.uint16), be.read_buffer(yb, np.uint16)
+        ok = ok and np.array_equal(y_got, y_one)
+        # and against the oracle: down projection on the gathered H
+        from conftest import dev_scales_to_canonical
+        hc = be.read_buffer(pair.hq_c.buf).reshape(m, ffn // 2)
+        hs = dev_scales_to_canonical(be.read_buffer(pair.hq_s.buf), m, ffn)
+        want = O.linear_q(hc, hs, ga_h, w2c, w2s, g2, bias=b2)
+        g, e = O.bf16_to_f32(y_got.reshape(m, hidden)).astype(np.float64), O.bf16_to_f32(want).astype(np.float64)
+        ok = ok and bool(np.linalg.norm(g - e) / np.linalg.norm(e) <= 1e-3)
+    dist.barrier()
+    t = torch.tensor([1 if ok else 0, 0 if pair is None else 1], device=f"cuda:{rank}")
+    dist.all_reduce(t)
+    if rank == 0:
+        ret.put((int(t[0].item()), int(t[1].item())))
+    be.submit()
+    dist.barrier()  # no rank leaves while a peer may still write into its buffers
+    if pair is not None:
+        pair.free()
+    be.close()
+    dist.destroy_process_group()
+
+
+def _run_two(worker):
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    return ret.get(timeout=5)
+
+
+def test_two_gpu_multicast_ffn_pair():
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ok, ran = _run_two(_worker_multicast)
+    assert ok == 2
+    if ran == 0:
+        pytest.skip("the platform has no NVSwitch multicast alias for symmetric allocations")
+
+
 def test_two_gpu_scatter_and_gather():
     import torch
 

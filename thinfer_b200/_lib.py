@@ -15,7 +15,7 @@ CAT_WEIGHTS, CAT_WORKSPACE, CAT_STAGING = 0, 1, 2
 DTYPE_F32, DTYPE_BF16 = 0, 1
 SCALES_CANONICAL, SCALES_DEVICE = 0, 1
 ACT_NONE, ACT_GELU_TANH = 0, 1
-LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS, LINEAR_OUT_NVFP4, LINEAR_NO_BF16_OUT = 1, 2, 4, 8
+LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS, LINEAR_OUT_NVFP4, LINEAR_NO_BF16_OUT, LINEAR_MULTICAST_OUT = 1, 2, 4, 8, 16
 
 
 class Buf(C.Structure):
@@ -119,6 +119,8 @@ SIGNATURES = {
     "tnf_compute_after_copy": (C.c_int32, [_ctx]),
     "tnf_compute_after_push": (C.c_int32, [_ctx]),
     "tnf_comm_barrier": (C.c_int32, [_ctx]),
+    "tnf_import_symmetric": (C.c_int32, [_ctx, C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, _u64p]),
+    "tnf_multicast_copy": (C.c_int32, [_ctx, Buf, C.c_uint64, C.c_uint64, C.c_uint64]),
 }
 
 _lib = None

@@ -63,6 +63,17 @@ uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need, const char* name
   return static_cast<uint8_t*>(it->second.ptr) + b.offset;
 }
 
+uint8_t* resolve_multicast(tnf_ctx* ctx, const tnf_buf& b, const char* name, int32_t* status) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto it = ctx->bufs.find(b.id);
+  if (it == ctx->bufs.end() || !it->second.mc) {
+    set_error("%s: TNF_LINEAR_MULTICAST_OUT needs a buffer registered with tnf_import_symmetric that has a multicast alias", name);
+    *status = TNF_ERR_INVALID_ARGUMENT;
+    return nullptr;
+  }
+  return static_cast<uint8_t*>(it->second.mc) + b.offset;
+}
+
 int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id) {
   if (category < 0 || category > 2 || bytes == 0) {
     set_error("tnf_alloc: bad category %d or zero size", category);
@@ -96,8 +107,8 @@ int32_t free_locked(tnf_ctx* ctx, uint64_t id) {
     set_error("tnf_free: unknown buffer id %llu", (unsigned long long)id);
     return TNF_ERR_UNKNOWN_BUFFER;
   }
-  // cudaFree waits for work that may still use the memory
-  cudaError_t e = cudaFree(it->second.ptr);
+  // cudaFree waits for work that may still use the memory; an imported range is only forgotten
+  cudaError_t e = it->second.owned ? cudaFree(it->second.ptr) : cudaSuccess;
   ctx->live[it->second.category] -= it->second.bytes;
   // tensor maps over the freed range are dropped (a later buffer may reuse the address)
   for (auto m = ctx->maps.begin(); m != ctx->maps.end();) {
@@ -244,6 +255,15 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   }
   GemmParams p{};
   p.store_bf16 = store_bf16 ? 1u : 0u;
+  const bool mc_out = (a->flags & TNF_LINEAR_MULTICAST_OUT) != 0;
+  if (mc_out && ((a->flags & TNF_LINEAR_SCATTER_PEERS) || a->gate_bf16.len)) {
+    set_error("TNF_LINEAR_MULTICAST_OUT cannot be combined with TNF_LINEAR_SCATTER_PEERS or a gated residual");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (mc_out && store_bf16) {
+    p.out_mc = reinterpret_cast<uint16_t*>(resolve_multicast(ctx, a->out_bf16, "out_bf16", &st));
+    if (!p.out_mc) return st;
+  }
   if (q_out) {
     if (a->n % 64 != 0 || a->n_offset % 64 != 0 || ldo % 64 != 0 || !(a->out_global > 0.0f) ||
         (a->flags & TNF_LINEAR_SCATTER_PEERS) || a->gate_bf16.len) {
@@ -256,6 +276,12 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
     if (!p.q_codes) return st;
     p.q_scales = resolve(ctx, a->out_scales, sf_device_bytes(a->m, ldo), "out_scales", &st);
     if (!p.q_scales) return st;
+    if (mc_out) {
+      p.q_codes_mc = resolve_multicast(ctx, a->out_codes, "out_codes", &st);
+      if (!p.q_codes_mc) return st;
+      p.q_scales_mc = resolve_multicast(ctx, a->out_scales, "out_scales", &st);
+      if (!p.q_scales_mc) return st;
+    }
     p.q_global = a->out_global;
     p.q_inv_t = 1.0f / (6.0f * a->out_global);
     p.q_k_atoms = sf_k_atoms(ldo);
@@ -302,7 +328,7 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
   CUtensorMap ma, mw;
-  if (q_out || gemm_use_pair(a->m, a->n, a->k)) {
+  if (q_out || mc_out || gemm_use_pair(a->m, a->n, a->k)) {  // only the CTA-pair kernel has the NVFP4 and multicast epilogues
     const uint32_t kb = gemm_pair_kblocks();
     CUtensorMap msa, msb, outs[kMaxPeers];
     if (!get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb), &ma) || !get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb), &mw) ||
@@ -374,7 +400,8 @@ int32_t tnf_destroy(tnf_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaDeviceSynchronize();
   tnf_comm_teardown(ctx);
-  for (auto& kv : ctx->bufs) cudaFree(kv.second.ptr);
+  for (auto& kv : ctx->bufs)
+    if (kv.second.owned) cudaFree(kv.second.ptr);
   for (auto& kv : ctx->hosts) {
     if (kv.second.owned) cudaFreeHost(kv.second.ptr);
     else cudaHostUnregister(kv.second.ptr);

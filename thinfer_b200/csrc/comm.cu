@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "context.h"
+#include "ptx.cuh"
 
 namespace tnf {
 
@@ -80,14 +81,35 @@ __global__ void unpack_cols_kernel(const uint4* __restrict__ gathered, uint4* __
   out[uint64_t(r) * row_stride + uint64_t(w) * n_local + c] = gathered[uint64_t(w) * rank_stride + uint64_t(r) * src_row_stride + c];
 }
 
-static cudaError_t ensure_gather_tmp(tnf_ctx* ctx, uint64_t need) {
-  if (need <= ctx->gather_tmp_bytes) return cudaSuccess;
-  if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
+// Staging of the NCCL gathers (send slice + receive area). It is an ordinary workspace buffer of the context:
+// charged to the budget, visible in tnf_mem_snapshot, refused on the host when it does not fit.
+static int32_t ensure_gather_tmp(tnf_ctx* ctx, uint64_t need) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (need <= ctx->gather_tmp_bytes) return TNF_OK;
+  if (ctx->gather_tmp_id) free_locked(ctx, ctx->gather_tmp_id);
+  ctx->gather_tmp_id = 0;
   ctx->gather_tmp = nullptr;
   ctx->gather_tmp_bytes = 0;
-  cudaError_t e = cudaMalloc(&ctx->gather_tmp, need);
-  if (e == cudaSuccess) ctx->gather_tmp_bytes = need;
-  return e;
+  int32_t st = alloc_locked(ctx, need, TNF_CAT_WORKSPACE, &ctx->gather_tmp_id);
+  if (st != TNF_OK) return st;
+  ctx->gather_tmp = ctx->bufs[ctx->gather_tmp_id].ptr;
+  ctx->gather_tmp_bytes = need;
+  return TNF_OK;
+}
+
+// src (local) -> the multicast alias of a symmetric buffer: one 16-byte multimem store per thread and round
+__global__ void multicast_copy_kernel(const uint4* __restrict__ src, uint4* dst_mc, uint64_t n16) {
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += uint64_t(gridDim.x) * blockDim.x)
+    multimem_st_v4(dst_mc + i, __ldg(src + i));
+  __threadfence_system();
+}
+
+cudaError_t launch_multicast_copy(const uint8_t* src, uint8_t* dst_mc, uint64_t bytes, int sm_count, cudaStream_t s) {
+  const uint64_t n16 = bytes / 16;
+  if (n16 == 0) return cudaSuccess;
+  const unsigned blocks = unsigned(std::min<uint64_t>((n16 + 255) / 256, uint64_t(sm_count) * 8));
+  multicast_copy_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst_mc), n16);
+  return cudaGetLastError();
 }
 
 }  // namespace tnf
@@ -105,8 +127,8 @@ void tnf_comm_teardown(tnf_ctx* ctx) {
       if (ctx->peer_out[s][i]) cudaIpcCloseMemHandle(ctx->peer_out[s][i]);
     ctx->n_peers[s] = 0;
   }
-  if (ctx->gather_tmp) cudaFree(ctx->gather_tmp);
-  ctx->gather_tmp = nullptr;
+  ctx->gather_tmp = nullptr;  // the staging buffer is in the context's table and goes with it
+  ctx->gather_tmp_bytes = 0;
 }
 
 extern "C" {
@@ -159,8 +181,8 @@ int32_t tnf_all_gather_cols(tnf_ctx* ctx, tnf_buf out_bf16, uint32_t m, uint32_t
   if (!out) return st;
   NcclApi* api = nccl_api();
   const uint64_t slice = uint64_t(m) * n_local * 2;
-  e = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
+  st = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
+  if (st != TNF_OK) return st;
   uint8_t* send = static_cast<uint8_t*>(ctx->gather_tmp);
   uint8_t* recv = send + slice;
   const uint32_t nl8 = n_local / 8, nt8 = n_total / 8;
@@ -204,8 +226,8 @@ int32_t tnf_all_gather_nvfp4(tnf_ctx* ctx, tnf_buf codes, tnf_buf scales, uint32
   const uint32_t s_loc = (n_local / 64) * 32, s_tot = sf_k_atoms(n_total) * 32;
   const uint64_t c_units = uint64_t(m) * c_loc, s_units = uint64_t(row_blocks) * s_loc;
   const uint64_t slice = (c_units + s_units) * 16;
-  e = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
-  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(gather staging)");
+  st = ensure_gather_tmp(ctx, slice * (uint64_t(ctx->world) + 1));
+  if (st != TNF_OK) return st;
   uint4* send = static_cast<uint4*>(ctx->gather_tmp);
   uint4* recv = send + slice / 16;
   const uint32_t rank = uint32_t(ctx->rank), world = uint32_t(ctx->world);
@@ -466,6 +488,47 @@ int32_t tnf_compute_after_copy(tnf_ctx* ctx) {
     ctx->event_pool.push_back(ev);
   }
   if (e != cudaSuccess) return cuda_fail(e, "tnf_compute_after_copy");
+  return TNF_OK;
+}
+
+int32_t tnf_import_symmetric(tnf_ctx* ctx, void* local_ptr, void* multicast_ptr, uint64_t bytes, int32_t category, uint64_t* id) {
+  if (!ctx || !local_ptr || !id || bytes == 0 || category < 0 || category > 2 || (reinterpret_cast<uintptr_t>(local_ptr) & 255) ||
+      (reinterpret_cast<uintptr_t>(multicast_ptr) & 255)) {
+    set_error("tnf_import_symmetric: null or misaligned pointer (256-byte alignment), zero size or bad category");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const uint64_t nid = ctx->next_id++;
+  tnf_buffer_rec rec;
+  rec.ptr = local_ptr;
+  rec.bytes = bytes;
+  rec.category = category;
+  rec.owned = false;
+  rec.mc = multicast_ptr;
+  ctx->bufs[nid] = rec;
+  ctx->live[category] += bytes;  // accounted like any other buffer; the memory itself belongs to the caller
+  ctx->peak[category] = std::max(ctx->peak[category], ctx->live[category]);
+  ctx->true_peak = std::max(ctx->true_peak, ctx->live[0] + ctx->live[1] + ctx->live[2]);
+  *id = nid;
+  return TNF_OK;
+}
+
+int32_t tnf_multicast_copy(tnf_ctx* ctx, tnf_buf src, uint64_t dst_id, uint64_t dst_off, uint64_t n) {
+  if (!ctx || n == 0 || (n | dst_off | src.offset) % 16) {
+    set_error("tnf_multicast_copy: size and offsets must be non-zero multiples of 16 bytes");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  int32_t st = TNF_OK;
+  const uint8_t* from = resolve(ctx, src, n, "src", &st);
+  if (!from) return st;
+  tnf_buf dst{dst_id, dst_off, n};
+  if (!resolve(ctx, dst, n, "dst", &st)) return st;
+  uint8_t* mc = resolve_multicast(ctx, dst, "dst", &st);
+  if (!mc) return st;
+  e = launch_multicast_copy(from, mc, n, ctx->sm_count, ctx->compute);
+  if (e != cudaSuccess) return cuda_fail(e, "multicast copy launch");
   return TNF_OK;
 }
 

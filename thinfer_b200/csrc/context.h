@@ -18,6 +18,8 @@ struct tnf_buffer_rec {
   void* ptr = nullptr;
   uint64_t bytes = 0;
   int category = 0;
+  bool owned = true;   // false: registered with tnf_import_symmetric, never freed here
+  void* mc = nullptr;  // NVSwitch multicast alias of the same range (imported symmetric buffers only)
 };
 
 struct tnf_host_rec {
@@ -58,8 +60,8 @@ struct tnf_ctx {
   // NCCL
   void* nccl_comm = nullptr;
   int world = 1, rank = 0;
-  void* gather_tmp = nullptr;
-  uint64_t gather_tmp_bytes = 0;
+  void* gather_tmp = nullptr;   // staging of the NCCL gathers: a workspace buffer of the table (gather_tmp_id)
+  uint64_t gather_tmp_id = 0, gather_tmp_bytes = 0;
 };
 
 void tnf_comm_teardown(tnf_ctx* ctx);  // comm.cu
@@ -69,6 +71,8 @@ void set_error(const char* fmt, ...);
 int32_t cuda_fail(cudaError_t e, const char* what);
 // Looks a view up and checks its range; returns the device address or null (error set).
 uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need_bytes, const char* name, int32_t* status);
+// Multicast alias of a view already validated by resolve(); null (error set) if its buffer has none.
+uint8_t* resolve_multicast(tnf_ctx* ctx, const tnf_buf& b, const char* name, int32_t* status);
 int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id);
 int32_t free_locked(tnf_ctx* ctx, uint64_t id);
 bool get_map(tnf_ctx* ctx, const MapSpec& spec, CUtensorMap* out);  // copies the (cached) map out under the lock

@@ -34,19 +34,24 @@ namespace tnf {
 
 namespace pair {
 constexpr int kThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+// Which warps take which role. The epilogue warp with index e reads TMEM lane quarter (warp id & 3).
+#ifdef TNF_ROLES_LAST  // experiment: producer and MMA issuer in the last two warps instead of the first two
+constexpr int kProducerWarp = 8, kMmaWarp = 9, kFirstEpilogueWarp = 0;
+#else
+constexpr int kProducerWarp = 0, kMmaWarp = 1, kFirstEpilogueWarp = 2;
+#endif
 constexpr int kStagingBytes = 8 * 4096;  // 8 epilogue warps x (32 rows x 128 B)
-constexpr int kBiasBytes = 8 * 256;      // 8 epilogue warps x 128 bf16 bias values (the warp's two column groups)
+constexpr int kBiasBytes = 8 * 256;      // 8 epilogue warps x 64 f32 bias values (the column group being processed)
 constexpr int kLutBytes = 512;           // 1/(scale*g) per E4M3 code for the quantising epilogue
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 192;  // accumulator b starts at column b * 192
 constexpr uint32_t kSfaCol = 448, kSfbCol = 464;
 }  // namespace pair
 
-// KB = 64-element K blocks (one MMA each) per pipeline stage: 4 -> five 38 KB stages of 256 K
-// elements (128-byte swizzled rows), 2 -> ten 19 KB stages of 128 K elements (64-byte swizzled
-// rows). Same bytes in flight; the finer stages keep more of them in flight while one stage is
-// being consumed and let the scale factors of consecutive stages alternate between two TMEM slots.
-// Measured on B200: the finer stages are SLOWER (3.0 vs 4.3 PFLOP/s on 4352x12288x3072), so 4 is the default.
+// KB = 64-element K blocks (one MMA each) per pipeline stage. 4 is what the library uses: five 38 KB stages of
+// 256 K elements (128-byte swizzled rows). Ten 19 KB stages of 128 K elements (KB = 2) hold the same bytes
+// but were measured 45 % slower on B200 (98 against 67 us on 4352 x 3072 x 9216): the fixed cost per stage
+// (barrier round trip, twelve scale copies, commit) does not shrink with the stage.
 template <int KB>
 struct PairCfg {
   static constexpr int kStages = KB == 4 ? 5 : 10;
@@ -68,34 +73,45 @@ __device__ __forceinline__ uint64_t make_desc_operand(uint32_t saddr) {
          (kLayout << 61);
 }
 
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | lo; }
+
 struct PairOutMaps {
   CUtensorMap m[kMaxPeers];
 };
 
-// 8 accumulator columns -> 8 bf16 (one 16-byte chunk of the staging row)
+// 8 accumulator columns -> 8 bf16 (one 16-byte chunk of the staging row). `b8` points at the 8 bias values
+// in shared memory as f32 (zero without a bias); in the fused GELU variant alpha and the bias arrive halved.
+// The fused variants work on packed pairs (fma.rn.f32x2): one FMA applies alpha and the bias to two columns.
 template <bool kGelu, bool kChain, bool kGate>
-__device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool has_bias, uint4 b4, uint4 g4, uint4 s4) {
-  const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w}, gw[4] = {g4.x, g4.y, g4.z, g4.w}, sw[4] = {s4.x, s4.y, s4.z, s4.w};
+__device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, const float* b8, uint4 g4, uint4 s4) {
+  const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, sw[4] = {s4.x, s4.y, s4.z, s4.w};
+  const float4 bl = *reinterpret_cast<const float4*>(b8), bh = *reinterpret_cast<const float4*>(b8 + 4);
+  const float bv[8] = {bl.x, bl.y, bl.z, bl.w, bh.x, bh.y, bh.z, bh.w};
   uint32_t o[4];
 #pragma unroll
   for (int h = 0; h < 4; ++h) {
-    float v[2];
+    float v0, v1;
+    if (kChain) {  // the reference's op chain: every step rounded to bf16, accurate tanh
+      float v[2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      float x = __uint_as_float(r[2 * h + e]) * alpha;
-      if (kChain) x = bf16r(x);
-      if (has_bias) {
-        x += e ? bf16_hi(bw[h]) : bf16_lo(bw[h]);
-        if (kChain) x = bf16r(x);
+      for (int e = 0; e < 2; ++e) {
+        float x = bf16r(__uint_as_float(r[2 * h + e]) * alpha);
+        x = bf16r(x + bv[2 * h + e]);  // adding the zero of "no bias" changes nothing
+        if (kGelu) x = bf16r(gelu_tanh_exact(x));
+        v[e] = x;
       }
-      if (kGelu) {
-        x = gelu_tanh<kChain>(x);
-        if (kChain) x = bf16r(x);
-      }
-      if (kGate) x = fmaf(e ? bf16_hi(gw[h]) : bf16_lo(gw[h]), x, e ? bf16_hi(sw[h]) : bf16_lo(sw[h]));
-      v[e] = x;
+      v0 = v[0];
+      v1 = v[1];
+    } else {
+      uint64_t y2 = fma2(pack2u(r[2 * h], r[2 * h + 1]), pack2(alpha, alpha), pack2(bv[2 * h], bv[2 * h + 1]));
+      if (kGelu) y2 = gelu_tanh_fast2_half(y2);
+      unpack2(y2, v0, v1);
     }
-    __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
+    if (kGate) {
+      v0 = fmaf(bf16_lo(gw[h]), v0, bf16_lo(sw[h]));
+      v1 = fmaf(bf16_hi(gw[h]), v1, bf16_hi(sw[h]));
+    }
+    __nv_bfloat162 pk = __floats2bfloat162_rn(v0, v1);
     o[h] = *reinterpret_cast<uint32_t*>(&pk);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
@@ -105,8 +121,9 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, bool 
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
 template <bool kGelu, bool kChain, bool kGate, bool kQuant>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
-                                                   uint8_t* buf_gen, const uint4* bias_smem, const float* lut, int lane) {
+                                                   uint8_t* buf_gen, const float* bias_smem, const float* lut, int lane) {
   const bool row_ok = row < p.m;
+  const float alpha = (kGelu && !kChain) ? 0.5f * p.alpha : p.alpha;  // the fused GELU works on x/2
   // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes. Each 16-byte group of codes
   // is stored as soon as it is complete, so only four code words are live beside the accumulators
   // (holding all eight spilled, and the spill reloads, not the math, cost ~30 us on the MLP-up shape).
@@ -129,10 +146,9 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       const int j = sub * 4 + jj;
-      uint4 b4 = make_uint4(0, 0, 0, 0);
-      if (p.bias) b4 = bias_smem[j];  // staged per tile (zero past n); broadcast read
-      const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], p.alpha, p.bias != nullptr, b4, g4[jj], s4[jj]);
-      *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
+      const uint4 o = epilogue8<kGelu, kChain, kGate>(&r[j * 8], alpha, bias_smem + j * 8, g4[jj], s4[jj]);  // broadcast reads
+      if (!kQuant || p.store_bf16)  // with only the NVFP4 copy wanted, the bf16 rows are never staged
+        *reinterpret_cast<uint4*>(buf_gen + lane * 128 + ((j ^ (lane & 7)) << 4)) = o;
       if (kQuant) {  // quantise the bf16-ROUNDED values, 16 columns at a time
         if (jj & 1) {
           const uint32_t w[8] = {prev.x, prev.y, prev.z, prev.w, o.x, o.y, o.z, o.w};
@@ -146,14 +162,22 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
         }
       }
     }
-    if (q_on)
-      *reinterpret_cast<uint4*>(p.q_codes + uint64_t(row) * (p.ldo >> 1) + (qcol >> 1) + sub * 16) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    if (q_on && !(kDiag && (p.diag & 128u))) {
+      const uint64_t off = uint64_t(row) * (p.ldo >> 1) + (qcol >> 1) + sub * 16;
+      const uint4 v = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+      if (p.q_codes_mc) multimem_st_v4(p.q_codes_mc + off, v);  // every rank's copy of the operand, this one included
+      else *reinterpret_cast<uint4*>(p.q_codes + off) = v;
+    }
   }
-  if (q_on) *reinterpret_cast<uint32_t*>(p.q_scales + sf_device_offset(row, qcol >> 4, p.q_k_atoms)) = sw;
+  if (q_on && !(kDiag && (p.diag & 128u))) {
+    const uint64_t off = sf_device_offset(row, qcol >> 4, p.q_k_atoms);
+    if (p.q_scales_mc) multimem_st_b32(p.q_scales_mc + off, sw);
+    else *reinterpret_cast<uint32_t*>(p.q_scales + off) = sw;
+  }
 }
 
 __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
-                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const uint4* bias_smem,
+                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const float* bias_smem,
                                                        const float* lut, int lane) {
   switch (mode) {
     case 0: epilogue_pair_math<false, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
@@ -228,7 +252,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     prefetch_tensormap(&out_maps.m[0]);
   }
   if (p.q_codes) fill_inv_scale_lut(lut_gen, p.q_global, threadIdx.x, blockDim.x);
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tmem_alloc_pair(tmem_holder, kTmemCols);
     tmem_relinquish_pair();
   }
@@ -242,7 +266,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   pdl_wait();               // operands written by the previous kernel are complete and visible
   if (ktr) p.trace[1201] = clock64();
 
-  if (warp == 0) {
+  if (warp == kProducerWarp) {
     // ---------------- TMA producer (both CTAs): the whole warp runs the loop, one lane issues ----------------
     {
       uint32_t stage = 0, phase = 0, titer = 0;
@@ -250,6 +274,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
         const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
         const int32_t m0 = int32_t(tm2 * 256u + rank * 128u), n0 = int32_t(tn * 256u);
+        // A ragged last column tile runs a narrower MMA (n_eff columns, a multiple of 16): the pair's two halves
+        // of the W tile are then rows [n0, n0 + n_eff/2) and [n0 + n_eff/2, n0 + n_eff), so that accumulator
+        // column j is still output column n0 + j.
+        const uint32_t n_eff = min(256u, (p.n - uint32_t(n0) + 15u) & ~15u);
         const int32_t sfa_row0 = int32_t((tm2 * 2u + rank) * p.k_atoms * 4u);
         const int32_t sfb_row0 = int32_t((uint32_t(n0) >> 7) * p.k_atoms * 4u);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
@@ -264,10 +292,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
           // loaded stage runs out, raises the abort flag and every role leaves through the tear-down
           if (!p.stall && elect_one()) {
             if (tr) p.trace[titer * 4 + 0] = clock64();
-            if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * kStageBytes);
+            const bool skip_a = kDiag && (p.diag & 32u) != 0u;
+            if (rank == 0)
+              mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * (kStageBytes - (skip_a ? kABytes : 0)));
             if (!skip_ab) {
-              tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * Cfg::kRowBytes), m0);
-              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * Cfg::kRowBytes), n0 + int32_t(rank * 128u));
+              if (!skip_a) tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * Cfg::kRowBytes), m0);
+              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * Cfg::kRowBytes), n0 + int32_t(rank * (n_eff >> 1)));
             }
             tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * (KB * 4u)));
             tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * (KB * 4u)));
@@ -281,12 +311,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (rank == 0) {  // whole warp runs the loop; one elected lane issues the tcgen05 instructions
-      constexpr uint32_t idesc = make_idesc_nvfp4(256, 256);
+
+      // descriptor words of stage 0, K block 0 (see make_desc_operand / make_desc_sf); the loop only adds to the low word
+      const uint64_t op0 = make_desc_operand<KB>(sA), sf0 = make_desc_sf(sSfa);
+      const uint32_t op_hi = uint32_t(op0 >> 32), sf_hi = uint32_t(sf0 >> 32);
+      const uint32_t a_lo0 = uint32_t(op0), b_lo0 = uint32_t(make_desc_operand<KB>(sB));
+      const uint32_t sfa_lo0 = uint32_t(sf0), sfb_lo0 = uint32_t(make_desc_sf(sSfb));
       uint32_t stage = 0, phase = 0, it = 0, titer = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
         const bool ttr = kDiag && (p.diag & 16u) && pair_id == 0 && it < 16u && lane == 0;
         if (ttr) p.trace[1024 + it * 8 + 0] = clock64();
@@ -299,37 +334,62 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         }
         if (ttr) p.trace[1024 + it * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + (it & 1u) * kAccStride;
+        const uint32_t n_eff = min(256u, (p.n - (tile / tiles_m2) * 256u + 15u) & ~15u);  // as in the producer
+        const uint32_t idesc = make_idesc_nvfp4(256, n_eff);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
+          if (kDiag && (p.diag & 16u) && pair_id == 0 && titer < 256u && lane == 0) p.trace[1300 + titer] = clock64();
+          // `ready`: the probe issued one stage ago already saw this stage loaded (the usual case once the loads
+          // run ahead), so the warp goes straight to issuing; otherwise it waits here
+          if (!ready && !mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          // probe the NEXT stage now: the answer arrives while this stage's instructions are being issued
+          const uint32_t nstage = stage + 1u == uint32_t(S) ? 0u : stage + 1u;
+          const bool probe = mbar_test_wait(bar_full + 8 * nstage, nstage == 0u ? phase ^ 1u : phase);
           const bool tr = kDiag && (p.diag & 16u) && pair_id == 0 && titer < 256u;
           if (elect_one()) {
           if (tr) p.trace[titer * 4 + 2] = clock64();
-          const uint32_t a_addr = sA + stage * kABytes, b_addr = sB + stage * kBBytes;
-          const uint32_t sfa_addr = sSfa + stage * kSfaBytes, sfb_addr = sSfb + stage * kSfbBytes;
+          // Descriptors of this stage: the constant high words were built before the loop, a stage only moves the
+          // 14-bit start-address field (shared addresses are below 256 KB, so the add never carries out of it).
+          const uint32_t a_lo = a_lo0 + stage * uint32_t(kABytes >> 4), b_lo = b_lo0 + stage * uint32_t(kBBytes >> 4);
+          const uint32_t sfa_lo = sfa_lo0 + stage * uint32_t(kSfaBytes >> 4), sfb_lo = sfb_lo0 + stage * uint32_t(kSfbBytes >> 4);
           // scale factors of this stage: slot (kt & 1) when two slots exist, so that these copies
           // do not wait for the previous stage's MMAs to finish reading theirs
           const uint32_t sf_slot = Cfg::kSfSlots == 2 ? (kt & 1u) : 0u;
           const uint32_t t_sfa = tmem_base + kSfaCol + sf_slot * (KB * 4), t_sfb = tmem_base + kSfbCol + sf_slot * (KB * 8);
-          if (!(kDiag && (p.diag & 2u)) || kt == 0)
+          const bool do_cp = !(kDiag && (p.diag & 2u)) || kt == 0, do_mma = !(kDiag && (p.diag & 4u));
+          if (kDiag && (p.diag & 64u)) {  // diagnostic order: each K block's scale copies right before its MMA
 #pragma unroll
-          for (int kb = 0; kb < KB; ++kb) {
-            tc_cp_32x128b_warpx4_pair(t_sfa + kb * 4, make_desc_sf(sfa_addr + kb * 512));
-            tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8, make_desc_sf(sfb_addr + kb * 512));
-            tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8 + 4, make_desc_sf(sfb_addr + 512 * KB + kb * 512));
+            for (int kb = 0; kb < KB; ++kb) {
+              if (do_cp) {
+                tc_cp_32x128b_warpx4_pair(t_sfa + kb * 4, desc64(sfa_lo + kb * 32, sf_hi));
+                tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8, desc64(sfb_lo + kb * 32, sf_hi));
+                tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8 + 4, desc64(sfb_lo + 32 * KB + kb * 32, sf_hi));
+              }
+              if (do_mma)
+                tc_mma_nvfp4_pair(d_tmem, desc64(a_lo + kb * 2, op_hi), desc64(b_lo + kb * 2, op_hi), idesc, t_sfa + kb * 4,
+                                  t_sfb + kb * 8, (kt | uint32_t(kb)) != 0u);
+            }
+          } else {
+            if (do_cp)
+#pragma unroll
+              for (int kb = 0; kb < KB; ++kb) {
+                tc_cp_32x128b_warpx4_pair(t_sfa + kb * 4, desc64(sfa_lo + kb * 32, sf_hi));
+                tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8, desc64(sfb_lo + kb * 32, sf_hi));
+                tc_cp_32x128b_warpx4_pair(t_sfb + kb * 8 + 4, desc64(sfb_lo + 32 * KB + kb * 32, sf_hi));
+              }
+            if (do_mma)
+#pragma unroll
+              for (int kb = 0; kb < KB; ++kb)
+                tc_mma_nvfp4_pair(d_tmem, desc64(a_lo + kb * 2, op_hi), desc64(b_lo + kb * 2, op_hi), idesc, t_sfa + kb * 4,
+                                  t_sfb + kb * 8, (kt | uint32_t(kb)) != 0u);
           }
-          if (!(kDiag && (p.diag & 4u)))
-#pragma unroll
-          for (int kb = 0; kb < KB; ++kb)
-            tc_mma_nvfp4_pair(d_tmem, make_desc_operand<KB>(a_addr + kb * 32), make_desc_operand<KB>(b_addr + kb * 32), idesc,
-                              t_sfa + kb * 4, t_sfb + kb * 8, (kt | uint32_t(kb)) != 0u);
           tc_commit_pair_mc(bar_empty + 8 * stage, 3);  // frees the stage in both CTAs
           if (tr) p.trace[titer * 4 + 3] = clock64();
           }
-          __syncwarp();
+          ready = __all_sync(0xFFFFFFFFu, probe) != 0;
           ++titer;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
@@ -343,10 +403,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     // Warp w reads TMEM lanes [32*(w%4), +32). Two warps share a lane quarter: the one with
     // h == 0 takes the first two 64-column groups in drain order (the first of which overlaps the
     // other accumulator), h == 1 the last two.
-    const uint32_t q = warp & 3, h = uint32_t(warp - 2) >> 2;
-    const uint32_t buf = sStaging + uint32_t(warp - 2) * 4096u;
+    const uint32_t ew = uint32_t(warp - kFirstEpilogueWarp);  // 0..7
+    const uint32_t q = warp & 3, h = ew >> 2;
+    const uint32_t buf = sStaging + ew * 4096u;
     uint8_t* buf_gen = smem_gen + (buf - smem_base);
-    uint4* bias_gen = reinterpret_cast<uint4*>(smem_gen + (sBias - smem_base) + uint32_t(warp - 2) * 256u);
+    float* bias_gen = reinterpret_cast<float*>(smem_gen + (sBias - smem_base) + ew * 256u);  // 64 f32: the current group's bias
+    const float bias_mul = (p.act == 1u && !p.chain) ? 0.5f : 1.0f;                          // the fused GELU works on x/2
     const uint32_t acc_free_leader = mapa_cluster(bar_acc_free, 0);
     uint32_t it = 0;
     bool ok = true;
@@ -358,23 +420,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       const uint32_t b = it & 1u;
       const uint32_t first = b ? 0u : 3u;  // 64-column group that overlaps the other accumulator
       const uint32_t g0 = (2u * h + first) & 3u, g1 = (2u * h + 1u + first) & 3u;
-      // stage this warp's 2 x 64 bias values in shared memory while the main loop is still running:
-      // lanes 0-7 fetch group g0, lanes 8-15 group g1, 16 bytes each (zero past n)
+      // this warp's 2 x 64 bias values: every lane fetches two columns of each group now, while the main loop
+      // is still running; they go to shared memory as f32 right before the group's arithmetic
+      uint32_t bq0 = 0u, bq1 = 0u;
       if (p.bias) {
-        __syncwarp();  // the previous tile's reads of the staging area are done
-        if (lane < 16) {
-          const uint32_t nc = n0 + ((lane >> 3) ? g1 : g0) * 64u + (lane & 7u) * 8u;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (nc < p.n) v = __ldg(reinterpret_cast<const uint4*>(p.bias + nc));
-          bias_gen[lane] = v;
-        }
-        __syncwarp();
+        const uint32_t nc0 = n0 + g0 * 64u + uint32_t(lane) * 2u, nc1 = n0 + g1 * 64u + uint32_t(lane) * 2u;
+        if (nc0 < p.n) bq0 = __ldg(reinterpret_cast<const uint32_t*>(p.bias + nc0));
+        if (nc1 < p.n) bq1 = __ldg(reinterpret_cast<const uint32_t*>(p.bias + nc1));
       }
       if (lane == 0 && p.gate) {
         if (n0 + g0 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g0 * 64u));
         if (n0 + g1 * 64u < p.n) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.gate + n0 + g1 * 64u));
       }
-      const bool ttr = kDiag && (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == 2;
+      const bool ttr = kDiag && (p.diag & 16u) && pair_id == 0 && rank == 0 && it < 16u && lane == 0 && warp == kFirstEpilogueWarp;
       if (ttr) p.trace[1024 + it * 8 + 3] = clock64();
       if (!mbar_wait_bounded(bar_acc_full, it & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
         ok = false;
@@ -413,14 +471,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         }
         const uint32_t ncol0 = n0 + g * 64u;
         if (row0 >= p.m || ncol0 >= p.n) continue;  // warp-uniform
+        if (kDiag && (p.diag & 256u)) continue;      // diagnostic: drain the accumulator only
         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
+        __syncwarp();                              // ... and every lane its reads of the previous group's bias
+        const uint32_t bq = half ? bq1 : bq0;
+        *reinterpret_cast<float2*>(bias_gen + lane * 2) = make_float2(bf16_lo(bq) * bias_mul, bf16_hi(bq) * bias_mul);
         __syncwarp();
-        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen + half * 8, lut_gen, lane);
+        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen, lut_gen, lane);
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {
-          if (!(kDiag && (p.diag & 1u)) && p.store_bf16) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
+          if (!(kDiag && (p.diag & 1u)) && p.store_bf16 && !p.out_mc) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
           bulk_commit_group();
+        }
+        // Multicast output: the staging rows leave as 16-byte multimem stores (8 lanes cover one 128-byte row
+        // segment, a warp instruction writes 4 rows); the switch delivers them to every rank's copy of the output,
+        // this rank's included, so there is no separate local store and no gather pass afterwards.
+        if (p.out_mc && p.store_bf16) {
+          const uint32_t chunk = lane & 7u, col = ncol0 + chunk * 8u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t rr = uint32_t(i) * 4u + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(buf_gen + rr * 128u + ((chunk ^ (rr & 7u)) << 4));
+            if (row0 + rr < p.m && col < p.n) multimem_st_v4(p.out_mc + uint64_t(row0 + rr) * p.ldo + p.n_offset + col, v);
+          }
         }
         // Peer windows: coalesced 16-byte stores straight from the staging rows (8 lanes cover one
         // 128-byte row segment, a warp instruction writes 4 rows). TMA stores to peer memory reached
@@ -441,6 +515,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       if (ttr) p.trace[1024 + it * 8 + 6] = clock64();
     }
     if (lane == 0) bulk_wait_group_read<0>();
+    if (p.out_mc || p.q_codes_mc) __threadfence_system();  // multicast stores are performed before the kernel ends
   }
 
   // ---------------- tear-down ----------------
@@ -453,7 +528,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   }
   cluster_arrive();
   cluster_wait();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
@@ -475,10 +550,7 @@ bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
   return m > 128 && uint64_t((m + 255u) / 256u) * ((n + 255u) / 256u) >= 32u;
 }
 
-uint32_t gemm_pair_kblocks() {
-  static uint32_t v = env_u32_pair("TNF_GEMM_STAGE_K", 256) == 128 ? 2u : 4u;  // diagnostic builds: K elements per stage
-  return v;
-}
+uint32_t gemm_pair_kblocks() { return 4u; }
 
 template <int KB>
 static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
@@ -522,8 +594,7 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
 cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
                                    const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
                                    int sm_count, cudaStream_t s) {
-  return gemm_pair_kblocks() == 4 ? launch_pair_kb<4>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s)
-                                  : launch_pair_kb<2>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s);
+  return launch_pair_kb<4>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s);
 }
 
 }  // namespace tnf

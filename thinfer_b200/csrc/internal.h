@@ -90,6 +90,9 @@ struct GemmParams {
   uint8_t* q_scales;           // ... and device-layout scales of an [m, n] operand
   float q_global, q_inv_t;     // its per-tensor scale g and 1/(6g)
   uint32_t q_k_atoms;          // sf_k_atoms(n)
+  uint16_t* out_mc;            // multicast alias of out[0] (null: plain stores); with it every store of the epilogue
+  uint8_t* q_codes_mc;         //   (bf16 rows, NVFP4 codes, scale words) goes out as multimem.st and lands on
+  uint8_t* q_scales_mc;        //   every rank of the group, this one included
   uint32_t store_bf16;         // 0: skip the bf16 store
   uint32_t* status;            // device status word
   long long wait_limit;        // SM cycles after which a device-side wait gives up (0 = kDefaultWaitLimitCycles)
@@ -104,6 +107,7 @@ cudaError_t launch_amax(const void* x, int dtype, uint64_t n, uint32_t* amax_bit
 cudaError_t launch_global_scale(const uint32_t* amax_bits, float* g, cudaStream_t s);
 cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t k, const float* g_ptr, float g_val,
                             uint8_t* codes, uint8_t* scales, bool device_layout, cudaStream_t s);
+cudaError_t launch_multicast_copy(const uint8_t* src, uint8_t* dst_mc, uint64_t bytes, int sm_count, cudaStream_t s);
 cudaError_t launch_scales_to_device(const uint8_t* in, uint32_t rows, uint32_t k, uint8_t* out, cudaStream_t s);
 
 // tcgen05 GEMM. a_codes [m, k/2], w_codes [n, k/2]; tensor maps are built (and cached) by the caller.

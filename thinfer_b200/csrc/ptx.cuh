@@ -44,6 +44,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (mbarrier.test_wait returns at once; try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. Gives up after ~limit_cycles SM cycles or as soon as *abort_flag (shared)
 // is non-zero; on giving up it raises the flag so that every other role leaves too.
 // Returns false when it gave up.
@@ -195,6 +208,18 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 template <int N>
 __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// ---- NVSwitch multicast stores -----------------------------------------------------------------------
+// A store to the multicast alias of a symmetric allocation is replicated by the switch into every
+// rank's copy at the same offset (bits are moved unchanged; the .f32 type only names the width).
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_b32(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(__uint_as_float(v)) : "memory");
 }
 
 // ---- tcgen05, CTA-pair forms ------------------------------------------------------------------

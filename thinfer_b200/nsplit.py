@@ -146,3 +146,123 @@ class PackedGather:
             src = Buf(self.recv.id, self.recv.offset + self.main_cap, self.recv.len - self.main_cap)
             _check(lib.tnf_interleave_cols(ctx, src, self.slot, self.scale_block, g.world, out_scales, k_atoms * 512,
                                            (self.m + 127) // 128, (self.n_local // 64) * 512))
+
+
+def row_partition(m: int, world: int, align: int = 128) -> List[Tuple[int, int]]:
+    """(row0, rows) of each rank's block of the activations: equal blocks of a multiple of `align` rows (a scale
+    atom of the device layout covers 128 rows), the last one takes what is left (possibly nothing)."""
+    per = ((m + world - 1) // world + align - 1) // align * align
+    out = []
+    for g in range(world):
+        r0 = min(g * per, m)
+        out.append((r0, min(per, m - r0)))
+    return out
+
+
+class SymmetricBuffer:
+    """Device memory that exists with the same size on every rank of the node, plus its NVSwitch multicast
+    alias: a store to the alias lands in every rank's copy at the same offset. The allocation and the exchange
+    of handles between the processes are torch's (``torch.distributed._symmetric_memory``); the library only
+    receives the two addresses (``tnf_import_symmetric``). Collective: every rank must create the same
+    buffers in the same order."""
+
+    def __init__(self, grp: NSplitGroup, nbytes: int, category: int = L.CAT_WORKSPACE, zero: bool = True):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        be = grp.be
+        self.grp = grp
+        self.nbytes = (nbytes + 255) // 256 * 256
+        self.tensor = symm.empty(self.nbytes, dtype=torch.uint8, device=f"cuda:{be.device}")
+        if zero:
+            self.tensor.zero_()
+            torch.cuda.synchronize()
+        self.handle = symm.rendezvous(self.tensor, dist.group.WORLD)
+        self.multicast_ptr = int(self.handle.multicast_ptr or 0)
+        bid = C.c_uint64()
+        _check(be.lib.tnf_import_symmetric(be._ctx, C.c_void_p(self.tensor.data_ptr()), C.c_void_p(self.multicast_ptr),
+                                           self.nbytes, category, C.byref(bid)))
+        self.buf = Buf(bid.value, 0, nbytes)
+
+    @property
+    def has_multicast(self) -> bool:
+        return self.multicast_ptr != 0
+
+    def barrier(self, channel: int = 0) -> None:
+        """Stream-ordered barrier of the ranks on the library's compute stream (signal pads of this buffer)."""
+        import torch
+
+        be = self.grp.be
+        stream = torch.cuda.ExternalStream(be.streams()[0], device=f"cuda:{be.device}")
+        with torch.cuda.stream(stream):
+            self.handle.barrier(channel=channel)
+
+    def free(self) -> None:
+        if self.buf is not None:
+            self.grp.be.free(self.buf)  # the library forgets the range; torch owns the memory
+            self.buf = None
+
+
+class MulticastFfn:
+    """The N-split FFN pair (up + bias + GELU, down + bias) with each all-gather fused into the kernel that
+    produces the data: rank g holds the column slices ``w_up`` [ffn/G, hidden] and ``w_dn`` [hidden/G, ffn];
+
+      1. every rank quantises ITS row block of x and stores the codes and scales through the multicast alias,
+         so that all ranks hold the whole NVFP4 operand (x is quantised once per step, not once per rank);
+      2. the up GEMM's epilogue quantises its GELU output and stores its column window of H (codes + scales)
+         through the multicast alias while the GEMM is still running;
+      3. the down GEMM's epilogue does the same with its window of the bf16 output y.
+
+    A barrier of the ranks follows each stage. Every rank ends with the full H (NVFP4) and the full y (bf16),
+    which is what an all-gather after each linear would leave, bit for bit."""
+
+    def __init__(self, grp: NSplitGroup, m: int, hidden: int, ffn: int, w_up, w_dn, ga_x: float, ga_h: float):
+        from .backend import device_scales_bytes
+
+        be = grp.be
+        self.grp, self.m, self.hidden, self.ffn = grp, m, hidden, ffn
+        self.w_up, self.w_dn, self.ga_x, self.ga_h = w_up, w_dn, ga_x, ga_h
+        self.up_off, self.up_w = column_partition(ffn, grp.world)[grp.rank]
+        self.dn_off, self.dn_w = column_partition(hidden, grp.world)[grp.rank]
+        if self.up_w % 64 or self.up_off % 64:
+            raise ValueError("the NVFP4 copy of H moves in whole 64-column groups: ffn / world must be a multiple of 64")
+        self.row0, self.rows = row_partition(m, grp.world)[grp.rank]
+        self.xq_c = SymmetricBuffer(grp, m * hidden // 2)
+        self.xq_s = SymmetricBuffer(grp, device_scales_bytes(m, hidden))
+        self.hq_c = SymmetricBuffer(grp, m * ffn // 2)
+        self.hq_s = SymmetricBuffer(grp, device_scales_bytes(m, ffn))
+        self.y = SymmetricBuffer(grp, m * hidden * 2)
+        if not self.y.has_multicast:
+            raise RuntimeError("this platform gave the symmetric allocation no multicast alias (no NVSwitch multicast)")
+        self.x_scale_block = device_scales_bytes(128, hidden)  # bytes of one 128-row block of x's scales
+        rows_cap = max(self.rows, 1)
+        self.stage_c = be.allocate(max(rows_cap * hidden // 2, 256))
+        self.stage_s = be.allocate(device_scales_bytes(rows_cap, hidden))
+
+    def step(self, x_rows: Buf) -> None:
+        """One pass. ``x_rows`` is this rank's row block of x (bf16 [rows, hidden], rows from ``row_partition``)."""
+        be, lib, ctx = self.grp.be, self.grp.be.lib, self.grp.be._ctx
+        sc = be.scope()
+        if self.rows:
+            g = C.c_float()
+            _check(lib.tnf_quantize_act(ctx, x_rows, self.rows, self.hidden, self.ga_x, L.SCALES_DEVICE, self.stage_c,
+                                        self.stage_s, None))
+            _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_c.id, 0, self.rows * self.hidden // 2), self.xq_c.buf.id,
+                                          self.row0 * self.hidden // 2, self.rows * self.hidden // 2))
+            nblk = (self.rows + 127) // 128
+            _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_s.id, 0, nblk * self.x_scale_block), self.xq_s.buf.id,
+                                          (self.row0 // 128) * self.x_scale_block, nblk * self.x_scale_block))
+        self.y.barrier(0)
+        sc.matmul(self.xq_c.buf, self.xq_s.buf, self.m, self.w_up, self.ga_x, None, act=L.ACT_GELU_TANH, n_offset=self.up_off,
+                  ldo=self.ffn, flags=L.LINEAR_MULTICAST_OUT, out_nvfp4=(self.hq_c.buf, self.hq_s.buf, self.ga_h))
+        self.y.barrier(1)
+        sc.matmul(self.hq_c.buf, self.hq_s.buf, self.m, self.w_dn, self.ga_h, self.y.buf, n_offset=self.dn_off, ldo=self.hidden,
+                  flags=L.LINEAR_MULTICAST_OUT)
+        self.y.barrier(0)
+
+    def free(self) -> None:
+        for b in (self.xq_c, self.xq_s, self.hq_c, self.hq_s, self.y):
+            b.free()
+        for b in (self.stage_c, self.stage_s):
+            self.grp.be.free(b)
