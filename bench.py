@@ -295,7 +295,7 @@ def make_weight(be, T, L, gen, n, k, sigma=0.02, with_bias=True):
 # --------------------------------------------------------------------------------------------
 # single launch shapes (also what the ncu captures under profiles/ run)
 # --------------------------------------------------------------------------------------------
-def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, out_nvfp4=False, seed=1234):
+def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=False, out_nvfp4=False, seed=1234, dense=False):
     """Average launch times of one linear shape through the C ABI: the activation quantiser and the GEMM with its
     fused epilogue, CUDA events on the library's compute stream. With flush_l2 a 256 MB buffer is overwritten
     between iterations (untimed) so that a small problem is read from HBM every time."""
@@ -309,6 +309,9 @@ def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=Fal
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)
     W = make_weight(be, T, L, gen, n, k)
+    if dense:  # the dense-activation arm: bf16 activations against the weight's dense image, no quantiser launch
+        W.prepare_dense(be)
+        quant = False
     a = be.allocate(max(m * k * 2, 256))
     as_torch(be, a, torch.bfloat16, (max(m * k, 128),))[: m * k].copy_(torch.randn(m * k, device=dev, generator=gen).to(torch.bfloat16))
     out = be.allocate(max(m * n * 2, 256))
@@ -328,10 +331,13 @@ def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=Fal
             torch.cuda.synchronize()
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         e[0].record(stream)
-        if quant or it == 0:
+        if (quant or it == 0) and not dense:
             sc.act_quant_shared(a, m, k, ga)
         e[1].record(stream)
-        sc.linear(None, m, W, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED, out_nvfp4=q_out)
+        if dense:
+            sc.linear(a, m, W, ga, out, act=act, out_nvfp4=q_out, dense_act=True)
+        else:
+            sc.linear(None, m, W, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED, out_nvfp4=q_out)
         e[2].record(stream)
         be.submit(60000)
         torch.cuda.synchronize()
@@ -341,7 +347,7 @@ def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=Fal
     flops = 2.0 * m * n * k
     gemm_ms, quant_ms = float(np.mean(tg)), float(np.mean(tq))
     res = {
-        "m": m, "n": n, "k": k, "act": act, "out_nvfp4": bool(out_nvfp4), "iters": iters, "flush_l2": bool(flush_l2),
+        "m": m, "n": n, "k": k, "act": act, "out_nvfp4": bool(out_nvfp4), "dense_act": bool(dense), "iters": iters, "flush_l2": bool(flush_l2),
         "gemm_ms": gemm_ms, "gemm_ms_min": float(np.min(tg)), "quant_ms": quant_ms if quant else None,
         "gemm_tflops": flops / (gemm_ms * 1e-3) / 1e12,
         "linear_tflops": flops / ((gemm_ms + (quant_ms if quant else 0.0)) * 1e-3) / 1e12,
@@ -355,6 +361,53 @@ def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=Fal
         be.free(b)
     W.free(be)
     return res
+
+
+def time_linear_rotating(be, m, n, k, act=0, rounds=5):
+    """A skinny (HBM-bound) linear measured the way it runs inside a step: launches back to back on the stream,
+    no host synchronisation between them, each one on a DIFFERENT weight of the same shape, enough copies that
+    their bytes exceed twice the L2 (so every launch reads its weight from HBM). One event pair around the whole
+    train; the time per launch is the quantiser + GEMM pair's device time including launch overlap."""
+    import torch
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+
+    sc = be.scope()
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    w_bytes = n * k // 2 + n * k // 16
+    copies = int(max(4, min(64, -(-(2 * 126 << 20) // w_bytes))))
+    ws = [make_weight(be, T, L, gen, n, k) for _ in range(copies)]
+    a = be.allocate(max(m * k * 2, 256))
+    as_torch(be, a, torch.bfloat16, (max(m * k, 128),))[: m * k].copy_(torch.randn(m * k, device=dev, generator=gen).to(torch.bfloat16))
+    out = be.allocate(max(m * n * 2, 256))
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    ga = 0.002
+
+    def train():
+        for w in ws:
+            sc.linear(a, m, w, ga, out, act=act)
+
+    train()
+    be.submit()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(rounds):
+        train()
+    e1.record(stream)
+    be.submit()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (rounds * copies)
+    min_bytes = 2 * m * k + m * k // 2 + m * k // 16 + w_bytes + 2 * n + 2 * m * n  # bf16 A in, quantised A, weight, bias, out
+    for b in (a, out):
+        be.free(b)
+    for w in ws:
+        w.free(be)
+    return {"us_per_linear": us, "launches_per_linear": 2, "copies": copies, "min_bytes": min_bytes, "gbs": min_bytes / (us * 1e-6) / 1e9,
+            "tflops": 2.0 * m * n * k / (us * 1e-6) / 1e12}
 
 
 def time_norm_quant(be, m, k, iters=20, warmup=3):
@@ -400,7 +453,7 @@ def run_launch_workload(args):
         res = time_norm_quant(be, args.m, args.k, args.iters, args.warmup)
     else:
         res = time_linear(be, args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
-                          args.out_nvfp4)
+                          args.out_nvfp4, dense=args.dense_act)
     be.close()
     print(json.dumps(res))
 
@@ -456,18 +509,28 @@ def other_shapes(be):
     fp4 = 4.0 * peaks["bf16_sustained"]
     out = {}
 
-    def tensor(name, r):
-        out[name] = {"gemm_us": r["gemm_ms"] * 1e3, "quant_us": r["quant_ms"] * 1e3, "tflops": r["gemm_tflops"], "bound": "tensor",
-                     "frac": r["gemm_tflops"] / fp4}
+    def tensor(name, r, peak=fp4):
+        out[name] = {"gemm_us": r["gemm_ms"] * 1e3, "quant_us": (r["quant_ms"] or 0.0) * 1e3, "tflops": r["gemm_tflops"], "bound": "tensor",
+                     "frac": r["gemm_tflops"] / peak}
 
-    def hbm(name, r):
-        out[name] = {"gemm_us": r["gemm_ms"] * 1e3, "quant_us": r["quant_ms"] * 1e3, "tflops": r["gemm_tflops"], "bound": "hbm",
-                     "min_bytes": r["gemm_min_bytes"], "gbs": r["gemm_gbs"], "frac": r["gemm_gbs"] / peaks["hbm_gbs"]}
+    def hbm(name, m, n, k):
+        # two views: isolated launches (L2 flushed, host sync between: what a lone call costs, launch latency
+        # included) and back-to-back launches over rotating weights (what the linear costs inside a step)
+        iso, rot = time_linear(be, m, n, k, iters=20, flush_l2=True), time_linear_rotating(be, m, n, k)
+        out[name] = {"bound": "hbm", "in_step_us": rot["us_per_linear"], "min_bytes": rot["min_bytes"], "gbs": rot["gbs"],
+                     "frac": rot["gbs"] / peaks["hbm_gbs"], "tflops": rot["tflops"], "weight_copies": rot["copies"],
+                     "isolated_gemm_us": iso["gemm_ms"] * 1e3, "isolated_quant_us": iso["quant_ms"] * 1e3,
+                     "note": "in_step: quantiser + GEMM launched back to back on rotating weights (> 2 x L2), no host sync; "
+                             "isolated: one launch between host syncs, L2 flushed"}
 
-    hbm("c1_256x3072x3072_bias", time_linear(be, 256, 3072, 3072, iters=20, flush_l2=True))
-    hbm("mod_1x3072x18432", time_linear(be, 1, 18432, 3072, iters=20, flush_l2=True))
+    hbm("c1_256x3072x3072_bias", 256, 3072, 3072)
+    hbm("mod_1x3072x18432", 1, 18432, 3072)
     tensor("c3_up_6630x3072x14336_gelu", time_linear(be, 6630, 14336, 3072, act=1, iters=10))
     tensor("c3_down_6630x14336x3072", time_linear(be, 6630, 3072, 14336, iters=10))
+    # the dense-activation arm (bf16 activations x the NVFP4 weight's dense bf16 image, tcgen05 kind::f16) on the two
+    # sites the reference keeps dense (proj, ffn_down); fraction of the measured sustained bf16 peak
+    tensor("c2_out_dense_act_4352x3072x3072", time_linear(be, 4352, 3072, 3072, iters=10, dense=True), peaks["bf16_sustained"])
+    tensor("c2_down_dense_act_4352x12288x3072", time_linear(be, 4352, 3072, 12288, iters=10, dense=True), peaks["bf16_sustained"])
     pair = time_ffn_pair(be, WAN_M, HIDDEN, WAN_FFN)
     out["c5_ffn_pair_26520_one_gpu"] = {"ms": pair["ms"], "tflops": pair["tflops"], "bound": "tensor", "frac": pair["tflops"] / fp4,
                                         "note": "the N > 1 lines split this work by output columns; this is their same-workload N = 1 time"}
@@ -832,7 +895,7 @@ def run_stream_bench(args, as_dict=False):
     compute, copy = (torch.cuda.ExternalStream(s_, device=dev) for s_ in be.streams())
     a_global = 0.002
 
-    # pinned-copy peak on this box: one 1 GiB cudaMemcpyAsync from the arena (the denominator for H2D efficiency)
+    # pinned-copy peak measured in this process: one 1 GiB cudaMemcpyAsync from the arena (the denominator for H2D efficiency)
     probe = be.allocate_in(GiB, L.CAT_STAGING)
     ev = C.c_uint64()
     best = 0.0
@@ -922,6 +985,7 @@ def main():
     ap.add_argument("--no-quant", action="store_true", help="linear: quantise the activations once, time the GEMM alone afterwards")
     ap.add_argument("--flush-l2", action="store_true", help="linear: overwrite a 256 MB buffer between iterations")
     ap.add_argument("--out-nvfp4", action="store_true", help="linear: the epilogue also emits the NVFP4 copy of the output")
+    ap.add_argument("--dense-act", action="store_true", help="linear: the dense-activation arm (bf16 activations, no quantiser)")
     ap.add_argument("--ring-slots", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -124,7 +124,7 @@ def run_multi_gpu(args):
     def step():
         mark("start")
         if ffn is not None:
-            ffn.step(Buf(x.id, my_row0 * HIDDEN * 2, my_rows * HIDDEN * 2))
+            ffn.step(Buf(x.id, my_row0 * HIDDEN * 2, my_rows * HIDDEN * 2), mark)
         elif fused:
             sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN, flags=grp.scatter_flags(0))
             grp.barrier()
@@ -181,7 +181,10 @@ def run_multi_gpu(args):
             sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN)
             grp.all_gather_cols(y, M, HIDDEN)
 
-    def compute_only():  # same GEMMs, no delivery to peers (for the breakdown)
+    def compute_only():  # same kernels, no delivery to peers (for the breakdown)
+        if ffn is not None:
+            ffn.step(Buf(x.id, my_row0 * HIDDEN * 2, my_rows * HIDDEN * 2), multicast=False)
+            return
         sc.linear(x, M, w_up, ga_x, h, act=1, n_offset=up_off, ldo=WAN_FFN)
         sc.linear(h, M, w_dn, ga_h, y, n_offset=dn_off, ldo=HIDDEN)
 
@@ -213,7 +216,7 @@ def run_multi_gpu(args):
     clocks = sampler.stop() if sampler else None
     ms = float(np.median(passes))
     breakdown = None
-    if os.environ.get("TNF_BENCH_BREAKDOWN"):  # one more step with an event after every stage (rank 0's view)
+    if ffn is not None or os.environ.get("TNF_BENCH_BREAKDOWN"):  # one more step with an event after every stage (rank 0's view)
         dist.barrier()
         trace_on[0] = True
         step()

@@ -157,6 +157,7 @@ typedef struct tnf_linear_args {
   tnf_buf out_codes;    /* TNF_LINEAR_OUT_NVFP4: [m, ldo/2] E2M1 codes of the bf16-rounded output; this call fills
                            the bytes of columns n_offset .. n_offset+n of each row */
   tnf_buf out_scales;   /* TNF_LINEAR_OUT_NVFP4: DEVICE-layout scales of an [m, ldo] operand (same window) */
+  tnf_buf w_dense;      /* TNF_LINEAR_DENSE_ACT: the weight's dense bf16 image [n,k] from tnf_prepare_dense */
 } tnf_linear_args;
 
 enum {
@@ -174,10 +175,39 @@ enum {
    * alias (multimem.st), so every rank of the group receives this rank's column window at the same
    * offsets while the GEMM is still running: the all-gather of an N-split output, fused into the
    * kernel that produces it. Follow with a barrier across the ranks before the result is read. */
-  TNF_LINEAR_MULTICAST_OUT = 16u
+  TNF_LINEAR_MULTICAST_OUT = 16u,
+  /* The site keeps its activations un-quantised: out = epilogue(w_global * (A_bf16 . Wd^T)) with Wd the dense image
+   * of the NVFP4 weight (w_dense). This is the reference's dense arm for sites whose A-side carries outliers
+   * (DenseActSites, thinfer-models/src/common/block.rs:458-479; the "dequant once, then matmul" branch of
+   * dispatch_matmul_site_diag, :2861-2881, with PreparedWeight::F16, :217-227). a_bf16 is required, a_global and
+   * TNF_LINEAR_A_PREQUANTIZED are not used, no activation quantiser runs; bf16 x bf16 products on the tensor
+   * cores (tcgen05.mma kind::f16), f32 accumulation, the same fused epilogue. k must be a multiple of 8. */
+  TNF_LINEAR_DENSE_ACT = 32u,
+  /* SwiGLU gating fused into the FFN-up GEMM: the weight is the ROW-INTERLEAVED pair [W1 row 0, W3 row 0,
+   * W1 row 1, ...] (n = 2 x hidden rows, quantised as one tensor), and the epilogue writes
+   * out[m, j] = silu(v[2j]) * v[2j+1] with silu(v) = v / (1 + exp(-v)): the reference's two matmul dispatches on
+   * the same A plus its silu_mul dispatch (thinfer-models/src/common/block.rs:1720-1762,
+   * thinfer-core/src/ops/silu_mul.rs) as one launch. out_bf16 is [m, ldo] with n/2 columns written at
+   * n_offset (ldo = 0 means n/2); a bias, if given, is interleaved like the rows; act must be TNF_ACT_NONE;
+   * n a multiple of 16; not combinable with a gated residual, OUT_NVFP4, SCATTER_PEERS or MULTICAST_OUT. */
+  TNF_LINEAR_SWIGLU = 64u
 };
 
+/* Which linear sites of a block keep their activations dense; same fields as the reference's DenseActSites
+ * (thinfer-models/src/common/block.rs:470-479). A site that is set runs with TNF_LINEAR_DENSE_ACT and needs
+ * the weight's dense image; the others quantise their activations to NVFP4. */
+typedef struct tnf_dense_act_sites {
+  uint32_t qkv, qkv_self, proj, ffn_up, ffn_down;
+} tnf_dense_act_sites;
+enum { TNF_SITE_QKV = 0, TNF_SITE_QKV_SELF = 1, TNF_SITE_PROJ = 2, TNF_SITE_FFN_UP = 3, TNF_SITE_FFN_DOWN = 4 };
+/* The tnf_linear_args.flags bits a site runs with under a policy (0 or TNF_LINEAR_DENSE_ACT). */
+uint32_t tnf_site_linear_flags(const tnf_dense_act_sites* policy, int32_t site);
+
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args);
+/* The dense bf16 image [n,k] of an NVFP4 weight for TNF_LINEAR_DENSE_ACT sites: code x block scale, exact in
+ * bf16, without the per-tensor scale (the epilogue applies it). Made once per weight and kept resident, like
+ * the reference's pre-dequantised PreparedWeight::F16 (thinfer-models/src/common/block.rs:211-227). */
+int32_t tnf_prepare_dense(tnf_ctx* ctx, tnf_buf w_codes, tnf_buf w_scales_device, uint32_t n, uint32_t k, tnf_buf out_bf16);
 
 /* LayerNorm (no affine) + AdaLN modulation + activation quantiser in one pass: the two
  * dispatches in front of every block linear, op_layernorm (thinfer-core/src/ops/layernorm.rs:95-125)

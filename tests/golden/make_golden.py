@@ -1,5 +1,7 @@
-"""Regenerates tests/golden/*.npz. Run in the build container only (needs the reference
-checkout for part 1); the .npz files are committed so that tests never read the reference.
+"""Regenerates tests/golden/*.npz; the files are committed so that tests never read the reference.
+
+    python tests/golden/make_golden.py --reference <path to a cretz/thinfer checkout>   # parts 1 and 2
+    python tests/golden/make_golden.py                                                  # part 2 only
 
 Part 1 — reference_fixtures.npz: the cases of the reference's committed conformance
 fixtures (thinfer-conformance/fixtures/{fp32,bf16w,bf16p}.safetensors, spec in
@@ -19,15 +21,14 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 
-REF_FIXTURES = os.path.join(os.environ.get("THINFER_REFERENCE", os.path.join(os.sep, "root", "reference")),
-                            "projects", "thinfer-conformance", "fixtures")  # the reference checkout of the build container
 CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic", "layernorm_basic", "bcast_modulate"]
 
 
-def part1():
+def part1(reference_root):
     import torch
     from safetensors import safe_open
 
+    REF_FIXTURES = os.path.join(reference_root, "projects", "thinfer-conformance", "fixtures")
     out = {}
     for variant in ("fp32", "bf16w", "bf16p"):
         with safe_open(os.path.join(REF_FIXTURES, f"{variant}.safetensors"), "pt") as h:
@@ -66,8 +67,13 @@ def part2():
 
 
 if __name__ == "__main__":
-    if os.path.isdir(REF_FIXTURES):
-        part1()
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default=None, help="root of a cretz/thinfer checkout; without it reference_fixtures.npz is left as committed")
+    args = ap.parse_args()
+    if args.reference:
+        part1(args.reference)
     else:
-        print("reference checkout absent: reference_fixtures.npz left as committed")
+        print("no --reference given: reference_fixtures.npz left as committed")
     part2()

@@ -30,7 +30,7 @@ def test_struct_layouts_match_header():
     from thinfer_b200._lib import Buf, LinearArgs, StackLinear
 
     assert ctypes.sizeof(Buf) == 24
-    assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4 + 2 * 24  # 5 scalars (+pad), 7 views, 6 words, 2 views
+    assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4 + 3 * 24  # 5 scalars (+pad), 7 views, 6 words, 3 views
     assert ctypes.sizeof(StackLinear) == 24
 
 
@@ -50,8 +50,31 @@ def test_abi_version_and_sizes():
     from thinfer_b200 import _lib
 
     lib = _lib.load()
-    assert lib.tnf_abi_version() == 2
+    assert lib.tnf_abi_version() == 3
     # 128-row x 4-block atoms of 512 bytes; K atoms rounded up to a multiple of 4
     assert lib.tnf_device_scales_bytes(128, 256) == 4 * 512
     assert lib.tnf_device_scales_bytes(129, 3072) == 2 * 48 * 512
     assert lib.tnf_device_scales_bytes(1, 64) == 4 * 512
+
+
+def test_rust_bindings_declare_every_header_symbol():
+    """rust/thinfer-native-cuda/src/ffi.rs (generated from the header) lists exactly the header's functions, and its
+    struct fields follow the ctypes mirror (same order, so the same layout under repr(C))."""
+    text = open(os.path.join(ROOT, "rust", "thinfer-native-cuda", "src", "ffi.rs")).read()
+    rust = sorted(set(re.findall(r"pub fn (tnf_[a-z0-9_]+)\s*\(", text)))
+    assert rust == declared_symbols()
+    from thinfer_b200._lib import DenseActSites, LinearArgs, NormQuantArgs, StackLinear
+
+    for rust_name, ct in (("TnfLinearArgs", LinearArgs), ("TnfNormQuantArgs", NormQuantArgs), ("TnfStackLinear", StackLinear),
+                          ("TnfDenseActSites", DenseActSites)):
+        body = re.search(r"pub struct %s \{(.*?)\n?\}" % rust_name, text, flags=re.S).group(1)
+        fields = re.findall(r"pub (\w+):", body)
+        assert fields == [f[0] for f in ct._fields_], rust_name
+
+
+def test_site_policy_flags_are_host_only():
+    from thinfer_b200 import DenseActSites, _lib as L
+
+    pol = DenseActSites(proj=True, ffn_down=True)
+    assert [pol.flags(s) for s in range(5)] == [0, 0, L.LINEAR_DENSE_ACT, 0, L.LINEAR_DENSE_ACT]
+    assert DenseActSites().flags(L.SITE_QKV) == 0 and pol.flags(7) == 0

@@ -63,3 +63,18 @@ def test_two_rank_gather_matches_unsplit():
         p.join(120)
         assert p.exitcode == 0
     assert ret.get(timeout=5) == 2
+
+
+def test_row_partition_covers_rows_in_whole_scale_blocks():
+    """Each rank quantises its own row block of the activations; blocks start on multiples of 128 rows (a scale
+    atom of the device layout covers 128 rows), cover every row once and may leave the last ranks empty."""
+    from thinfer_b200.nsplit import row_partition
+
+    for m, world in [(26520, 1), (26520, 2), (26520, 4), (26520, 8), (2350, 2), (100, 4), (128, 8), (1, 2)]:
+        parts = row_partition(m, world)
+        assert len(parts) == world and sum(r for _, r in parts) == m
+        nxt = 0
+        for r0, rows in parts:
+            assert r0 == nxt and r0 % 128 == 0 or rows == 0
+            nxt = r0 + rows
+        assert nxt == m

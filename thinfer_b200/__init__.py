@@ -6,5 +6,5 @@ C ABI in ``include/thinfer_nvfp4.h``. Everything computes on the GPU through
 """
 from . import _lib  # noqa: F401
 from .backend import (  # noqa: F401
-    Backend, BatchScope, BudgetExceeded, DeviceTimeout, Nvfp4Weight, TnfError, UnknownBuffer,
+    Backend, BatchScope, BudgetExceeded, DenseActSites, DeviceTimeout, Nvfp4Weight, TnfError, UnknownBuffer, interleave_swiglu,
 )

@@ -16,6 +16,7 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 SCALES_CANONICAL, SCALES_DEVICE = 0, 1
 ACT_NONE, ACT_GELU_TANH = 0, 1
 LINEAR_A_PREQUANTIZED, LINEAR_SCATTER_PEERS, LINEAR_OUT_NVFP4, LINEAR_NO_BF16_OUT, LINEAR_MULTICAST_OUT = 1, 2, 4, 8, 16
+LINEAR_DENSE_ACT, LINEAR_SWIGLU = 32, 64
 
 
 class Buf(C.Structure):
@@ -31,8 +32,16 @@ class LinearArgs(C.Structure):
         ("gate_bf16", Buf), ("residual_bf16", Buf), ("out_bf16", Buf),
         ("act", C.c_uint32), ("parity_mode", C.c_uint32), ("n_offset", C.c_uint32),
         ("ldo", C.c_uint32), ("flags", C.c_uint32), ("out_global", C.c_float),
-        ("out_codes", Buf), ("out_scales", Buf),
+        ("out_codes", Buf), ("out_scales", Buf), ("w_dense", Buf),
     ]
+
+
+class DenseActSites(C.Structure):
+    """tnf_dense_act_sites: which sites keep un-quantised activations (DenseActSites in the reference)."""
+    _fields_ = [("qkv", C.c_uint32), ("qkv_self", C.c_uint32), ("proj", C.c_uint32), ("ffn_up", C.c_uint32), ("ffn_down", C.c_uint32)]
+
+
+SITE_QKV, SITE_QKV_SELF, SITE_PROJ, SITE_FFN_UP, SITE_FFN_DOWN = range(5)
 
 
 class NormQuantArgs(C.Structure):
@@ -82,6 +91,8 @@ SIGNATURES = {
     "tnf_prepare_scales": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, Buf]),
     "tnf_quantize_act": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float, C.c_int32, Buf, Buf, C.POINTER(C.c_float)]),
     "tnf_linear_nvfp4": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_prepare_dense": (C.c_int32, [_ctx, Buf, Buf, C.c_uint32, C.c_uint32, Buf]),
+    "tnf_site_linear_flags": (C.c_uint32, [C.POINTER(DenseActSites), C.c_int32]),
     "tnf_linear_nvfp4_noalloc": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
     "tnf_norm_modulate_quantize": (C.c_int32, [_ctx, C.POINTER(NormQuantArgs)]),
     "tnf_noalloc_scratch_bytes": (C.c_uint64, []),

@@ -187,6 +187,7 @@ class Nvfp4Weight:
     global_scale: float
     bias: Optional[Buf] = None
     scales_canonical: Optional[Buf] = None
+    dense: Optional[Buf] = None  # bf16 [n,k] image for dense-activation sites (PreparedWeight::F16 in the reference)
 
     @staticmethod
     def from_dense(be: Backend, w: np.ndarray, bias_bf16: Optional[np.ndarray] = None,
@@ -225,10 +226,40 @@ class Nvfp4Weight:
         bias = be.upload(bias_bf16.astype(np.uint16, copy=False), L.CAT_WEIGHTS) if bias_bf16 is not None else None
         return Nvfp4Weight(n, k, cb, dev, float(global_scale), bias, None)
 
+    def prepare_dense(self, be: Backend) -> Buf:
+        """Make (once) and keep the dense bf16 image a ``dense_act`` site multiplies with: code x block scale, exact."""
+        if self.dense is None:
+            self.dense = be.allocate_in(self.n * self.k * 2, L.CAT_WEIGHTS)
+            _check(be.lib.tnf_prepare_dense(be._ctx, self.codes, self.scales_device, self.n, self.k, self.dense))
+        return self.dense
+
     def free(self, be: Backend) -> None:
-        for b in (self.codes, self.scales_device, self.bias, self.scales_canonical):
+        for b in (self.codes, self.scales_device, self.bias, self.scales_canonical, self.dense):
             if b is not None:
                 be.free(b)
+
+
+def interleave_swiglu(w1: np.ndarray, w3: np.ndarray) -> np.ndarray:
+    """[W1 row 0, W3 row 0, W1 row 1, ...]: the weight (or bias) layout of a ``swiglu`` linear."""
+    assert w1.shape == w3.shape
+    out = np.empty((2 * w1.shape[0],) + w1.shape[1:], w1.dtype)
+    out[0::2], out[1::2] = w1, w3
+    return out
+
+
+@dataclass
+class DenseActSites:
+    """Which linear sites of a block keep un-quantised activations; the reference's ``DenseActSites``
+    (thinfer-models/src/common/block.rs:470-479). ``flags(site)`` gives the linear flags for that site."""
+    qkv: bool = False
+    qkv_self: bool = False
+    proj: bool = False
+    ffn_up: bool = False
+    ffn_down: bool = False
+
+    def flags(self, site: int) -> int:
+        c = L.DenseActSites(int(self.qkv), int(self.qkv_self), int(self.proj), int(self.ffn_up), int(self.ffn_down))
+        return int(L.load().tnf_site_linear_flags(C.byref(c), site))
 
 
 class BatchScope:
@@ -270,6 +301,11 @@ class BatchScope:
             flags |= L.LINEAR_OUT_NVFP4 | (L.LINEAR_NO_BF16_OUT if out is None else 0)
         else:
             args.out_codes, args.out_scales = _NONE, _NONE
+        args.w_dense = _NONE
+        if flags & L.LINEAR_DENSE_ACT:
+            if w.dense is None:
+                raise InvalidArgument(L.ERR_INVALID_ARGUMENT, "dense_act site: call Nvfp4Weight.prepare_dense first")
+            args.w_dense = w.dense
         args.n_offset, args.ldo, args.flags = n_offset, ldo, flags
         return args
 
@@ -285,11 +321,22 @@ class BatchScope:
 
     def linear(self, a_bf16: Optional[Buf], m: int, w: Nvfp4Weight, a_global: float, out: Optional[Buf],
                act: int = L.ACT_NONE, gate: Optional[Buf] = None, residual: Optional[Buf] = None, chain: bool = False,
-               n_offset: int = 0, ldo: int = 0, flags: int = 0, bias=None, out_nvfp4=None) -> None:
+               n_offset: int = 0, ldo: int = 0, flags: int = 0, bias=None, out_nvfp4=None, dense_act: bool = False,
+               swiglu: bool = False) -> None:
         """out = epilogue(a_global*w_global * (quant(A) . Wq^T)): the ``biased`` call site, fused.
+
+        ``dense_act=True`` is the reference's dense arm for outlier-carrying sites (``DenseActSites``): the
+        activations stay bf16 and multiply the weight's dense image (``Nvfp4Weight.prepare_dense``); ``a_global``
+        is ignored. ``swiglu=True``: ``w`` is the row-interleaved pair from :func:`interleave_swiglu` and the
+        epilogue writes ``silu(A.W1^T) * (A.W3^T)``, ``w.n // 2`` columns (the reference's ``op_silu_mul`` after its
+        two FFN-up matmuls, thinfer-models/src/common/block.rs:1720-1762).
 
         ``out_nvfp4=(codes, scales_device, g)`` also emits the result quantised to NVFP4 (the A operand
         of the next linear: MLP up -> GELU -> down); ``out=None`` then skips the bf16 store."""
+        if dense_act:
+            flags |= L.LINEAR_DENSE_ACT
+        if swiglu:
+            flags |= L.LINEAR_SWIGLU
         args = self._args(m, w, a_bf16, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias, out_nvfp4)
         _check(self.be.lib.tnf_linear_nvfp4(self.be._ctx, C.byref(args)))
 

@@ -237,20 +237,35 @@ static int32_t check_dims(uint32_t m, uint32_t n, uint32_t k) {
 // shared tail of tnf_linear_nvfp4 / tnf_gemm_nvfp4
 static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales) {
   int32_t st = TNF_OK;
-  const uint32_t ldo = a->ldo ? a->ldo : a->n;
-  if (ldo % 8 != 0 || a->n_offset % 8 != 0 || a->n_offset + a->n > ldo) {
-    set_error("bad output window: n_offset %u + n %u within ldo %u, all multiples of 8", a->n_offset, a->n, ldo);
+  const bool swiglu = (a->flags & TNF_LINEAR_SWIGLU) != 0;
+  const uint32_t n_out_cols = swiglu ? a->n / 2 : a->n;  // columns this call writes
+  const uint32_t ldo = a->ldo ? a->ldo : n_out_cols;
+  if (ldo % 8 != 0 || a->n_offset % 8 != 0 || a->n_offset + n_out_cols > ldo) {
+    set_error("bad output window: n_offset %u + %u columns within ldo %u, all multiples of 8", a->n_offset, n_out_cols, ldo);
     return TNF_ERR_INVALID_ARGUMENT;
   }
-  uint8_t* w_codes = resolve(ctx, a->w_codes, uint64_t(a->n) * (a->k / 2), "w_codes", &st);
-  if (!w_codes) return st;
-  uint8_t* w_scales = resolve(ctx, a->w_scales, sf_device_bytes(a->n, a->k), "w_scales", &st);
-  if (!w_scales) return st;
+  if (swiglu && (a->n % 16 != 0 || a->act != TNF_ACT_NONE || a->gate_bf16.len ||
+                 (a->flags & (TNF_LINEAR_OUT_NVFP4 | TNF_LINEAR_SCATTER_PEERS | TNF_LINEAR_MULTICAST_OUT)))) {
+    set_error("TNF_LINEAR_SWIGLU needs n %% 16 == 0 (n=%u), act none, no gated residual, and none of OUT_NVFP4 / SCATTER_PEERS / "
+              "MULTICAST_OUT", a->n);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  const bool dense = (a->flags & TNF_LINEAR_DENSE_ACT) != 0;
+  uint8_t *w_codes = nullptr, *w_scales = nullptr;
+  if (dense) {  // a_codes carries the bf16 activations, the weight is its dense image
+    w_codes = resolve(ctx, a->w_dense, uint64_t(a->n) * a->k * 2, "w_dense", &st);
+    if (!w_codes) return st;
+  } else {
+    w_codes = resolve(ctx, a->w_codes, uint64_t(a->n) * (a->k / 2), "w_codes", &st);
+    if (!w_codes) return st;
+    w_scales = resolve(ctx, a->w_scales, sf_device_bytes(a->n, a->k), "w_scales", &st);
+    if (!w_scales) return st;
+  }
   const bool q_out = (a->flags & TNF_LINEAR_OUT_NVFP4) != 0;
   const bool store_bf16 = !(q_out && (a->flags & TNF_LINEAR_NO_BF16_OUT));
   uint8_t* out = nullptr;
   if (store_bf16) {
-    out = resolve(ctx, a->out_bf16, (uint64_t(a->m - 1) * ldo + a->n_offset + a->n) * 2, "out_bf16", &st);
+    out = resolve(ctx, a->out_bf16, (uint64_t(a->m - 1) * ldo + a->n_offset + n_out_cols) * 2, "out_bf16", &st);
     if (!out) return st;
   }
   GemmParams p{};
@@ -296,7 +311,9 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   }
   p.m = a->m; p.n = a->n; p.k = a->k;
   p.k_atoms = sf_k_atoms(a->k);
-  p.alpha = a->a_global * a->w_global;
+  p.alpha = dense ? a->w_global : a->a_global * a->w_global;
+  p.dense = dense ? 1u : 0u;
+  p.swiglu = swiglu ? 1u : 0u;
   p.sfa = a_scales;
   p.sfb = w_scales;
   if (a->bias_bf16.len) {
@@ -328,16 +345,23 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
   CUtensorMap ma, mw;
-  if (q_out || mc_out || gemm_use_pair(a->m, a->n, a->k)) {  // only the CTA-pair kernel has the NVFP4 and multicast epilogues
+  if (dense || swiglu || q_out || mc_out || gemm_use_pair(a->m, a->n, a->k)) {  // only the CTA-pair kernel has the dense arm and the NVFP4 / multicast epilogues
     const uint32_t kb = gemm_pair_kblocks();
     CUtensorMap msa, msb, outs[kMaxPeers];
-    if (!get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb), &ma) || !get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb), &mw) ||
-        !get_map(ctx, scales_spec(a_scales, a->m, a->k, kb), &msa) || !get_map(ctx, scales_spec(w_scales, a->n, a->k, kb), &msb))
+    if (dense) {  // bf16 [rows, k]: boxes of 64 elements (128 bytes) x 128 rows, 128-byte swizzle; no scale maps
+      if (!get_map(ctx, MapSpec{a_codes, 2, a->k, a->m, uint64_t(a->k) * 2, 64, 128, 128}, &ma) ||
+          !get_map(ctx, MapSpec{w_codes, 2, a->k, a->n, uint64_t(a->k) * 2, 64, 128, 128}, &mw))
+        return TNF_ERR_INVALID_ARGUMENT;
+      msa = msb = ma;
+    } else if (!get_map(ctx, pair_codes_spec(a_codes, a->m, a->k, kb), &ma) || !get_map(ctx, pair_codes_spec(w_codes, a->n, a->k, kb), &mw) ||
+               !get_map(ctx, scales_spec(a_scales, a->m, a->k, kb), &msa) || !get_map(ctx, scales_spec(w_scales, a->n, a->k, kb), &msb))
       return TNF_ERR_INVALID_ARGUMENT;
     for (uint32_t d = 0; d < p.n_out; ++d) {
       // without a bf16 destination the map is never used; any valid one fills the slot
       if (!store_bf16) outs[d] = ma;
-      else if (!get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo), &outs[d])) return TNF_ERR_INVALID_ARGUMENT;
+      else if (swiglu) {  // n/2 output columns; boxes of 32 columns x 32 rows, dense 64-byte rows in shared memory
+        if (!get_map(ctx, MapSpec{p.out[d] + a->n_offset, 2, n_out_cols, a->m, uint64_t(ldo) * 2, 32, 32, 0}, &outs[d])) return TNF_ERR_INVALID_ARGUMENT;
+      } else if (!get_map(ctx, out_spec(p.out[d] + a->n_offset, a->m, a->n, ldo), &outs[d])) return TNF_ERR_INVALID_ARGUMENT;
     }
     for (uint32_t d = p.n_out; d < kMaxPeers; ++d) outs[d] = outs[0];
     TNF_CUDA(launch_gemm_nvfp4_pair(ma, mw, msa, msb, outs, p, ctx->sm_count, ctx->compute), "nvfp4 pair gemm launch");
@@ -356,7 +380,7 @@ using namespace tnf;
 
 extern "C" {
 
-uint32_t tnf_abi_version(void) { return 2; }
+uint32_t tnf_abi_version(void) { return 3; }
 const char* tnf_last_error(void) { return g_err; }
 
 int32_t tnf_create(int32_t device, uint64_t vram_budget_bytes, tnf_ctx** out) {
@@ -736,6 +760,29 @@ int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32
                            static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr);
 }
 
+int32_t tnf_prepare_dense(tnf_ctx* ctx, tnf_buf w_codes, tnf_buf w_scales_device, uint32_t n, uint32_t k, tnf_buf out_bf16) {
+  TNF_CHECK_CTX(ctx);
+  if (n == 0 || k == 0 || k % 32 != 0) {
+    set_error("tnf_prepare_dense: n=%u k=%u (k %% 32 == 0)", n, k);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  uint8_t* c = resolve(ctx, w_codes, uint64_t(n) * (k / 2), "w_codes", &st);
+  if (!c) return st;
+  uint8_t* s = resolve(ctx, w_scales_device, sf_device_bytes(n, k), "w_scales_device", &st);
+  if (!s) return st;
+  uint8_t* o = resolve(ctx, out_bf16, uint64_t(n) * k * 2, "out_bf16", &st);
+  if (!o) return st;
+  TNF_CUDA(launch_dequant_dense(c, s, n, k, reinterpret_cast<uint16_t*>(o), ctx->compute), "dense image launch");
+  return TNF_OK;
+}
+
+uint32_t tnf_site_linear_flags(const tnf_dense_act_sites* policy, int32_t site) {
+  if (!policy) return 0u;
+  const uint32_t on[5] = {policy->qkv, policy->qkv_self, policy->proj, policy->ffn_up, policy->ffn_down};
+  return (site >= 0 && site < 5 && on[site]) ? uint32_t(TNF_LINEAR_DENSE_ACT) : 0u;
+}
+
 // ---- the linear ------------------------------------------------------------------------------------
 
 int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
@@ -746,10 +793,20 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
   }
   int32_t st = check_dims(a->m, a->n, a->k);
   if (st != TNF_OK) return st;
-  if (!(a->a_global > 0.0f) || !(a->w_global > 0.0f) || a->act > 1 || a->parity_mode > 1) {
+  const bool dense = (a->flags & TNF_LINEAR_DENSE_ACT) != 0;
+  if ((!dense && !(a->a_global > 0.0f)) || !(a->w_global > 0.0f) || a->act > 1 || a->parity_mode > 1) {
     set_error("tnf_linear_nvfp4: scales must be > 0 (a %g, w %g), act %u, parity_mode %u", a->a_global, a->w_global,
               a->act, a->parity_mode);
     return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (dense) {  // un-quantised activations: no quantiser launch, the GEMM reads a_bf16 itself
+    if ((a->flags & TNF_LINEAR_A_PREQUANTIZED) || a->k % 8 != 0) {
+      set_error("TNF_LINEAR_DENSE_ACT: not combinable with TNF_LINEAR_A_PREQUANTIZED; k=%u must be a multiple of 8", a->k);
+      return TNF_ERR_INVALID_ARGUMENT;
+    }
+    uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
+    if (!src) return st;
+    return run_gemm(ctx, a, src, nullptr);
   }
   if (!(a->flags & TNF_LINEAR_A_PREQUANTIZED)) {
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);

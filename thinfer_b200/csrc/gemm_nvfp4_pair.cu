@@ -121,7 +121,8 @@ __device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, const
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
 template <bool kGelu, bool kChain, bool kGate, bool kQuant>
 __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], const GemmParams& p, uint32_t row, uint32_t ncol0,
-                                                   uint8_t* buf_gen, const float* bias_smem, const float* lut, int lane) {
+                                                   uint8_t* buf_gen, const float* bias_smem, const float* lut, int lane,
+                                                   uint8_t* stage_q, uint32_t gq) {
   const bool row_ok = row < p.m;
   const float alpha = (kGelu && !kChain) ? 0.5f * p.alpha : p.alpha;  // the fused GELU works on x/2
   // NVFP4 copy of this row's 64 columns: 32 code bytes + 4 scale bytes. Each 16-byte group of codes
@@ -162,41 +163,84 @@ __device__ __forceinline__ void epilogue_pair_math(const uint32_t (&r)[64], cons
         }
       }
     }
-    if (q_on && !(kDiag && (p.diag & 128u))) {
+    if (kQuant && stage_q) {
+      // multicast output: this row's 16 code bytes go to the CTA's staging tile (128 rows x 128 bytes, 16-byte
+      // chunks XOR-swizzled by the row) and leave later as whole 128-byte row segments
+      const uint32_t lr = row & 127u, c = gq * 2u + uint32_t(sub);
+      *reinterpret_cast<uint4*>(stage_q + lr * 128u + ((c ^ (lr & 7u)) << 4)) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    } else if (q_on && !(kDiag && (p.diag & 128u))) {
       const uint64_t off = uint64_t(row) * (p.ldo >> 1) + (qcol >> 1) + sub * 16;
       const uint4 v = make_uint4(cw[0], cw[1], cw[2], cw[3]);
       if (p.q_codes_mc) multimem_st_v4(p.q_codes_mc + off, v);  // every rank's copy of the operand, this one included
       else *reinterpret_cast<uint4*>(p.q_codes + off) = v;
     }
   }
-  if (q_on && !(kDiag && (p.diag & 128u))) {
+  if (kQuant && stage_q) {
+    // the scale word into the staged copy of this 64-column group's 512-byte atom; rows past m hold zero scales
+    const uint32_t lr = row & 127u;
+    *reinterpret_cast<uint32_t*>(stage_q + 16384u + gq * 512u + (lr & 31u) * 16u + (lr >> 5) * 4u) = row_ok ? sw : 0u;
+  } else if (q_on && !(kDiag && (p.diag & 128u))) {
     const uint64_t off = sf_device_offset(row, qcol >> 4, p.q_k_atoms);
     if (p.q_scales_mc) multimem_st_b32(p.q_scales_mc + off, sw);
     else *reinterpret_cast<uint32_t*>(p.q_scales + off) = sw;
   }
 }
 
-__device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
-                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const float* bias_smem,
-                                                       const float* lut, int lane) {
-  switch (mode) {
-    case 0: epilogue_pair_math<false, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 1: epilogue_pair_math<true, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 2: epilogue_pair_math<false, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 3: epilogue_pair_math<true, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 4: epilogue_pair_math<false, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 5: epilogue_pair_math<true, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 6: epilogue_pair_math<false, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 7: epilogue_pair_math<true, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    // with an NVFP4 copy of the output (the host refuses the combination with a gated residual)
-    case 8: epilogue_pair_math<false, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 9: epilogue_pair_math<true, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    case 10: epilogue_pair_math<false, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
-    default: epilogue_pair_math<true, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane); break;
+// SwiGLU pairwise gating (thinfer-core/src/ops/silu_mul.rs: out = silu(a) * b, silu(v) = v / (1 + exp(-v))) on a
+// GEMM over the row-interleaved weight [W1 row 0, W3 row 0, W1 row 1, ...]: accumulator columns 2j and 2j+1 are
+// a[j] and b[j], one output column. One warp's 32 rows x 64 accumulator columns -> 32 bf16 per row, staged as
+// dense 64-byte rows (no swizzle) for a 32-column TMA store. Chain mode rounds a and b to bf16 first, as the
+// reference's two matmul dispatches do.
+template <bool kChain>
+__device__ __forceinline__ void epilogue_pair_swiglu(const uint32_t (&r)[64], const GemmParams& p, uint8_t* buf_gen,
+                                                     const float* bias_smem, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 bl = *reinterpret_cast<const float4*>(bias_smem + j * 8), bh = *reinterpret_cast<const float4*>(bias_smem + j * 8 + 4);
+    const float bv[8] = {bl.x, bl.y, bl.z, bl.w, bh.x, bh.y, bh.z, bh.w};
+    float o[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      float a, b;
+      if (kChain) {
+        a = bf16r(bf16r(__uint_as_float(r[j * 8 + 2 * h]) * p.alpha) + bv[2 * h]);
+        b = bf16r(bf16r(__uint_as_float(r[j * 8 + 2 * h + 1]) * p.alpha) + bv[2 * h + 1]);
+      } else {
+        unpack2(fma2(pack2u(r[j * 8 + 2 * h], r[j * 8 + 2 * h + 1]), pack2(p.alpha, p.alpha), pack2(bv[2 * h], bv[2 * h + 1])), a, b);
+      }
+      o[h] = __fdividef(a, 1.0f + __expf(-a)) * b;
+    }
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+    *reinterpret_cast<uint2*>(buf_gen + lane * 64 + j * 8) = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
   }
 }
 
-template <int KB>
+__device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint32_t (&r)[64], const GemmParams& p,
+                                                       uint32_t row, uint32_t ncol0, uint8_t* buf_gen, const float* bias_smem,
+                                                       const float* lut, int lane, uint8_t* stage_q, uint32_t gq) {
+  switch (mode) {
+    case 0: epilogue_pair_math<false, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 1: epilogue_pair_math<true, false, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 2: epilogue_pair_math<false, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 3: epilogue_pair_math<true, true, false, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 4: epilogue_pair_math<false, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 5: epilogue_pair_math<true, false, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 6: epilogue_pair_math<false, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 7: epilogue_pair_math<true, true, true, false>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    // with an NVFP4 copy of the output (the host refuses the combination with a gated residual)
+    case 8: epilogue_pair_math<false, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 9: epilogue_pair_math<true, false, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 10: epilogue_pair_math<false, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+    case 12: epilogue_pair_swiglu<false>(r, p, buf_gen, bias_smem, lane); break;
+    case 13: epilogue_pair_swiglu<true>(r, p, buf_gen, bias_smem, lane); break;
+    default: epilogue_pair_math<true, true, false, true>(r, p, row, ncol0, buf_gen, bias_smem, lut, lane, stage_q, gq); break;
+  }
+}
+
+// kDense: the dense-activation arm of the same kernel. A is bf16 [m,k] (not quantised), W the exact bf16 image of
+// code x block scale [n,k] made once per weight; a stage holds 64 K elements of each (the same 128-byte swizzled
+// rows), there are no scale factors, and the MMAs are kind::f16 with K = 16. Pipeline and epilogue are shared.
+template <int KB, bool kDense>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                            const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
@@ -206,7 +250,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   constexpr int S = Cfg::kStages;
   constexpr int kABytes = Cfg::kABytes, kBBytes = Cfg::kBBytes, kSfaBytes = Cfg::kSfaBytes, kSfbBytes = Cfg::kSfbBytes;
   constexpr int kStageBytes = Cfg::kStageBytes;
-  constexpr uint32_t kStageK = KB * 64;
+  constexpr uint32_t kStageK = kDense ? KB * 16 : KB * 64;  // K elements per stage: 128 bytes of bf16 or of packed E2M1
+  constexpr uint32_t kStageX = kDense ? kStageK : uint32_t(Cfg::kRowBytes);  // stage step along dim 0 of the operand maps
+  constexpr uint32_t kLoadBytes = kDense ? uint32_t(kABytes + kBBytes) : uint32_t(kStageBytes);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -226,6 +272,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   const uint32_t tmem_holder = bar_acc_free + 8;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8 - smem_base));
+  // staged NVFP4 multicast output: the CTA's eight epilogue warps meet on these ("tile staged" / "staging free")
+  const uint32_t bar_qs_full = tmem_holder + 16, bar_qs_free = tmem_holder + 24;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
@@ -243,6 +291,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_free, 16);  // every epilogue warp of both CTAs arrives once per tile
+    mbar_init(bar_qs_full, 8);
+    mbar_init(bar_qs_free, 8);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_a);
@@ -294,15 +344,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
             if (tr) p.trace[titer * 4 + 0] = clock64();
             const bool skip_a = kDiag && (p.diag & 32u) != 0u;
             if (rank == 0)
-              mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * (kStageBytes - (skip_a ? kABytes : 0)));
+              mbar_arrive_expect_tx(bar_full + 8 * stage, skip_ab ? 2u * (kSfaBytes + kSfbBytes) : 2u * (kLoadBytes - (skip_a ? kABytes : 0)));
             if (!skip_ab) {
-              if (!skip_a) tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * Cfg::kRowBytes), m0);
-              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * Cfg::kRowBytes), n0 + int32_t(rank * (n_eff >> 1)));
+              if (!skip_a) tma_load_2d_pair(sA + stage * kABytes, &map_a, full, int32_t(kt * kStageX), m0);
+              tma_load_2d_pair(sB + stage * kBBytes, &map_w, full, int32_t(kt * kStageX), n0 + int32_t(rank * (n_eff >> 1)));
             }
-            tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * (KB * 4u)));
-            tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * (KB * 4u)));
-            tma_load_2d_pair(sSfb + stage * kSfbBytes + 512 * KB, &map_sfb, full, 0,
-                             sfb_row0 + int32_t(p.k_atoms * 4u + kt * (KB * 4u)));
+            if (!kDense) {
+              tma_load_2d_pair(sSfa + stage * kSfaBytes, &map_sfa, full, 0, sfa_row0 + int32_t(kt * (KB * 4u)));
+              tma_load_2d_pair(sSfb + stage * kSfbBytes, &map_sfb, full, 0, sfb_row0 + int32_t(kt * (KB * 4u)));
+              tma_load_2d_pair(sSfb + stage * kSfbBytes + 512 * KB, &map_sfb, full, 0,
+                               sfb_row0 + int32_t(p.k_atoms * 4u + kt * (KB * 4u)));
+            }
             if (tr) p.trace[titer * 4 + 1] = clock64();
           }
           __syncwarp();
@@ -335,7 +387,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (ttr) p.trace[1024 + it * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + (it & 1u) * kAccStride;
         const uint32_t n_eff = min(256u, (p.n - (tile / tiles_m2) * 256u + 15u) & ~15u);  // as in the producer
-        const uint32_t idesc = make_idesc_nvfp4(256, n_eff);
+        const uint32_t idesc = kDense ? make_idesc_bf16(256, n_eff) : make_idesc_nvfp4(256, n_eff);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
           if (kDiag && (p.diag & 16u) && pair_id == 0 && titer < 256u && lane == 0) p.trace[1300 + titer] = clock64();
           // `ready`: the probe issued one stage ago already saw this stage loaded (the usual case once the loads
@@ -360,7 +412,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
           const uint32_t sf_slot = Cfg::kSfSlots == 2 ? (kt & 1u) : 0u;
           const uint32_t t_sfa = tmem_base + kSfaCol + sf_slot * (KB * 4), t_sfb = tmem_base + kSfbCol + sf_slot * (KB * 8);
           const bool do_cp = !(kDiag && (p.diag & 2u)) || kt == 0, do_mma = !(kDiag && (p.diag & 4u));
-          if (kDiag && (p.diag & 64u)) {  // diagnostic order: each K block's scale copies right before its MMA
+          if (kDense) {
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+              tc_mma_bf16_pair(d_tmem, desc64(a_lo + kb * 2, op_hi), desc64(b_lo + kb * 2, op_hi), idesc, (kt | uint32_t(kb)) != 0u);
+          } else if (kDiag && (p.diag & 64u)) {  // diagnostic order: each K block's scale copies right before its MMA
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
               if (do_cp) {
@@ -412,7 +468,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     const uint32_t acc_free_leader = mapa_cluster(bar_acc_free, 0);
     uint32_t it = 0;
     bool ok = true;
-    const uint32_t mode = (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.q_codes ? 8u : (p.gate ? 4u : 0u));
+    const uint32_t mode = p.swiglu ? (p.chain ? 13u : 12u)
+                                   : (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.q_codes ? 8u : (p.gate ? 4u : 0u));
+    // NVFP4 output through the multicast alias with no bf16 store: the (then idle) bf16 staging area collects the
+    // CTA's whole tile of codes and scale atoms, and all eight warps write it out in 128-byte row segments and whole
+    // 16-byte atom rows. Scattered 16- and 4-byte multimem stores straight from the registers ran at a fifth of the link rate.
+    uint8_t* stage_q = (p.q_codes_mc && !p.store_bf16) ? smem_gen + (sStaging - smem_base) : nullptr;
     for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
       const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
       const uint32_t row0 = tm2 * 256u + rank * 128u + q * 32u;
@@ -461,6 +522,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         if (ttr) p.trace[1024 + it * 8 + 5] = clock64();
       }
       const uint32_t row = row0 + lane;
+      if (stage_q && it > 0u &&  // the previous tile's write-out has finished reading the staging area
+          !mbar_wait_bounded(bar_qs_free, (it - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+        ok = false;
+        break;
+      }
 #pragma unroll 1
       for (uint32_t half = 0; half < 2; ++half) {
         const uint32_t g = half ? g1 : g0;
@@ -470,18 +536,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
           tmem_ld_wait();
         }
         const uint32_t ncol0 = n0 + g * 64u;
-        if (row0 >= p.m || ncol0 >= p.n) continue;  // warp-uniform
+        // warp-uniform; with a staged output a warp whose rows are all past m still stages their (zero) scale words
+        if (ncol0 >= p.n || (row0 >= p.m && !stage_q)) continue;
         if (kDiag && (p.diag & 256u)) continue;      // diagnostic: drain the accumulator only
         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
         __syncwarp();                              // ... and every lane its reads of the previous group's bias
         const uint32_t bq = half ? bq1 : bq0;
         *reinterpret_cast<float2*>(bias_gen + lane * 2) = make_float2(bf16_lo(bq) * bias_mul, bf16_hi(bq) * bias_mul);
         __syncwarp();
-        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen, lut_gen, lane);
+        epilogue_pair_dispatch(mode, r, p, row, ncol0, buf_gen, bias_gen, lut_gen, lane, stage_q, g);
         fence_proxy_async();  // generic-proxy writes to smem -> visible to the TMA store
         __syncwarp();
         if (lane == 0) {
-          if (!(kDiag && (p.diag & 1u)) && p.store_bf16 && !p.out_mc) tma_store_2d(&out_maps.m[0], buf, int32_t(ncol0), int32_t(row0));
+          // SwiGLU halves the columns: the 64 accumulator columns of this group are output columns ncol0/2 .. +32
+          if (!(kDiag && (p.diag & 1u)) && p.store_bf16 && !p.out_mc)
+            tma_store_2d(&out_maps.m[0], buf, int32_t(p.swiglu ? ncol0 >> 1 : ncol0), int32_t(row0));
           bulk_commit_group();
         }
         // Multicast output: the staging rows leave as 16-byte multimem stores (8 lanes cover one 128-byte row
@@ -511,6 +580,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
             }
           }
         }
+      }
+      if (stage_q && ok) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_qs_full);  // release: this warp's part of the tile is staged
+        if (!mbar_wait_bounded(bar_qs_full, it & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+          ok = false;
+          break;
+        }
+        const uint32_t t = ew * 32u + uint32_t(lane);
+        const uint32_t trow0 = tm2 * 256u + rank * 128u, qcol0 = p.n_offset + n0;
+#pragma unroll
+        for (uint32_t pass = 0; pass < 4u; ++pass) {  // 8 lanes cover a row's 128 code bytes, 32 rows per pass
+          const uint32_t lr = pass * 32u + (t >> 3), c = t & 7u, grow = trow0 + lr;
+          if (grow < p.m && n0 + (c >> 1) * 64u < p.n)
+            multimem_st_v4(p.q_codes_mc + uint64_t(grow) * (p.ldo >> 1) + (qcol0 >> 1) + c * 16u,
+                           *reinterpret_cast<const uint4*>(stage_q + lr * 128u + ((c ^ (lr & 7u)) << 4)));
+        }
+        if (t < 128u && trow0 < p.m && n0 + (t >> 5) * 64u < p.n)  // four 512-byte scale atoms, 16 bytes per thread
+          multimem_st_v4(p.q_scales_mc + sf_device_offset(trow0, (qcol0 >> 4) + (t >> 5) * 4u, p.q_k_atoms) + (t & 31u) * 16u,
+                         *reinterpret_cast<const uint4*>(stage_q + 16384u + (t >> 5) * 512u + (t & 31u) * 16u));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_qs_free);
       }
       if (ttr) p.trace[1024 + it * 8 + 6] = clock64();
     }
@@ -552,7 +643,7 @@ bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k) {
 
 uint32_t gemm_pair_kblocks() { return 4u; }
 
-template <int KB>
+template <int KB, bool kDense>
 static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
                                   const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p_in,
                                   int sm_count, cudaStream_t s) {
@@ -563,14 +654,14 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= kMaxDevices) dev = 0;
   if (once.first_use() >= 0) {  // the shared-memory opt-in is a per-device attribute of the function
-    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(nvfp4_gemm_pair_kernel<KB, kDense>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(unsigned(sm_count & ~1), 1, 1);
     cfg.blockDim = dim3(pair::kThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     int clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemm_pair_kernel<KB>, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemm_pair_kernel<KB, kDense>, &cfg);
     if (e != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
       clusters = sm_count / 2;
@@ -587,14 +678,15 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
   const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs[dev] > 0 ? max_pairs[dev] : sm_count / 2));
   PairOutMaps om;
   for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
-  return launch_pdl(nvfp4_gemm_pair_kernel<KB>, dim3(pairs * 2), dim3(pair::kThreads), Cfg::kSmemBytes, s, map_a, map_w, map_sfa,
+  return launch_pdl(nvfp4_gemm_pair_kernel<KB, kDense>, dim3(pairs * 2), dim3(pair::kThreads), Cfg::kSmemBytes, s, map_a, map_w, map_sfa,
                     map_sfb, om, p);
 }
 
 cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
                                    const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
                                    int sm_count, cudaStream_t s) {
-  return launch_pair_kb<4>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s);
+  return p.dense ? launch_pair_kb<4, true>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s)
+                 : launch_pair_kb<4, false>(map_a, map_w, map_sfa, map_sfb, out_maps, p, sm_count, s);
 }
 
 }  // namespace tnf

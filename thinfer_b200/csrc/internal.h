@@ -93,6 +93,9 @@ struct GemmParams {
   uint16_t* out_mc;            // multicast alias of out[0] (null: plain stores); with it every store of the epilogue
   uint8_t* q_codes_mc;         //   (bf16 rows, NVFP4 codes, scale words) goes out as multimem.st and lands on
   uint8_t* q_scales_mc;        //   every rank of the group, this one included
+  uint32_t dense;              // dense-activation arm: A is bf16 [m,k], W the exact bf16 image of code x block scale
+                               // [n,k]; no scale factors, tcgen05.mma kind::f16 (pair kernel only)
+  uint32_t swiglu;             // pairwise gating epilogue: out[m, j] = silu(v[2j]) * v[2j+1], n/2 output columns
   uint32_t store_bf16;         // 0: skip the bf16 store
   uint32_t* status;            // device status word
   long long wait_limit;        // SM cycles after which a device-side wait gives up (0 = kDefaultWaitLimitCycles)
@@ -108,6 +111,8 @@ cudaError_t launch_global_scale(const uint32_t* amax_bits, float* g, cudaStream_
 cudaError_t launch_quantize(const void* src, int dtype, uint32_t rows, uint32_t k, const float* g_ptr, float g_val,
                             uint8_t* codes, uint8_t* scales, bool device_layout, cudaStream_t s);
 cudaError_t launch_multicast_copy(const uint8_t* src, uint8_t* dst_mc, uint64_t bytes, int sm_count, cudaStream_t s);
+cudaError_t launch_dequant_dense(const uint8_t* codes, const uint8_t* scales_device, uint32_t n, uint32_t k, uint16_t* out_bf16,
+                                 cudaStream_t s);
 cudaError_t launch_scales_to_device(const uint8_t* in, uint32_t rows, uint32_t k, uint8_t* out, cudaStream_t s);
 
 // tcgen05 GEMM. a_codes [m, k/2], w_codes [n, k/2]; tensor maps are built (and cached) by the caller.

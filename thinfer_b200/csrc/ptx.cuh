@@ -212,14 +212,16 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 
 // ---- NVSwitch multicast stores -----------------------------------------------------------------------
 // A store to the multicast alias of a symmetric allocation is replicated by the switch into every
-// rank's copy at the same offset (bits are moved unchanged; the .f32 type only names the width).
+// rank's copy at the same offset (bits are moved unchanged; the .f32 type only names the width). Weak stores:
+// the kernels end with a system-scope fence, and the ranks meet at a barrier before anyone reads (relaxed.sys
+// stores measured the same).
 __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
                "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
                : "memory");
 }
 __device__ __forceinline__ void multimem_st_b32(void* mc_addr, uint32_t v) {
-  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(__uint_as_float(v)) : "memory");
+  asm volatile("multimem.st.weak.global.f32 [%0], %1;" ::"l"(mc_addr), "f"(__uint_as_float(v)) : "memory");
 }
 
 // ---- tcgen05, CTA-pair forms ------------------------------------------------------------------
@@ -252,6 +254,16 @@ __device__ __forceinline__ void tc_mma_nvfp4_pair(uint32_t d_tmem, uint64_t ades
       : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem], bf16 operands, f32 accumulator (the dense-activation arm).
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---- descriptors ----------------------------------------------------------------------------
 // Shared-memory matrix descriptor, K-major operand rows of 128 bytes, 128-byte swizzle:
 // start>>4 | LBO(1)<<16 | SBO(1024>>4)<<32 | version 1<<46 | SWIZZLE_128B(2)<<61.
@@ -265,6 +277,11 @@ __device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
 }
 // Instruction descriptor, kind::mxf4nvf4: A/B E2M1 (format 1), both K-major, UE4M3 scales,
 // N>>3 at bit 17, M>>4 at bit 24, K = 64.
+// Instruction descriptor, kind::f16 with bf16 A and B (format 1 each), both K-major, f32 accumulator (format 1 at
+// bit 4), N>>3 at bit 17, M>>4 at bit 24, K = 16.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t m, uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
 __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t m, uint32_t n) {
   return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }

@@ -150,7 +150,43 @@ __global__ void scales_to_device_kernel(const uint8_t* __restrict__ in, uint32_t
   out[sf_device_offset(r, b, k_atoms)] = (r < rows && b < nb) ? in[uint64_t(r) * nb + b] : uint8_t(0);
 }
 
+// NVFP4 weight -> the dense bf16 image the dense-activation arm multiplies with: code x block scale WITHOUT the
+// per-tensor scale, which the GEMM epilogue applies. E2M1 has two significant bits and E4M3 four, so every
+// product is exact in bf16 (and below 6 * 448): the image loses nothing. One thread per 16-element block.
+__device__ __forceinline__ float e2m1_decode_dev(uint32_t c) {
+  const uint32_t m = c & 7u;
+  const float v = m < 2u ? 0.5f * float(m) : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));  // 0, .5, 1, 1.5, 2, 3, 4, 6
+  return (c & 8u) ? -v : v;
+}
+__global__ void dequant_dense_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales_device, uint32_t n,
+                                     uint32_t nb, uint32_t k_atoms, uint16_t* __restrict__ out) {
+  uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= uint64_t(n) * nb) return;
+  const uint32_t r = uint32_t(t / nb), b = uint32_t(t % nb);
+  const float d = e4m3_decode_dev(scales_device[sf_device_offset(r, b, k_atoms)] & 0x7Fu);
+  const uint2 cw = *reinterpret_cast<const uint2*>(codes + (uint64_t(r) * nb + b) * 8u);
+  const uint32_t w[2] = {cw.x, cw.y};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t by = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+    __nv_bfloat162 pk = __floats2bfloat162_rn(e2m1_decode_dev(by & 0xFu) * d, e2m1_decode_dev(by >> 4) * d);
+    o[i] = *reinterpret_cast<uint32_t*>(&pk);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + (uint64_t(r) * nb + b) * 16u);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 // ---- launchers ----------------------------------------------------------------------------------
+cudaError_t launch_dequant_dense(const uint8_t* codes, const uint8_t* scales_device, uint32_t n, uint32_t k, uint16_t* out_bf16,
+                                 cudaStream_t s) {
+  const uint64_t threads = uint64_t(n) * (k >> 4);
+  if (threads == 0) return cudaSuccess;
+  dequant_dense_kernel<<<unsigned((threads + 255) / 256), 256, 0, s>>>(codes, scales_device, n, k >> 4, sf_k_atoms(k), out_bf16);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_amax(const void* x, int dtype, uint64_t n, uint32_t* amax_bits, cudaStream_t s) {
   cudaError_t e = cudaMemsetAsync(amax_bits, 0, 4, s);
   if (e != cudaSuccess) return e;

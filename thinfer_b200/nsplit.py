@@ -240,26 +240,43 @@ class MulticastFfn:
         self.stage_c = be.allocate(max(rows_cap * hidden // 2, 256))
         self.stage_s = be.allocate(device_scales_bytes(rows_cap, hidden))
 
-    def step(self, x_rows: Buf) -> None:
-        """One pass. ``x_rows`` is this rank's row block of x (bf16 [rows, hidden], rows from ``row_partition``)."""
+    def step(self, x_rows: Buf, mark=None, multicast: bool = True) -> None:
+        """One pass. ``x_rows`` is this rank's row block of x (bf16 [rows, hidden], rows from ``row_partition``).
+        ``mark(label)``, if given, is called after every stage has been queued (for event timing).
+        ``multicast=False`` runs the same kernels with plain local stores and no barriers (each rank then only
+        holds its own rows of x and its own column windows: for timing the arithmetic alone)."""
         be, lib, ctx = self.grp.be, self.grp.be.lib, self.grp.be._ctx
         sc = be.scope()
+        mark = mark or (lambda label: None)
+        flags = L.LINEAR_MULTICAST_OUT if multicast else 0
         if self.rows:
-            g = C.c_float()
-            _check(lib.tnf_quantize_act(ctx, x_rows, self.rows, self.hidden, self.ga_x, L.SCALES_DEVICE, self.stage_c,
-                                        self.stage_s, None))
-            _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_c.id, 0, self.rows * self.hidden // 2), self.xq_c.buf.id,
-                                          self.row0 * self.hidden // 2, self.rows * self.hidden // 2))
             nblk = (self.rows + 127) // 128
-            _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_s.id, 0, nblk * self.x_scale_block), self.xq_s.buf.id,
-                                          (self.row0 // 128) * self.x_scale_block, nblk * self.x_scale_block))
-        self.y.barrier(0)
+            c_bytes, s_bytes = self.rows * self.hidden // 2, nblk * self.x_scale_block
+            c_off, s_off = self.row0 * self.hidden // 2, (self.row0 // 128) * self.x_scale_block
+            if multicast:
+                _check(lib.tnf_quantize_act(ctx, x_rows, self.rows, self.hidden, self.ga_x, L.SCALES_DEVICE, self.stage_c,
+                                            self.stage_s, None))
+                _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_c.id, 0, c_bytes), self.xq_c.buf.id, c_off, c_bytes))
+                _check(lib.tnf_multicast_copy(ctx, Buf(self.stage_s.id, 0, s_bytes), self.xq_s.buf.id, s_off, s_bytes))
+            else:
+                _check(lib.tnf_quantize_act(ctx, x_rows, self.rows, self.hidden, self.ga_x, L.SCALES_DEVICE,
+                                            Buf(self.xq_c.buf.id, c_off, c_bytes), Buf(self.xq_s.buf.id, s_off, s_bytes), None))
+        mark("quantise own rows of x" + (" + multicast" if multicast else ""))
+        if multicast:
+            self.y.barrier(0)
+            mark("barrier")
         sc.matmul(self.xq_c.buf, self.xq_s.buf, self.m, self.w_up, self.ga_x, None, act=L.ACT_GELU_TANH, n_offset=self.up_off,
-                  ldo=self.ffn, flags=L.LINEAR_MULTICAST_OUT, out_nvfp4=(self.hq_c.buf, self.hq_s.buf, self.ga_h))
-        self.y.barrier(1)
+                  ldo=self.ffn, flags=flags, out_nvfp4=(self.hq_c.buf, self.hq_s.buf, self.ga_h))
+        mark("up + GELU -> H (NVFP4)" + (", multicast" if multicast else ""))
+        if multicast:
+            self.y.barrier(1)
+            mark("barrier")
         sc.matmul(self.hq_c.buf, self.hq_s.buf, self.m, self.w_dn, self.ga_h, self.y.buf, n_offset=self.dn_off, ldo=self.hidden,
-                  flags=L.LINEAR_MULTICAST_OUT)
-        self.y.barrier(0)
+                  flags=flags)
+        mark("down -> y (bf16)" + (", multicast" if multicast else ""))
+        if multicast:
+            self.y.barrier(0)
+            mark("barrier")
 
     def free(self) -> None:
         for b in (self.xq_c, self.xq_s, self.hq_c, self.hq_s, self.y):
