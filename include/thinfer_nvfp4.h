@@ -93,6 +93,15 @@ int32_t tnf_sync(tnf_ctx* ctx, uint32_t timeout_ms);
  * workspace, live staging, peak weights, peak workspace, peak staging, true concurrent
  * peak, bytes streamed host->device since creation}. */
 int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]);
+/* MemArbiter::reclaim_until_fits (thinfer-core/src/arbiter.rs:129-160): an allocation that does not fit the
+ * budget first asks the registered holders of weight memory (every tnf_stack of the context: WeightReclaimer,
+ * thinfer-core/src/residency.rs:1473-1547) to give memory back -- resident weight sets, largest first; a set that
+ * is given back is streamed through its ring from the next step on -- and is refused with
+ * TNF_ERR_BUDGET_EXCEEDED only if that was not enough. *bytes = total given back so far. */
+int32_t tnf_reclaimed_bytes(tnf_ctx* ctx, uint64_t* bytes);
+/* set_transient_reserve (thinfer-core/src/residency.rs:535-537): bytes of the budget that weight plans
+ * (tnf_stack_create with a context budget, tnf_stack_restore) leave free for transient workspace. */
+int32_t tnf_set_transient_reserve(tnf_ctx* ctx, uint64_t bytes);
 /* Upper bound, in SM cycles, of every device-side wait of the kernels launched afterwards (a wait on a
  * loaded stage, a freed stage, a finished or drained accumulator). A wait that runs out makes its kernel
  * return normally with the status word set, and the next tnf_sync returns TNF_ERR_TIMEOUT: the analogue of a
@@ -313,6 +322,15 @@ int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* aux
 /* out = {resident weight bytes, ring bytes, bytes uploaded by the last step, uploads in
  * the last step, resident (layer, linear) records, streamed records}. */
 int32_t tnf_stack_stats(tnf_stack* st, uint64_t out[6]);
+/* Phase eviction (evict_all_and_free, thinfer-core/src/residency.rs:1415-1465): waits for the work in flight and
+ * frees every weight buffer of the stack (resident sets and rings), so that another consumer of the same budget
+ * -- a VAE phase, a second model -- can run. The records stay in the pinned host arena; the next
+ * tnf_stack_step (or tnf_stack_restore) re-plans under what the budget then allows and uploads again. */
+int32_t tnf_stack_evict_all(tnf_stack* st);
+/* Re-plans and re-uploads the stack's weights now. weight_budget_bytes = 0 keeps the budget given at creation;
+ * either is capped by what the context's budget leaves beside the other live buffers and the transient
+ * reserve. Also undoes demotions made by the reclaim chain once memory is free again. */
+int32_t tnf_stack_restore(tnf_stack* st, uint64_t weight_budget_bytes);
 int32_t tnf_stack_destroy(tnf_stack* st);
 
 /* ---- container: GGUF-v3 header parser + tensor catalog ------------------------------- */

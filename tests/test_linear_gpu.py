@@ -85,6 +85,35 @@ def test_epilogue_modes(backend, mode):
         backend.free(rb)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (3, 520, 1056), (8, 264, 4128), (4, 136, 64)])
+@pytest.mark.parametrize("mode", ["gelu", "gelu_chain", "gate"])
+def test_skinny_kernel_epilogue_modes(backend, m, n, k, mode):
+    """M <= 8 runs the one-launch skinny kernel (activation quantiser in the prologue, weights streamed on the CUDA
+    cores): same contract, same epilogue variants, K not a multiple of its 1024-element warp step."""
+    a, w, b = _inputs(m, n, k, 300 + m)
+    wc, ws, gw = O.quantize_weight(w)
+    ga = O.global_scale(O.amax_bf16(a))
+    kw, okw, extra = {}, {}, []
+    if mode.startswith("gelu"):
+        kw["act"] = okw["act"] = 1
+    if mode.endswith("chain"):
+        kw["chain"] = okw["chain"] = True
+    if mode == "gate":
+        gate = O.f32_to_bf16(O.gaussian(n, 0xD200))
+        res = O.f32_to_bf16(O.gaussian(m * n, 0xE200).reshape(m, n))
+        gb, rb = backend.upload(gate), backend.upload(res)
+        extra = [gb, rb]
+        kw.update(gate=gb, residual=rb)
+        okw.update(gate=gate, residual=res)
+    got, _, _ = _run(backend, a, w, b, **kw)
+    want = O.linear(a, ga, wc, ws, gw, bias=b, **okw)
+    assert not np.isnan(O.bf16_to_f32(got)).any()
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
+    assert (got == want).mean() > (0.9 if mode == "gelu" else 0.98)
+    for buf in extra:
+        backend.free(buf)
+
+
 def test_golden_vectors(backend, golden_nvfp4):
     import thinfer_b200 as T
 

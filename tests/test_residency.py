@@ -101,6 +101,80 @@ def test_stack_streamed_equals_resident_and_oracle(backend):
 
 
 @pytest.mark.gpu
+def test_reclaim_chain_phase_eviction_and_restore():
+    """The reclaim side of the residency manager. Under a context budget: (1) an allocation that does not fit first
+    makes the stack give resident weight sets back (they are streamed from then on) and then succeeds; (2) a
+    phase eviction frees every weight buffer; the next step brings the weights back by itself; (3) a restore after
+    the other consumer is gone pins everything again. The step's outputs never change."""
+    import thinfer_b200 as T
+    from thinfer_b200.backend import BudgetExceeded
+    from thinfer_b200.residency import StackLinearSpec as S, record_bytes
+
+    hidden, layers, a_global = 128, 9, 0.004
+    specs = [S(384, 128, 0, True, 0, 0), S(128, 384, 0, True, 1, 0)]
+    weights = layers * sum(record_bytes(s.n, s.k) for s in specs)
+    be = T.Backend(0, vram_budget=weights + (6 << 20))  # everything resident fits, with 6 MiB to spare
+    try:
+        st, _ = _build(be, layers, specs, [160], hidden, 700)
+        x = O.f32_to_bf16(O.gaussian(160 * hidden, 41).reshape(160, hidden))
+        xb, ob = [be.upload(x)], [be.allocate(160 * hidden * 2)]
+        info = st.build(weight_budget=0, ring_slots=2)
+        assert info["streamed_records"] == 0
+
+        def run():
+            st.step(xb, ob, a_global)
+            be.submit(30000)
+            return be.read_buffer(ob[0], np.uint16).copy()
+
+        ref = run()
+        # (1) another consumer takes most of the spare room and then some: the stack must give memory back
+        spare = be.mem_snapshot()
+        room = weights + (6 << 20) - (spare["live_weights"] + spare["live_workspace"] + spare["live_staging"])
+        other = be.allocate_in(room + weights // 3, 1)
+        got = C_u64()
+        be.lib.tnf_reclaimed_bytes(be._ctx, got)
+        assert got.value >= weights // 3 - 2 * max(record_bytes(s.n, s.k) for s in specs) * 2
+        s1 = st.stats()
+        assert s1["streamed_records"] > 0 and s1["resident_bytes"] < info["resident_bytes"]
+        assert np.array_equal(run(), ref) and np.array_equal(run(), ref)  # the second step finds its rings in flight
+        with pytest.raises(BudgetExceeded):  # nothing more to give that would make this fit
+            be.allocate_in(weights * 4, 1)
+        # (2) phase eviction: all weight memory goes, the records stay in the pinned arena
+        st.evict_all()
+        assert be.mem_snapshot()["live_weights"] == 0
+        assert np.array_equal(run(), ref)  # the step restored what the budget allows by itself
+        # (3) the other consumer leaves: restore pins everything again
+        be.free(other)
+        s3 = st.restore()
+        assert s3["streamed_records"] == 0 and s3["resident_bytes"] == info["resident_bytes"]
+        assert np.array_equal(run(), ref)
+        # transient reserve: a plan leaves that much of the budget free
+        from thinfer_b200.backend import _check
+        snap = be.mem_snapshot()
+        budget = weights + (6 << 20)
+        reserve = budget - snap["live_workspace"] - snap["live_staging"] - int(0.6 * weights)  # leaves room for 60 % of the weights
+        _check(be.lib.tnf_set_transient_reserve(be._ctx, reserve))
+        s4 = st.restore()
+        live = be.mem_snapshot()
+        assert live["live_weights"] + live["live_workspace"] + live["live_staging"] + reserve <= budget
+        _check(be.lib.tnf_set_transient_reserve(be._ctx, budget))  # no room at all: refused on the host, weights stay evicted
+        with pytest.raises(BudgetExceeded):
+            st.restore()
+        _check(be.lib.tnf_set_transient_reserve(be._ctx, reserve))
+        s4 = st.restore()
+        assert s4["streamed_records"] > 0 and np.array_equal(run(), ref)
+        st.close()
+    finally:
+        be.close()
+
+
+def C_u64():
+    import ctypes
+
+    return ctypes.c_uint64()
+
+
+@pytest.mark.gpu
 def test_stack_budget_below_ring_reserve_is_refused(backend):
     from thinfer_b200.backend import BudgetExceeded
     from thinfer_b200.residency import StackLinearSpec as S

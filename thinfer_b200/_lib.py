@@ -113,6 +113,10 @@ SIGNATURES = {
     "tnf_stack_step": (C.c_int32, [C.c_void_p, _u64p, _u64p, _u64p, C.c_float]),
     "tnf_stack_stats": (C.c_int32, [C.c_void_p, _u64p]),
     "tnf_stack_destroy": (C.c_int32, [C.c_void_p]),
+    "tnf_stack_evict_all": (C.c_int32, [C.c_void_p]),
+    "tnf_stack_restore": (C.c_int32, [C.c_void_p, C.c_uint64]),
+    "tnf_reclaimed_bytes": (C.c_int32, [_ctx, _u64p]),
+    "tnf_set_transient_reserve": (C.c_int32, [_ctx, C.c_uint64]),
     "tnf_gguf_parse": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p), _u64p]),
     "tnf_gguf_free": (C.c_int32, [C.c_void_p]),
     "tnf_gguf_info": (C.c_int32, [C.c_void_p, _u64p]),

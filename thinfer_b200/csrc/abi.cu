@@ -80,6 +80,18 @@ int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id) {
     return TNF_ERR_INVALID_ARGUMENT;
   }
   uint64_t total = ctx->live[0] + ctx->live[1] + ctx->live[2];
+  if (ctx->budget && total + bytes > ctx->budget && !ctx->in_reclaim) {
+    // reclaim_until_fits (thinfer-core/src/arbiter.rs:129-160): ask the registered holders, in order, to give
+    // memory back before refusing; a holder frees whole weight sets and streams them from then on
+    ctx->in_reclaim = true;
+    for (auto& r : ctx->reclaimers) {
+      total = ctx->live[0] + ctx->live[1] + ctx->live[2];
+      if (total + bytes <= ctx->budget) break;
+      ctx->reclaimed += r.fn(r.owner, total + bytes - ctx->budget);
+    }
+    ctx->in_reclaim = false;
+    total = ctx->live[0] + ctx->live[1] + ctx->live[2];
+  }
   if (ctx->budget && total + bytes > ctx->budget) {
     // refused on the host; the device is not touched
     set_error("budget exceeded: live %llu + request %llu > budget %llu", (unsigned long long)total,
@@ -235,7 +247,9 @@ static int32_t check_dims(uint32_t m, uint32_t n, uint32_t k) {
 }
 
 // shared tail of tnf_linear_nvfp4 / tnf_gemm_nvfp4
-static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales) {
+// `a_raw` non-null: the skinny-M kernel takes the bf16 activations themselves (its prologue is the quantiser).
+static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales,
+                        const uint8_t* a_raw = nullptr) {
   int32_t st = TNF_OK;
   const bool swiglu = (a->flags & TNF_LINEAR_SWIGLU) != 0;
   const uint32_t n_out_cols = swiglu ? a->n / 2 : a->n;  // columns this call writes
@@ -344,6 +358,10 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.status = ctx->dwords;
   p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
+  if (a_raw) {
+    TNF_CUDA(launch_gemv_nvfp4(a_raw, a->a_global, w_codes, p, ctx->compute), "nvfp4 skinny-M launch");
+    return TNF_OK;
+  }
   CUtensorMap ma, mw;
   if (dense || swiglu || q_out || mc_out || gemm_use_pair(a->m, a->n, a->k)) {  // only the CTA-pair kernel has the dense arm and the NVFP4 / multicast epilogues
     const uint32_t kb = gemm_pair_kblocks();
@@ -598,6 +616,26 @@ int32_t tnf_debug_trace(tnf_ctx* ctx, unsigned long long* dst_2048) {
 }
 #endif
 
+int32_t tnf_reclaimed_bytes(tnf_ctx* ctx, uint64_t* bytes) {
+  if (!ctx || !bytes) {
+    set_error("tnf_reclaimed_bytes: null argument");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  *bytes = ctx->reclaimed;
+  return TNF_OK;
+}
+
+int32_t tnf_set_transient_reserve(tnf_ctx* ctx, uint64_t bytes) {
+  if (!ctx) {
+    set_error("null context");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  ctx->transient_reserve = bytes;
+  return TNF_OK;
+}
+
 int32_t tnf_set_device_wait_limit(tnf_ctx* ctx, uint64_t sm_cycles) {
   if (!ctx) {
     set_error("null context");
@@ -807,6 +845,12 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
     if (!src) return st;
     return run_gemm(ctx, a, src, nullptr);
+  }
+  if (a->flags == 0 && gemv_applies(a->m, a->n, a->k)) {
+    // a handful of rows: one launch that quantises A in its prologue and streams W (no scratch, no quantiser launch)
+    uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
+    if (!src) return st;
+    return run_gemm(ctx, a, nullptr, nullptr, src);
   }
   if (!(a->flags & TNF_LINEAR_A_PREQUANTIZED)) {
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);

@@ -366,11 +366,11 @@ int32_t tnf_push_peers(tnf_ctx* ctx, int32_t set, tnf_buf src, uint64_t dst_offs
     e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
     if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
   }
-  // copies go out in ring order (next rank first), so with one lane every rank receives from one sender
-  // at a time; TNF_PUSH_STREAMS=k spreads them over k streams (measured: no gain with 3 peers, a loss with 7)
+  // copies go out in ring order (next rank first), so with one lane every rank receives from one sender at a
+  // time. More lanes measured no gain with 3 peers and a loss with 7; diagnostic builds can still try (TNF_PUSH_STREAMS).
   const int np = ctx->n_peers[set];
   static const int want_lanes = [] {
-    const char* v = std::getenv("TNF_PUSH_STREAMS");
+    const char* v = kDiag ? std::getenv("TNF_PUSH_STREAMS") : nullptr;
     const int k = v ? std::atoi(v) : 1;
     return k < 1 ? 1 : (k > 8 ? 8 : k);
   }();

@@ -28,6 +28,14 @@ struct tnf_host_rec {
   bool owned = false;  // cudaHostAlloc'ed by us (else cudaHostRegister'ed in place)
 };
 
+// A holder of device memory that can give some back when an allocation does not fit the budget: the
+// WeightReclaimer the reference registers with its arbiter (thinfer-core/src/residency.rs:1473-1547,
+// thinfer-core/src/arbiter.rs:129-160). `fn` is called with the context's mutex held and returns the bytes it freed.
+struct tnf_reclaimer {
+  void* owner = nullptr;
+  uint64_t (*fn)(void* owner, uint64_t want_bytes) = nullptr;
+};
+
 struct tnf_ctx {
   int device = 0;
   int sm_count = 148;
@@ -45,6 +53,10 @@ struct tnf_ctx {
   std::vector<cudaEvent_t> event_pool;
   // MemAccount: live and peak per category, true concurrent peak, streamed bytes
   uint64_t live[3] = {0, 0, 0}, peak[3] = {0, 0, 0}, true_peak = 0, streamed = 0;
+  std::vector<tnf_reclaimer> reclaimers;  // asked in registration order by alloc_locked before it refuses
+  bool in_reclaim = false;
+  uint64_t reclaimed = 0;                 // bytes given back by reclaimers so far
+  uint64_t transient_reserve = 0;         // bytes of the budget a weight plan leaves free for transient workspace
   // scratch for on-the-fly activation quantisation (workspace category)
   uint64_t scratch_codes_id = 0, scratch_scales_id = 0;
   uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;

@@ -122,6 +122,9 @@ cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w
 cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_sfa,
                                    const CUtensorMap& map_sfb, const CUtensorMap* out_maps, const GemmParams& p,
                                    int sm_count, cudaStream_t s);
+// Skinny-M kernel (M <= 8): activation quantiser + weight streaming on the CUDA cores in one launch.
+bool gemv_applies(uint32_t m, uint32_t n, uint32_t k);
+cudaError_t launch_gemv_nvfp4(const void* a_bf16, float a_global, const uint8_t* w_codes, const GemmParams& p, cudaStream_t s);
 bool gemm_use_pair(uint32_t m, uint32_t n, uint32_t k);
 uint32_t gemm_pair_kblocks();  // 64-element K blocks per pipeline stage of the pair kernel (2 or 4): sets the TMA boxes
 

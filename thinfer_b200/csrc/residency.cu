@@ -50,6 +50,7 @@ struct Role {  // one linear of the layer, across all layers
   std::vector<cudaEvent_t> ready, freed;
   std::vector<int64_t> holds;    // streamed-layer sequence number each slot holds or is being filled with
   int64_t next_upload = 0;       // next streamed-layer sequence number to upload (monotonic, cyclic modulo streamed)
+  int64_t epoch_step = 0;        // the stack's step count when this role's plan was last (re)made: sequences restart there
   uint64_t out_id = 0;           // workspace for this linear's output [m, n]
 };
 
@@ -66,6 +67,11 @@ struct tnf_stack {
   uint64_t layer_bytes = 0;
   uint64_t pinned_bytes = 0, ring_bytes = 0, uploaded_last = 0, uploads_last = 0;
   int64_t steps_done = 0;
+  uint64_t weight_budget = 0;  // as given at creation (0 = unlimited)
+  uint32_t ring_slots = 4;
+  bool in_step = false;        // a step is being enqueued: the reclaimer must not change the plan under it
+  bool evicted = false;        // tnf_stack_evict_all ran: the next step (or tnf_stack_restore) brings the weights back
+  uint64_t demoted_bytes = 0;  // resident bytes given back to the arbiter's reclaim chain so far
 };
 
 using namespace tnf;
@@ -89,6 +95,147 @@ static int32_t upload_record(tnf_stack* st, Role& r, int64_t seq) {
   st->uploaded_last += r.lay.bytes;
   st->uploads_last += 1;
   return TNF_OK;
+}
+
+
+// ---- plan / materialise / release: the three steps behind create, restore, evict and reclaim --------------------
+// Role-major pin plan under `budget` bytes for resident + ring weights (0 = unlimited): every role starts streamed
+// (a ring of `slots` records); roles are then pinned whole, largest first, while the budget allows; one more role
+// may be pinned in part. Returns false when the budget is below the ring reserve.
+static bool plan_roles(tnf_stack* st, uint64_t budget, uint64_t* need_rings_out) {
+  const uint32_t layers = st->layers, slots = std::min<uint32_t>(st->ring_slots, layers);
+  uint64_t need_rings = 0;
+  for (auto& r : st->roles) need_rings += uint64_t(slots) * r.lay.bytes;
+  if (need_rings_out) *need_rings_out = need_rings;
+  if (budget && need_rings > budget) return false;
+  std::vector<uint32_t> order(st->roles.size());
+  for (uint32_t j = 0; j < order.size(); ++j) order[j] = j;
+  std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return st->roles[a].lay.bytes > st->roles[b].lay.bytes; });
+  uint64_t avail = budget ? budget - need_rings : ~0ull;
+  bool partial_done = false;
+  for (auto& r : st->roles) r.pinned_layers = 0;
+  for (uint32_t j : order) {
+    Role& r = st->roles[j];
+    const uint64_t full_cost = uint64_t(layers - slots) * r.lay.bytes;  // the ring's bytes are given back
+    if (layers <= slots || full_cost <= avail) {
+      r.pinned_layers = layers;
+      if (layers > slots) avail -= full_cost;
+    } else if (!partial_done) {
+      r.pinned_layers = uint32_t(std::min<uint64_t>(avail / r.lay.bytes, layers - slots));
+      avail -= uint64_t(r.pinned_layers) * r.lay.bytes;
+      partial_done = true;
+    }
+  }
+  return true;
+}
+
+// Frees a role's weight buffers (resident set and ring) and its ring events. Context mutex held; the caller has
+// made sure no work in flight still reads them.
+static void release_role_locked(tnf_stack* st, Role& r) {
+  tnf_ctx* ctx = st->ctx;
+  if (r.pinned_id) {
+    st->pinned_bytes -= ctx->bufs[r.pinned_id].bytes;
+    free_locked(ctx, r.pinned_id);
+  }
+  if (r.ring_id) {
+    st->ring_bytes -= ctx->bufs[r.ring_id].bytes;
+    free_locked(ctx, r.ring_id);
+  }
+  r.pinned_id = r.ring_id = 0;
+  for (auto e : r.ready) cudaEventDestroy(e);
+  for (auto e : r.freed) cudaEventDestroy(e);
+  r.ready.clear();
+  r.freed.clear();
+  r.holds.clear();
+  r.slots = 0;
+}
+
+// Allocates what r.pinned_layers asks for (resident buffer, ring, ring events created signalled) and restarts the
+// role's upload sequence at the current step. Context mutex held.
+static int32_t materialise_role_locked(tnf_stack* st, Role& r) {
+  tnf_ctx* ctx = st->ctx;
+  const uint32_t layers = st->layers, slots = std::min<uint32_t>(st->ring_slots, layers);
+  int32_t status = TNF_OK;
+  if (r.pinned_layers) {
+    status = alloc_locked(ctx, uint64_t(r.pinned_layers) * r.lay.bytes, TNF_CAT_WEIGHTS, &r.pinned_id);
+    if (status != TNF_OK) return status;
+    st->pinned_bytes += uint64_t(r.pinned_layers) * r.lay.bytes;
+  }
+  if (r.pinned_layers < layers) {
+    r.slots = std::min<uint32_t>(slots, layers - r.pinned_layers);
+    status = alloc_locked(ctx, uint64_t(r.slots) * r.lay.bytes, TNF_CAT_WEIGHTS, &r.ring_id);
+    if (status != TNF_OK) return status;
+    st->ring_bytes += uint64_t(r.slots) * r.lay.bytes;
+  }
+  for (uint32_t i = 0; i < r.slots; ++i) {
+    cudaEvent_t a, b;
+    cudaEventCreateWithFlags(&a, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&b, cudaEventDisableTiming);
+    r.ready.push_back(a);
+    r.freed.push_back(b);
+    r.holds.push_back(-1);
+  }
+  r.next_upload = 0;
+  r.epoch_step = st->steps_done;
+  return TNF_OK;
+}
+
+// Queues the upload of a role's resident records on the copy stream.
+static int32_t upload_pinned(tnf_stack* st, Role& r) {
+  if (!r.pinned_layers) return TNF_OK;
+  tnf_ctx* ctx = st->ctx;
+  uint8_t* dst = static_cast<uint8_t*>(ctx->bufs[r.pinned_id].ptr);
+  for (uint32_t l = 0; l < r.pinned_layers; ++l) {
+    cudaError_t ce = cudaMemcpyAsync(dst + uint64_t(l) * r.lay.bytes, st->host_base + uint64_t(l) * st->layer_bytes + r.layer_off,
+                                     r.lay.bytes, cudaMemcpyHostToDevice, ctx->copy);
+    if (ce != cudaSuccess) return cuda_fail(ce, "stack: resident upload");
+  }
+  return TNF_OK;
+}
+
+// The stack's entry in the arbiter's reclaim chain (WeightReclaimer, thinfer-core/src/residency.rs:1473-1547):
+// resident weight sets are given back largest first; a role that loses its resident set is streamed through a ring
+// from the next step on. Work in flight is waited for once, before the first free. Context mutex held.
+static uint64_t stack_reclaim(void* owner, uint64_t want) {
+  tnf_stack* st = static_cast<tnf_stack*>(owner);
+  if (st->evicted || st->in_step) return 0;
+  std::vector<uint32_t> order;
+  for (uint32_t j = 0; j < st->roles.size(); ++j)
+    if (st->roles[j].pinned_layers > std::min<uint32_t>(st->ring_slots, st->layers)) order.push_back(j);
+  std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) {
+    return uint64_t(st->roles[a].pinned_layers) * st->roles[a].lay.bytes > uint64_t(st->roles[b].pinned_layers) * st->roles[b].lay.bytes;
+  });
+  uint64_t freed = 0;
+  bool synced = false;
+  for (uint32_t j : order) {
+    if (freed >= want) break;
+    Role& r = st->roles[j];
+    if (!synced) {
+      cudaStreamSynchronize(st->ctx->compute);
+      cudaStreamSynchronize(st->ctx->copy);
+      synced = true;
+    }
+    const uint64_t before = uint64_t(r.pinned_layers) * r.lay.bytes + uint64_t(r.slots) * r.lay.bytes;
+    release_role_locked(st, r);
+    r.pinned_layers = 0;
+    if (materialise_role_locked(st, r) != TNF_OK) continue;  // the ring always fits: it is smaller than what was freed
+    const uint64_t after = uint64_t(r.slots) * r.lay.bytes;
+    freed += before - after;
+  }
+  st->demoted_bytes += freed;
+  return freed;
+}
+
+// The weight budget a plan may use now: the configured one, capped by what the context's budget leaves after
+// everything that is not this stack's weights and after the transient reserve.
+static uint64_t effective_budget(tnf_stack* st, uint64_t configured) {
+  tnf_ctx* ctx = st->ctx;
+  if (!ctx->budget) return configured;
+  const uint64_t live = ctx->live[0] + ctx->live[1] + ctx->live[2];
+  const uint64_t own = st->pinned_bytes + st->ring_bytes;
+  const uint64_t others = live - own + ctx->transient_reserve;
+  const uint64_t room = ctx->budget > others ? ctx->budget - others : 1;  // 0 would read as "unlimited"
+  return configured ? std::min(configured, room) : room;
 }
 
 extern "C" {
@@ -156,50 +303,22 @@ int32_t tnf_stack_create(tnf_ctx* ctx, uint32_t layers, uint32_t n_linears, cons
     delete st;
     return TNF_ERR_INVALID_ARGUMENT;
   }
-  // ---- pin plan: role-major. Every role starts streamed (ring of `slots` records); roles are
-  // then pinned whole, largest first, while the budget allows; one more role may be pinned in part.
-  const uint32_t slots = std::min<uint32_t>(ring_slots, layers);
+  // ---- pin plan, device memory, resident uploads
+  st->weight_budget = weight_budget_bytes;
+  st->ring_slots = ring_slots;
   uint64_t need_rings = 0;
-  for (auto& r : st->roles) need_rings += uint64_t(slots) * r.lay.bytes;
-  if (weight_budget_bytes && need_rings > weight_budget_bytes) {
+  if (!plan_roles(st, weight_budget_bytes, &need_rings)) {
     set_error("weight budget %llu is below the ring reserve %llu (%u slots per linear)",
-              (unsigned long long)weight_budget_bytes, (unsigned long long)need_rings, slots);
+              (unsigned long long)weight_budget_bytes, (unsigned long long)need_rings, std::min<uint32_t>(ring_slots, layers));
     delete st;
     return TNF_ERR_BUDGET_EXCEEDED;  // refused on the host; the device is not touched
   }
-  std::vector<uint32_t> order(n_linears);
-  for (uint32_t j = 0; j < n_linears; ++j) order[j] = j;
-  std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return st->roles[a].lay.bytes > st->roles[b].lay.bytes; });
-  uint64_t avail = weight_budget_bytes ? weight_budget_bytes - need_rings : ~0ull;
-  bool partial_done = false;
-  for (uint32_t j : order) {
-    Role& r = st->roles[j];
-    const uint64_t full_cost = uint64_t(layers - slots) * r.lay.bytes;  // the ring's bytes are given back
-    if (layers <= slots || full_cost <= avail) {
-      r.pinned_layers = layers;
-      if (layers > slots) avail -= full_cost;
-    } else if (!partial_done) {
-      r.pinned_layers = uint32_t(std::min<uint64_t>(avail / r.lay.bytes, layers - slots));
-      avail -= uint64_t(r.pinned_layers) * r.lay.bytes;
-      partial_done = true;
-    }
-  }
-  // ---- device memory
   int32_t status = TNF_OK;
   {
     std::lock_guard<std::mutex> lk(ctx->mu);
     for (auto& r : st->roles) {
-      if (r.pinned_layers) {
-        status = alloc_locked(ctx, uint64_t(r.pinned_layers) * r.lay.bytes, TNF_CAT_WEIGHTS, &r.pinned_id);
-        if (status != TNF_OK) break;
-        st->pinned_bytes += uint64_t(r.pinned_layers) * r.lay.bytes;
-      }
-      if (r.pinned_layers < layers) {
-        r.slots = std::min<uint32_t>(slots, layers - r.pinned_layers);
-        status = alloc_locked(ctx, uint64_t(r.slots) * r.lay.bytes, TNF_CAT_WEIGHTS, &r.ring_id);
-        if (status != TNF_OK) break;
-        st->ring_bytes += uint64_t(r.slots) * r.lay.bytes;
-      }
+      status = materialise_role_locked(st, r);
+      if (status != TNF_OK) break;
       status = alloc_locked(ctx, std::max<uint64_t>(uint64_t(st->m_rows[r.desc.stream_id]) * r.desc.n * 2, 256), TNF_CAT_WORKSPACE, &r.out_id);
       if (status != TNF_OK) break;
     }
@@ -215,26 +334,11 @@ int32_t tnf_stack_create(tnf_ctx* ctx, uint32_t layers, uint32_t n_linears, cons
     tnf_stack_destroy(st);
     return status;
   }
-  // ---- resident records are uploaded once, here; ring events are created signalled
   for (auto& r : st->roles) {
-    if (r.pinned_layers) {
-      uint8_t* dst = static_cast<uint8_t*>(ctx->bufs[r.pinned_id].ptr);
-      for (uint32_t l = 0; l < r.pinned_layers; ++l) {
-        ce = cudaMemcpyAsync(dst + uint64_t(l) * r.lay.bytes, st->host_base + uint64_t(l) * st->layer_bytes + r.layer_off,
-                             r.lay.bytes, cudaMemcpyHostToDevice, ctx->copy);
-        if (ce != cudaSuccess) {
-          tnf_stack_destroy(st);
-          return cuda_fail(ce, "stack: resident upload");
-        }
-      }
-    }
-    for (uint32_t i = 0; i < r.slots; ++i) {
-      cudaEvent_t a, b;
-      cudaEventCreateWithFlags(&a, cudaEventDisableTiming);
-      cudaEventCreateWithFlags(&b, cudaEventDisableTiming);
-      r.ready.push_back(a);
-      r.freed.push_back(b);
-      r.holds.push_back(-1);
+    status = upload_pinned(st, r);
+    if (status != TNF_OK) {
+      tnf_stack_destroy(st);
+      return status;
     }
   }
   ce = cudaStreamSynchronize(ctx->copy);
@@ -242,7 +346,72 @@ int32_t tnf_stack_create(tnf_ctx* ctx, uint32_t layers, uint32_t n_linears, cons
     tnf_stack_destroy(st);
     return cuda_fail(ce, "stack: resident upload sync");
   }
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->reclaimers.push_back(tnf_reclaimer{st, stack_reclaim});
+  }
   *out = st;
+  return TNF_OK;
+}
+
+int32_t tnf_stack_evict_all(tnf_stack* st) {
+  if (!st) {
+    set_error("tnf_stack_evict_all: null stack");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  tnf_ctx* ctx = st->ctx;
+  cudaError_t ce = cudaSetDevice(ctx->device);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
+  cudaStreamSynchronize(ctx->compute);
+  cudaStreamSynchronize(ctx->copy);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  for (auto& r : st->roles) {
+    release_role_locked(st, r);
+    r.pinned_layers = 0;
+  }
+  st->evicted = true;
+  return TNF_OK;
+}
+
+int32_t tnf_stack_restore(tnf_stack* st, uint64_t weight_budget_bytes) {
+  if (!st) {
+    set_error("tnf_stack_restore: null stack");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  tnf_ctx* ctx = st->ctx;
+  cudaError_t ce = cudaSetDevice(ctx->device);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
+  cudaStreamSynchronize(ctx->compute);
+  cudaStreamSynchronize(ctx->copy);
+  if (weight_budget_bytes) st->weight_budget = weight_budget_bytes;
+  int32_t status = TNF_OK;
+  {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    for (auto& r : st->roles) release_role_locked(st, r);
+    uint64_t need_rings = 0;
+    const uint64_t budget = effective_budget(st, st->weight_budget);
+    if (!plan_roles(st, budget, &need_rings)) {
+      for (auto& r : st->roles) r.pinned_layers = 0;
+      st->evicted = true;
+      set_error("tnf_stack_restore: %llu bytes are available for weights, the rings alone need %llu",
+                (unsigned long long)budget, (unsigned long long)need_rings);
+      return TNF_ERR_BUDGET_EXCEEDED;
+    }
+    ctx->in_reclaim = true;  // a restore never asks other holders (or itself) to give memory back
+    for (auto& r : st->roles) {
+      status = materialise_role_locked(st, r);
+      if (status != TNF_OK) break;
+    }
+    ctx->in_reclaim = false;
+  }
+  if (status != TNF_OK) return status;
+  for (auto& r : st->roles) {
+    status = upload_pinned(st, r);
+    if (status != TNF_OK) return status;
+  }
+  ce = cudaStreamSynchronize(ctx->copy);
+  if (ce != cudaSuccess) return cuda_fail(ce, "stack: resident upload sync");
+  st->evicted = false;
   return TNF_OK;
 }
 
@@ -255,11 +424,20 @@ int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* aux
   tnf_ctx* ctx = st->ctx;
   cudaError_t ce = cudaSetDevice(ctx->device);
   if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
+  if (st->evicted) {  // a phase eviction happened: bring the weights back under what the budget allows now
+    int32_t s = tnf_stack_restore(st, 0);
+    if (s != TNF_OK) return s;
+  }
   st->uploaded_last = 0;
   st->uploads_last = 0;
-  // first use: fill every ring (later steps find their first layers already in flight)
+  struct InStep {
+    tnf_stack* s;
+    explicit InStep(tnf_stack* p) : s(p) { s->in_step = true; }
+    ~InStep() { s->in_step = false; }
+  } in_step_guard(st);
+  // first use of a ring (after creation, a restore or a reclaim): fill it; later steps find their first layers in flight
   for (auto& r : st->roles) {
-    while (r.slots && r.next_upload < int64_t(r.slots) && st->steps_done == 0) {
+    while (r.slots && r.next_upload < int64_t(r.slots) && st->steps_done == r.epoch_step) {
       int32_t s = upload_record(st, r, r.next_upload);
       if (s != TNF_OK) return s;
       ++r.next_upload;
@@ -307,7 +485,7 @@ int32_t tnf_stack_step(tnf_stack* st, const uint64_t* x_ids, const uint64_t* aux
         w_off = uint64_t(l) * r.lay.bytes;
       } else {
         const uint32_t streamed = st->layers - r.pinned_layers;
-        const int64_t seq = st->steps_done * int64_t(streamed) + int64_t(l - r.pinned_layers);
+        const int64_t seq = (st->steps_done - r.epoch_step) * int64_t(streamed) + int64_t(l - r.pinned_layers);
         slot = int(seq % r.slots);
         if (r.holds[slot] != seq) {
           set_error("stack: ring of linear %zu holds sequence %lld in slot %d, expected %lld", j, (long long)r.holds[slot],
@@ -378,12 +556,11 @@ int32_t tnf_stack_destroy(tnf_stack* st) {
   cudaStreamSynchronize(ctx->compute);
   {
     std::lock_guard<std::mutex> lk(ctx->mu);
+    for (auto it = ctx->reclaimers.begin(); it != ctx->reclaimers.end();)
+      it = it->owner == st ? ctx->reclaimers.erase(it) : it + 1;
     for (auto& r : st->roles) {
-      if (r.pinned_id) free_locked(ctx, r.pinned_id);
-      if (r.ring_id) free_locked(ctx, r.ring_id);
+      release_role_locked(st, r);
       if (r.out_id) free_locked(ctx, r.out_id);
-      for (auto e : r.ready) cudaEventDestroy(e);
-      for (auto e : r.freed) cudaEventDestroy(e);
     }
     for (auto id : st->x_ping) if (id) free_locked(ctx, id);
     for (auto id : st->x_pong) if (id) free_locked(ctx, id);

@@ -123,6 +123,16 @@ class LayerStack:
         ax = (C.c_uint64 * n)(*[b.id for b in aux]) if aux is not None else None
         _check(self.be.lib.tnf_stack_step(self._stack, xs, ax, os_, a_global))
 
+    def evict_all(self) -> None:
+        """Phase eviction: free every weight buffer of the stack (``evict_all_and_free`` in the reference); the
+        next ``step`` brings the weights back under what the budget then allows."""
+        _check(self.be.lib.tnf_stack_evict_all(self._stack))
+
+    def restore(self, weight_budget: int = 0) -> dict:
+        """Re-plan and re-upload now (also undoes demotions made by the reclaim chain once memory is free)."""
+        _check(self.be.lib.tnf_stack_restore(self._stack, weight_budget))
+        return self.stats()
+
     def stats(self) -> dict:
         out = (C.c_uint64 * 6)()
         _check(self.be.lib.tnf_stack_stats(self._stack, out))
