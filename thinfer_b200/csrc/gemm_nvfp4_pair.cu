@@ -237,6 +237,24 @@ __device__ __forceinline__ void epilogue_pair_dispatch(uint32_t mode, const uint
   }
 }
 
+// Work item w of the persistent loop -> row tile, first column and MMA width. Tiles [0, full_tiles) run whole
+// (256 columns, fewer on a ragged last column tile: n_eff is a multiple of 16). The tiles of the last, partly filled
+// wave are split into two 128-column halves when that lets every pair take part in it: the tail then costs half a
+// tile time instead of a whole one (4352 x 9216: 612 tiles on 74 pairs = 8 waves + 20 tiles -> 40 halves).
+__device__ __forceinline__ void decode_item(const GemmParams& p, uint32_t tiles_m2, uint32_t w, uint32_t& tm2, uint32_t& n0,
+                                            uint32_t& n_eff) {
+  uint32_t tile = w, sub = 0u, width = 256u;
+  if (w >= p.full_tiles) {
+    const uint32_t t = w - p.full_tiles;
+    tile = p.full_tiles + (t >> 1);
+    sub = t & 1u;
+    width = 128u;
+  }
+  tm2 = tile % tiles_m2;
+  n0 = (tile / tiles_m2) * 256u + sub * 128u;
+  n_eff = min(width, (p.n - n0 + 15u) & ~15u);
+}
+
 // kDense: the dense-activation arm of the same kernel. A is bf16 [m,k] (not quantised), W the exact bf16 image of
 // code x block scale [n,k] made once per weight; a stage holds 64 K elements of each (the same 128-byte swizzled
 // rows), there are no scale factors, and the MMAs are kind::f16 with K = 16. Pipeline and epilogue are shared.
@@ -280,7 +298,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
   const bool ktr = kDiag && (p.diag & 16u) && blockIdx.x == 0 && threadIdx.x == 0;
   if (ktr) p.trace[1200] = clock64();
   const uint32_t pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const uint32_t tiles_m2 = p.tiles_m, num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts 256-row pair tiles here
+  const uint32_t tiles_m2 = p.tiles_m;  // tiles_m counts 256-row pair tiles here
+  const uint32_t num_tiles = p.full_tiles + (p.tiles_m * p.tiles_n - p.full_tiles) * 2u;  // work items (see decode_item)
   const uint32_t num_k_tiles = (p.k + kStageK - 1u) / kStageK;
   const long long wait_limit = p.wait_limit > 0 ? p.wait_limit : kDefaultWaitLimitCycles;
 
@@ -322,12 +341,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
       uint32_t stage = 0, phase = 0, titer = 0;
       bool ok = true;
       for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
-        const int32_t m0 = int32_t(tm2 * 256u + rank * 128u), n0 = int32_t(tn * 256u);
-        // A ragged last column tile runs a narrower MMA (n_eff columns, a multiple of 16): the pair's two halves
-        // of the W tile are then rows [n0, n0 + n_eff/2) and [n0 + n_eff/2, n0 + n_eff), so that accumulator
-        // column j is still output column n0 + j.
-        const uint32_t n_eff = min(256u, (p.n - uint32_t(n0) + 15u) & ~15u);
+        // A narrower item (ragged last column tile, half tile of the tail) runs a narrower MMA of n_eff columns: the
+        // pair's two halves of the W tile are then rows [n0, n0 + n_eff/2) and [n0 + n_eff/2, n0 + n_eff), so that
+        // accumulator column j is still output column n0 + j.
+        uint32_t tm2, n0u, n_eff;
+        decode_item(p, tiles_m2, tile, tm2, n0u, n_eff);
+        const int32_t m0 = int32_t(tm2 * 256u + rank * 128u), n0 = int32_t(n0u);
         const int32_t sfa_row0 = int32_t((tm2 * 2u + rank) * p.k_atoms * 4u);
         const int32_t sfb_row0 = int32_t((uint32_t(n0) >> 7) * p.k_atoms * 4u);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
@@ -386,7 +405,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         }
         if (ttr) p.trace[1024 + it * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + (it & 1u) * kAccStride;
-        const uint32_t n_eff = min(256u, (p.n - (tile / tiles_m2) * 256u + 15u) & ~15u);  // as in the producer
+        uint32_t tm2_, n0_, n_eff;
+        decode_item(p, tiles_m2, tile, tm2_, n0_, n_eff);  // as in the producer
         const uint32_t idesc = kDense ? make_idesc_bf16(256, n_eff) : make_idesc_nvfp4(256, n_eff);
         for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
           if (kDiag && (p.diag & 16u) && pair_id == 0 && titer < 256u && lane == 0) p.trace[1300 + titer] = clock64();
@@ -475,9 +495,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
     // 16-byte atom rows. Scattered 16- and 4-byte multimem stores straight from the registers ran at a fifth of the link rate.
     uint8_t* stage_q = (p.q_codes_mc && !p.store_bf16) ? smem_gen + (sStaging - smem_base) : nullptr;
     for (uint32_t tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
-      const uint32_t tm2 = tile % tiles_m2, tn = tile / tiles_m2;
+      uint32_t tm2, n0, n_eff;
+      decode_item(p, tiles_m2, tile, tm2, n0, n_eff);
       const uint32_t row0 = tm2 * 256u + rank * 128u + q * 32u;
-      const uint32_t n0 = tn * 256u;
       const uint32_t b = it & 1u;
       const uint32_t first = b ? 0u : 3u;  // 64-column group that overlaps the other accumulator
       const uint32_t g0 = (2u * h + first) & 3u, g1 = (2u * h + 1u + first) & 3u;
@@ -537,7 +557,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
         }
         const uint32_t ncol0 = n0 + g * 64u;
         // warp-uniform; with a staged output a warp whose rows are all past m still stages their (zero) scale words
-        if (ncol0 >= p.n || (row0 >= p.m && !stage_q)) continue;
+        if (g * 64u >= n_eff || ncol0 >= p.n || (row0 >= p.m && !stage_q)) continue;
         if (kDiag && (p.diag & 256u)) continue;      // diagnostic: drain the accumulator only
         if (lane == 0) bulk_wait_group_read<0>();  // the previous store has finished reading the staging buffer
         __syncwarp();                              // ... and every lane its reads of the previous group's bias
@@ -593,11 +613,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::kThreads, 1)
 #pragma unroll
         for (uint32_t pass = 0; pass < 4u; ++pass) {  // 8 lanes cover a row's 128 code bytes, 32 rows per pass
           const uint32_t lr = pass * 32u + (t >> 3), c = t & 7u, grow = trow0 + lr;
-          if (grow < p.m && n0 + (c >> 1) * 64u < p.n)
+          if (grow < p.m && (c >> 1) * 64u < n_eff && n0 + (c >> 1) * 64u < p.n)
             multimem_st_v4(p.q_codes_mc + uint64_t(grow) * (p.ldo >> 1) + (qcol0 >> 1) + c * 16u,
                            *reinterpret_cast<const uint4*>(stage_q + lr * 128u + ((c ^ (lr & 7u)) << 4)));
         }
-        if (t < 128u && trow0 < p.m && n0 + (t >> 5) * 64u < p.n)  // four 512-byte scale atoms, 16 bytes per thread
+        if (t < 128u && trow0 < p.m && (t >> 5) * 64u < n_eff && n0 + (t >> 5) * 64u < p.n)  // four 512-byte scale atoms, 16 bytes per thread
           multimem_st_v4(p.q_scales_mc + sf_device_offset(trow0, (qcol0 >> 4) + (t >> 5) * 4u, p.q_k_atoms) + (t & 31u) * 16u,
                          *reinterpret_cast<const uint4*>(stage_q + 16384u + (t >> 5) * 512u + (t & 31u) * 16u));
         __syncwarp();
@@ -675,7 +695,12 @@ static cudaError_t launch_pair_kb(const CUtensorMap& map_a, const CUtensorMap& m
   p.tiles_n = (p.n + 255u) / 256u;
   const uint32_t tiles = p.tiles_m * p.tiles_n;
   if (tiles == 0) return cudaSuccess;
-  const uint32_t pairs = std::min<uint32_t>(tiles, uint32_t(max_pairs[dev] > 0 ? max_pairs[dev] : sm_count / 2));
+  const uint32_t avail = uint32_t(max_pairs[dev] > 0 ? max_pairs[dev] : sm_count / 2);
+  const uint32_t tail = tiles % avail;
+  // split the last wave's tiles into halves when every half then finds a pair of its own (and no half is empty)
+  p.full_tiles = (tiles > avail && tail > 0 && 2u * tail <= avail && p.n % 256u == 0u && !(kDiag && (diag & 2048u))) ? tiles - tail : tiles;
+  const uint32_t items = p.full_tiles + (tiles - p.full_tiles) * 2u;
+  const uint32_t pairs = std::min<uint32_t>(items, avail);
   PairOutMaps om;
   for (int i = 0; i < kMaxPeers; ++i) om.m[i] = out_maps[i];
   return launch_pdl(nvfp4_gemm_pair_kernel<KB, kDense>, dim3(pairs * 2), dim3(pair::kThreads), Cfg::kSmemBytes, s, map_a, map_w, map_sfa,

@@ -86,6 +86,7 @@ struct GemmParams {
   uint32_t ldo, n_offset;
   uint32_t act, chain;
   uint32_t tiles_m, tiles_n;
+  uint32_t full_tiles;         // pair kernel: tiles [0, full_tiles) run whole; each later one as two 128-column halves
   uint8_t* q_codes;            // optional NVFP4 copy of the output: codes [m, n/2] ...
   uint8_t* q_scales;           // ... and device-layout scales of an [m, n] operand
   float q_global, q_inv_t;     // its per-tensor scale g and 1/(6g)
