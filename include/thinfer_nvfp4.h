@@ -188,9 +188,17 @@ enum {
   /* The site keeps its activations un-quantised: out = epilogue(w_global * (A_bf16 . Wd^T)) with Wd the dense image
    * of the NVFP4 weight (w_dense). This is the reference's dense arm for sites whose A-side carries outliers
    * (DenseActSites, thinfer-models/src/common/block.rs:458-479; the "dequant once, then matmul" branch of
-   * dispatch_matmul_site_diag, :2861-2881, with PreparedWeight::F16, :217-227). a_bf16 is required, a_global and
-   * TNF_LINEAR_A_PREQUANTIZED are not used, no activation quantiser runs; bf16 x bf16 products on the tensor
-   * cores (tcgen05.mma kind::f16), f32 accumulation, the same fused epilogue. k must be a multiple of 8. */
+   * dispatch_matmul_site_diag, :2861-2881, with PreparedWeight::F16, :217-227). a_bf16 is required, a_global is
+   * not used, no activation quantiser runs; bf16 x bf16 products on the tensor cores (tcgen05.mma kind::f16),
+   * f32 accumulation, the same fused epilogue. k must be a multiple of 8.
+   * w_dense may also be a weight that was never quantised (plain bf16 [n,k], w_global = 1): the reference's
+   * refiner weights (thinfer-core/src/ops/matmul_i8_bf16.rs:15-17).
+   * Mixed arm -- low-bit activations x dense bf16 weight, the role of the reference's matmul_i8_bf16
+   * (thinfer-core/src/ops/matmul_i8_bf16.rs:1-17,113-292): with TNF_LINEAR_A_PREQUANTIZED as well (activations in
+   * the shared scratch), or through tnf_gemm_nvfp4 with this flag (activations as codes + DEVICE scales), the
+   * NVFP4 activations are first widened to bf16 in a workspace buffer (exact: a code times its block scale has
+   * at most 6 significant bits) and out = epilogue(a_global * w_global * (Aq . Wd^T)). NVFP4 has no zero point, so
+   * the reference's `za * sum_k b` correction term (bf16_block_sum.rs) has no counterpart. */
   TNF_LINEAR_DENSE_ACT = 32u,
   /* SwiGLU gating fused into the FFN-up GEMM: the weight is the ROW-INTERLEAVED pair [W1 row 0, W3 row 0,
    * W1 row 1, ...] (n = 2 x hidden rows, quantised as one tensor), and the epilogue writes
@@ -253,7 +261,8 @@ uint64_t tnf_noalloc_scratch_bytes(void);
  * tnf_linear_nvfp4(flags = TNF_LINEAR_A_PREQUANTIZED). */
 int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32_t k, float global_scale);
 
-/* Pre-quantised operands on both sides (codes + DEVICE scales): the GEMM alone. */
+/* Pre-quantised operands on both sides (codes + DEVICE scales): the GEMM alone. With TNF_LINEAR_DENSE_ACT the
+ * weight side is w_dense instead (mixed arm, see the flag). */
 int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args, tnf_buf a_codes, tnf_buf a_scales_device);
 
 /* ---- streaming residency (WeightResidency, thinfer-core/src/residency.rs) ------------ */
@@ -332,6 +341,52 @@ int32_t tnf_stack_evict_all(tnf_stack* st);
  * reserve. Also undoes demotions made by the reclaim chain once memory is free again. */
 int32_t tnf_stack_restore(tnf_stack* st, uint64_t weight_budget_bytes);
 int32_t tnf_stack_destroy(tnf_stack* st);
+
+/* ---- host IO: readers with readahead hints ---------------------------------------------- */
+
+/* A random-access reader over one file or one tensor's bytes: `trait WeightReader`
+ * (thinfer-core/src/weight.rs:57-77) as a struct of function pointers, so that the embedding program can
+ * pass its own readers. len and read_at are required; read_at lands exactly `n` bytes of [offset, offset+n)
+ * in caller memory and returns TNF_OK or an error code. will_read is the prefetch hint "the next read_at
+ * will be exactly (offset, n)" (:69-76): best effort, a wrong or ignored hint costs speed, never bytes; NULL
+ * means "no hints". close releases `user` (NULL: nothing to release). One reader is used by one thread
+ * at a time (the reference enforces that with `&mut self`). */
+typedef struct tnf_reader {
+  void* user;
+  uint64_t (*len)(void* user);
+  int32_t (*read_at)(void* user, uint64_t offset, void* dst, uint64_t n);
+  void (*will_read)(void* user, uint64_t offset, uint64_t n);
+  void (*close)(void* user);
+} tnf_reader;
+
+#define TNF_READER_DEFAULT_HINTS 0xFFFFFFFFu /* hint_chunks: the reference's READ_PREFETCH_CHUNKS (4) */
+
+/* MmapFileOpener::new + FileOpener::open (thinfer-native/src/lib.rs:15-52): maps the whole file read-only.
+ * read_at is a bounds-checked memcpy (:57-70); will_read is madvise(MADV_WILLNEED) on the range
+ * (:72-86), which starts the page-in as large batched IOs. An empty file gives an empty reader. */
+int32_t tnf_mmap_open(const char* path, tnf_reader* out);
+/* out = {read_at calls, bytes read, hints accepted, bytes hinted} of a reader made by tnf_mmap_open. */
+int32_t tnf_mmap_stats(const tnf_reader* r, uint64_t out[4]);
+/* OffsetView (thinfer-core/src/weight.rs:102-127): restricts `inner` to [base, base+len) and rebases
+ * offsets to [0, len). The view borrows `inner`, which must outlive it; closing the view leaves it open. */
+int32_t tnf_reader_view(const tnf_reader* inner, uint64_t base, uint64_t len, tnf_reader* out);
+void tnf_reader_close(tnf_reader* r);
+/* The chunk loop of stream_source_to_gpu (thinfer-core/src/residency.rs:1253-1292) without a device: reads
+ * [offset, offset+n) into `dst` in chunks of chunk_bytes (0 = 16 MiB), hinting the first hint_chunks
+ * chunks up front and, after each chunk, the chunk hint_chunks ahead of it. Host only. */
+int32_t tnf_reader_read(const tnf_reader* r, uint64_t offset, uint64_t n, void* dst, uint64_t chunk_bytes,
+                        uint32_t hint_chunks);
+/* The same loop into a pinned arena (tnf_host_register), e.g. one NVFP4 record of a container straight into
+ * the arena a tnf_stack streams from: the bytes on disk are the bytes the copy engine sends. */
+int32_t tnf_reader_read_to_arena(tnf_ctx* ctx, const tnf_reader* r, uint64_t offset, uint64_t n, uint64_t host_id,
+                                 uint64_t host_off, uint64_t chunk_bytes, uint32_t hint_chunks);
+/* stream_source_to_gpu (thinfer-core/src/residency.rs:1197-1341): streams `total` source bytes starting at
+ * src_offset into the device view `dst`; dst.len >= total, and the bytes of the view past `total` are
+ * zero-filled (the reference's padded_len). Chunks pass through two pinned staging slots kept by the
+ * context, so reading chunk i+1 overlaps the copy of chunk i on the copy stream. *event (may be NULL)
+ * identifies the completion of the last copy. */
+int32_t tnf_upload_from_reader(tnf_ctx* ctx, const tnf_reader* r, uint64_t src_offset, uint64_t total, tnf_buf dst,
+                               uint64_t chunk_bytes, uint32_t hint_chunks, uint64_t* event);
 
 /* ---- container: GGUF-v3 header parser + tensor catalog ------------------------------- */
 

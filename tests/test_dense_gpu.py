@@ -98,3 +98,69 @@ def test_site_policy_accuracy_on_device(backend):
         assert e_dense < e_fp4 < 0.16 and e_dense < 0.11, (name, e_fp4, e_dense)
         assert e_fp4 < 1.6 * e_dense
     print("site policy on device (rel. Frobenius error vs f64): " + ", ".join(f"{k} fp4 {v[0]:.4f} dense {v[1]:.4f}" for k, v in errs.items()))
+
+
+@pytest.mark.parametrize("m,n,k,act", [(200, 520, 512, 1), (2100, 2312, 320, 0)])
+def test_unquantised_bf16_weight_site(backend, m, n, k, act):
+    """A weight that is never quantised (the reference's refiner weights, thinfer-core/src/ops/matmul_i8_bf16.rs:15-17)
+    runs through the dense arm as it is: bf16 x bf16 on the tensor cores, f32 accumulation, per-tensor scale 1."""
+    import thinfer_b200 as T
+
+    a, w, b = _inputs(m, n, k, 3 * m + n)
+    wb = O.f32_to_bf16(w)
+    be = backend
+    W = T.Nvfp4Weight.from_bf16(be, wb, b)
+    abuf = be.upload(a)
+    out = be.allocate(m * n * 2)
+    be.scope().linear(abuf, m, W, 0.0, out, act=act, dense_act=True)
+    be.submit(30000)
+    got = be.read_buffer(out, np.uint16).reshape(m, n)
+    want = O.epilogue(O.gemm_f32(O.bf16_to_f32(a), O.bf16_to_f32(wb)), 1.0, bias=b, act=act)
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
+    assert (got == want).mean() > (0.9 if act else 0.98)
+    with pytest.raises(T.InvalidArgument, match="dense_act"):
+        be.scope().linear(abuf, m, W, 1.0, out)  # no NVFP4 form: the FP4 arm must refuse, not read null codes
+    be.free(abuf)
+    be.free(out)
+    W.free(be)
+
+
+@pytest.mark.parametrize("m,n,k,act,shared", [(200, 520, 512, 1, False), (2304, 2304, 256, 0, True), (37, 264, 96, 0, True)])
+def test_mixed_arm_nvfp4_activations_times_bf16_weight(backend, m, n, k, act, shared):
+    """Low-bit activations x dense bf16 weight (the role of the reference's matmul_i8_bf16,
+    thinfer-core/src/ops/matmul_i8_bf16.rs:1-17): the NVFP4 activations are widened to bf16 exactly, so the result
+    is the oracle's product of the dequantised activations with the bf16 weight, scaled by a_global * w_global in
+    the epilogue. Both entries: the pre-quantised GEMM call and the shared-scratch linear."""
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+
+    a, w, b = _inputs(m, n, k, 5 * m + n)
+    wb = O.f32_to_bf16(w)
+    ga = O.global_scale(O.amax_bf16(a))
+    ac, as_ = O.quantize_act(a, ga)
+    want = O.epilogue(O.gemm_f32(O.dequant(ac, as_, 1.0), O.bf16_to_f32(wb)), ga * 1.0, bias=b, act=act)
+    be = backend
+    W = T.Nvfp4Weight.from_bf16(be, wb, b)
+    abuf = be.upload(a)
+    out = be.allocate(m * n * 2)
+    sc = be.scope()
+    if shared:
+        sc.act_quant_shared(abuf, m, k, ga)
+        sc.linear(None, m, W, ga, out, act=act, dense_act=True, flags=L.LINEAR_A_PREQUANTIZED)
+    else:
+        qc, qs, _ = sc.act_quant(abuf, m, k, ga, device_layout=True)
+        sc.matmul(qc, qs, m, W, ga, out, act=act, dense_act=True)
+    be.submit(30000)
+    got = be.read_buffer(out, np.uint16).reshape(m, n)
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
+    assert (got == want).mean() > (0.9 if act else 0.98)
+    if shared:  # the scratch is tagged with its shape: another shape is refused
+        with pytest.raises(T.InvalidArgument, match="shared scratch"):
+            W2 = T.Nvfp4Weight(n, k + 32, None, None, 1.0, None, None, W.dense)
+            sc.linear(None, m, W2, ga, out, dense_act=True, flags=L.LINEAR_A_PREQUANTIZED)
+    else:
+        be.free(qc)
+        be.free(qs)
+    be.free(abuf)
+    be.free(out)
+    W.free(be)

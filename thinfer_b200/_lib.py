@@ -66,6 +66,19 @@ class StackLinear(C.Structure):
                 ("input", C.c_uint32), ("stream_id", C.c_uint32)]
 
 
+READER_DEFAULT_HINTS = 0xFFFFFFFF
+READER_LEN = C.CFUNCTYPE(C.c_uint64, C.c_void_p)
+READER_READ_AT = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64)
+READER_WILL_READ = C.CFUNCTYPE(None, C.c_void_p, C.c_uint64, C.c_uint64)
+READER_CLOSE = C.CFUNCTYPE(None, C.c_void_p)
+
+
+class Reader(C.Structure):
+    """tnf_reader: len / read_at / will_read / close over an opaque `user` (WeightReader in the reference)."""
+    _fields_ = [("user", C.c_void_p), ("len", READER_LEN), ("read_at", READER_READ_AT), ("will_read", READER_WILL_READ),
+                ("close", READER_CLOSE)]
+
+
 _u64p, _u32p, _vpp = C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.POINTER(C.c_void_p)
 _ctx = C.c_void_p
 
@@ -117,6 +130,14 @@ SIGNATURES = {
     "tnf_stack_restore": (C.c_int32, [C.c_void_p, C.c_uint64]),
     "tnf_reclaimed_bytes": (C.c_int32, [_ctx, _u64p]),
     "tnf_set_transient_reserve": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_mmap_open": (C.c_int32, [C.c_char_p, C.POINTER(Reader)]),
+    "tnf_mmap_stats": (C.c_int32, [C.POINTER(Reader), _u64p]),
+    "tnf_reader_view": (C.c_int32, [C.POINTER(Reader), C.c_uint64, C.c_uint64, C.POINTER(Reader)]),
+    "tnf_reader_close": (None, [C.POINTER(Reader)]),
+    "tnf_reader_read": (C.c_int32, [C.POINTER(Reader), C.c_uint64, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint32]),
+    "tnf_reader_read_to_arena": (C.c_int32, [_ctx, C.POINTER(Reader), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                             C.c_uint64, C.c_uint32]),
+    "tnf_upload_from_reader": (C.c_int32, [_ctx, C.POINTER(Reader), C.c_uint64, C.c_uint64, Buf, C.c_uint64, C.c_uint32, _u64p]),
     "tnf_gguf_parse": (C.c_int32, [C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p), _u64p]),
     "tnf_gguf_free": (C.c_int32, [C.c_void_p]),
     "tnf_gguf_info": (C.c_int32, [C.c_void_p, _u64p]),

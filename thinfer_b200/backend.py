@@ -182,8 +182,8 @@ class Nvfp4Weight:
     """A linear's resident weight: E2M1 codes [n,k/2], device-layout E4M3 scales, f32 scale, bias."""
     n: int
     k: int
-    codes: Buf
-    scales_device: Buf
+    codes: Optional[Buf]          # None: a weight kept in bf16 only (from_bf16)
+    scales_device: Optional[Buf]
     global_scale: float
     bias: Optional[Buf] = None
     scales_canonical: Optional[Buf] = None
@@ -225,6 +225,18 @@ class Nvfp4Weight:
         be.free(canon)
         bias = be.upload(bias_bf16.astype(np.uint16, copy=False), L.CAT_WEIGHTS) if bias_bf16 is not None else None
         return Nvfp4Weight(n, k, cb, dev, float(global_scale), bias, None)
+
+    @staticmethod
+    def from_bf16(be: Backend, w_bf16: np.ndarray, bias_bf16: Optional[np.ndarray] = None) -> "Nvfp4Weight":
+        """A weight that is never quantised (bf16 bits as uint16, [n,k]): only the dense arm (``dense_act=True``) and the
+        mixed arm (NVFP4 activations x this weight) can use it. The reference keeps its refiner weights this way
+        (thinfer-core/src/ops/matmul_i8_bf16.rs:15-17)."""
+        if w_bf16.dtype != np.uint16 or w_bf16.ndim != 2:
+            raise InvalidArgument(L.ERR_INVALID_ARGUMENT, "from_bf16 takes bf16 bits as a uint16 [n,k] array")
+        n, k = w_bf16.shape
+        dense = be.upload(w_bf16, L.CAT_WEIGHTS)
+        bias = be.upload(bias_bf16.astype(np.uint16, copy=False), L.CAT_WEIGHTS) if bias_bf16 is not None else None
+        return Nvfp4Weight(n, k, None, None, 1.0, bias, None, dense)
 
     def prepare_dense(self, be: Backend) -> Buf:
         """Make (once) and keep the dense bf16 image a ``dense_act`` site multiplies with: code x block scale, exact."""
@@ -289,7 +301,9 @@ class BatchScope:
         args.m, args.n, args.k = m, w.n, w.k
         args.a_global, args.w_global = a_global, w.global_scale
         args.a_bf16 = a if a is not None else _NONE
-        args.w_codes, args.w_scales = w.codes, w.scales_device
+        if w.codes is None and not flags & L.LINEAR_DENSE_ACT:
+            raise InvalidArgument(L.ERR_INVALID_ARGUMENT, "a bf16-only weight needs dense_act=True")
+        args.w_codes, args.w_scales = w.codes or _NONE, w.scales_device or _NONE
         use_bias = w.bias if bias is None else (None if bias is False else bias)
         args.bias_bf16 = use_bias if use_bias is not None else _NONE
         args.gate_bf16 = gate if gate is not None else _NONE
@@ -342,8 +356,12 @@ class BatchScope:
 
     def matmul(self, a_codes: Buf, a_scales_device: Buf, m: int, w: Nvfp4Weight, a_global: float, out: Optional[Buf],
                act: int = L.ACT_NONE, gate=None, residual=None, chain: bool = False, n_offset: int = 0, ldo: int = 0,
-               flags: int = 0, bias=None, out_nvfp4=None) -> None:
-        """The GEMM alone on pre-quantised operands."""
+               flags: int = 0, bias=None, out_nvfp4=None, dense_act: bool = False) -> None:
+        """The GEMM alone on pre-quantised operands. ``dense_act=True`` is the mixed arm: the NVFP4 activations are
+        widened to bf16 (exact) and multiply the weight's dense image, or a weight that was never quantised
+        (``Nvfp4Weight.from_bf16``) -- the role of the reference's matmul_i8_bf16."""
+        if dense_act:
+            flags |= L.LINEAR_DENSE_ACT
         args = self._args(m, w, None, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias, out_nvfp4)
         _check(self.be.lib.tnf_gemm_nvfp4(self.be._ctx, C.byref(args), a_codes, a_scales_device))
 

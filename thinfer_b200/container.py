@@ -12,7 +12,6 @@ arena and streamed unchanged.
 from __future__ import annotations
 
 import ctypes as C
-import os
 import struct
 from dataclasses import dataclass
 from typing import Dict, Iterable, Optional, Sequence, Tuple, Union
@@ -91,25 +90,28 @@ class TensorEntry:
 class Container:
     """An opened container: catalog by name + reads into caller memory."""
 
-    def __init__(self, path: str, first_read: int = 4096):
-        self.path = path
-        self.file_size = os.path.getsize(path)
+    def __init__(self, source: Union[str, "Reader"], first_read: int = 4096):
+        """``source``: a file path (opened with the library's mmap reader) or any ``reader.Reader``."""
+        from .reader import MmapReader, Reader
+
+        self.path = source if isinstance(source, str) else None
+        self.reader: Reader = MmapReader(source) if isinstance(source, str) else source
+        self.file_size = len(self.reader)
         lib = L.load()
         handle, need = C.c_void_p(), C.c_uint64()
         want = min(first_read, self.file_size)
-        with open(path, "rb") as f:
-            while True:  # the reference's streaming pattern: read up to the offset the parser asked for, retry
-                f.seek(0)
-                buf = f.read(want)
-                rc = lib.tnf_gguf_parse(buf, len(buf), C.byref(handle), C.byref(need))
-                if rc == 0:
-                    break
-                if rc == L.GGUF_NEED_MORE:
-                    if need.value > self.file_size:
-                        raise ContainerError(f"{path}: header runs past the end of the file (needs byte {need.value})")
-                    want = min(max(int(need.value), 2 * want), self.file_size)
-                    continue
-                raise ContainerError(f"{path}: {lib.tnf_last_error().decode()}")
+        name = self.path or "<reader>"
+        while True:  # the reference's streaming pattern: read up to the offset the parser asked for, retry
+            buf = self.reader.read(0, want).tobytes()
+            rc = lib.tnf_gguf_parse(buf, len(buf), C.byref(handle), C.byref(need))
+            if rc == 0:
+                break
+            if rc == L.GGUF_NEED_MORE:
+                if need.value > self.file_size:
+                    raise ContainerError(f"{name}: header runs past the end of the file (needs byte {need.value})")
+                want = min(max(int(need.value), 2 * want), self.file_size)
+                continue
+            raise ContainerError(f"{name}: {lib.tnf_last_error().decode()}")
         self.header_reads_to = want
         info = (C.c_uint64 * 4)()
         lib.tnf_gguf_info(handle, info)
@@ -134,12 +136,18 @@ class Container:
             raise ContainerError(f"{name}: {n} bytes do not fit its slot of {e.size} bytes")
         if dst.dtype != np.uint8 or dst.size < n:
             raise ValueError(f"{name}: destination holds {dst.size} bytes, tensor has {n}")
-        with open(self.path, "rb", buffering=0) as f:
-            f.seek(e.offset)
-            got = f.readinto(memoryview(dst)[:n])
-        if got != n:
-            raise ContainerError(f"{name}: short read ({got} of {n} bytes)")
+        self.reader.read(e.offset, n, out=dst)
         return n
+
+    def hint(self, name: str) -> None:
+        """Readahead hint for a tensor about to be read (``WeightReader::will_read``)."""
+        e = self.tensors.get(name)
+        if e is not None:
+            self.reader.will_read(e.offset, e.on_disk_bytes or e.size)
+
+    def close(self) -> None:
+        if self.path is not None:  # a reader passed in belongs to the caller
+            self.reader.close()
 
     def read(self, name: str) -> np.ndarray:
         e = self.tensors[name] if name in self.tensors else None
@@ -158,9 +166,15 @@ def load_stack(container: Container, stack) -> int:
     """Fill a LayerStack's pinned arena from the container's NVFP4 records (no transcoding: the bytes
     on disk are the bytes the copy engine streams). Returns the bytes read."""
     total = 0
+    names = [record_name(layer, j) for layer in range(stack.layers) for j in range(len(stack.linears))]
+    for name in names[:2]:
+        container.hint(name)
     for layer in range(stack.layers):
         for j, spec in enumerate(stack.linears):
             name = record_name(layer, j)
+            ahead = layer * len(stack.linears) + j + 2
+            if ahead < len(names):
+                container.hint(names[ahead])  # the page-in of record i+2 runs under the copy of record i
             e = container.tensors.get(name)
             if e is None:
                 raise ContainerError(f"unknown tensor {name!r}")

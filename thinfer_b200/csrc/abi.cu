@@ -230,6 +230,33 @@ static int32_t ensure_scratch(tnf_ctx* ctx, uint32_t m, uint32_t k) {
   return TNF_OK;
 }
 
+// Workspace for the bf16 image of NVFP4 activations (the mixed arm: low-bit activations x a dense bf16 weight).
+static int32_t ensure_wide(tnf_ctx* ctx, uint64_t bytes) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  if (bytes <= ctx->wide_bytes) return TNF_OK;
+  if (ctx->wide_id) free_locked(ctx, ctx->wide_id);
+  ctx->wide_id = 0;
+  ctx->wide_bytes = 0;
+  int32_t st = alloc_locked(ctx, bytes, TNF_CAT_WORKSPACE, &ctx->wide_id);
+  if (st != TNF_OK) return st;
+  ctx->wide_bytes = bytes;
+  return TNF_OK;
+}
+
+// Mixed arm: NVFP4 activations (codes + device scales) against a dense bf16 weight. The tensor cores have no
+// FP4 x bf16 form, so the activations are widened to bf16 first -- exact: a code times its block scale has at
+// most 6 significant bits -- and the bf16 GEMM applies a_global * w_global in its epilogue.
+static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales,
+                        const uint8_t* a_raw, bool widened);
+static int32_t run_mixed(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales) {
+  int32_t st = ensure_wide(ctx, uint64_t(a->m) * a->k * 2);
+  if (st != TNF_OK) return st;
+  uint8_t* wide = static_cast<uint8_t*>(ctx->bufs[ctx->wide_id].ptr);
+  TNF_CUDA(launch_dequant_dense(a_codes, a_scales, a->m, a->k, reinterpret_cast<uint16_t*>(wide), ctx->compute),
+           "activation widening launch");
+  return run_gemm(ctx, a, wide, nullptr, nullptr, true);
+}
+
 static int32_t check_dims(uint32_t m, uint32_t n, uint32_t k) {
   if (m == 0 || n == 0 || k == 0) {
     set_error("empty problem m=%u n=%u k=%u", m, n, k);
@@ -248,8 +275,10 @@ static int32_t check_dims(uint32_t m, uint32_t n, uint32_t k) {
 
 // shared tail of tnf_linear_nvfp4 / tnf_gemm_nvfp4
 // `a_raw` non-null: the skinny-M kernel takes the bf16 activations themselves (its prologue is the quantiser).
+// `widened`: the dense arm's bf16 activations are the exact image (code x block scale) of NVFP4 activations, so
+// the per-tensor activation scale still has to be applied.
 static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a_codes, const uint8_t* a_scales,
-                        const uint8_t* a_raw = nullptr) {
+                        const uint8_t* a_raw, bool widened) {
   int32_t st = TNF_OK;
   const bool swiglu = (a->flags & TNF_LINEAR_SWIGLU) != 0;
   const uint32_t n_out_cols = swiglu ? a->n / 2 : a->n;  // columns this call writes
@@ -325,7 +354,7 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   }
   p.m = a->m; p.n = a->n; p.k = a->k;
   p.k_atoms = sf_k_atoms(a->k);
-  p.alpha = dense ? a->w_global : a->a_global * a->w_global;
+  p.alpha = (dense && !widened) ? a->w_global : a->a_global * a->w_global;
   p.dense = dense ? 1u : 0u;
   p.swiglu = swiglu ? 1u : 0u;
   p.sfa = a_scales;
@@ -450,6 +479,10 @@ int32_t tnf_destroy(tnf_ctx* ctx) {
   }
   for (auto& kv : ctx->events) cudaEventDestroy(kv.second);
   for (auto ev : ctx->event_pool) cudaEventDestroy(ev);
+  for (int i = 0; i < 2; ++i) {
+    if (ctx->stage_host[i]) cudaFreeHost(ctx->stage_host[i]);
+    if (ctx->stage_done[i]) cudaEventDestroy(ctx->stage_done[i]);
+  }
   cudaFree(ctx->dwords);
   cudaStreamDestroy(ctx->compute);
   cudaStreamDestroy(ctx->copy);
@@ -837,20 +870,31 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
               a->act, a->parity_mode);
     return TNF_ERR_INVALID_ARGUMENT;
   }
-  if (dense) {  // un-quantised activations: no quantiser launch, the GEMM reads a_bf16 itself
-    if ((a->flags & TNF_LINEAR_A_PREQUANTIZED) || a->k % 8 != 0) {
-      set_error("TNF_LINEAR_DENSE_ACT: not combinable with TNF_LINEAR_A_PREQUANTIZED; k=%u must be a multiple of 8", a->k);
+  if (dense) {
+    if (a->k % 8 != 0) {
+      set_error("TNF_LINEAR_DENSE_ACT: k=%u must be a multiple of 8", a->k);
       return TNF_ERR_INVALID_ARGUMENT;
     }
+    if (a->flags & TNF_LINEAR_A_PREQUANTIZED) {
+      // mixed arm: the NVFP4 activations in the shared scratch (tnf_quantize_act_shared) against the dense weight
+      if (!(a->a_global > 0.0f) || ctx->scratch_m != a->m || ctx->scratch_k != a->k) {
+        set_error("TNF_LINEAR_DENSE_ACT | TNF_LINEAR_A_PREQUANTIZED: a_global %g must be > 0 and the shared scratch must hold "
+                  "m=%u k=%u (it holds m=%u k=%u)", a->a_global, a->m, a->k, ctx->scratch_m, ctx->scratch_k);
+        return TNF_ERR_INVALID_ARGUMENT;
+      }
+      return run_mixed(ctx, a, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
+                       static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr));
+    }
+    // un-quantised activations: no quantiser launch, the GEMM reads a_bf16 itself
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
     if (!src) return st;
-    return run_gemm(ctx, a, src, nullptr);
+    return run_gemm(ctx, a, src, nullptr, nullptr, false);
   }
   if (a->flags == 0 && gemv_applies(a->m, a->n, a->k)) {
     // a handful of rows: one launch that quantises A in its prologue and streams W (no scratch, no quantiser launch)
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
     if (!src) return st;
-    return run_gemm(ctx, a, nullptr, nullptr, src);
+    return run_gemm(ctx, a, nullptr, nullptr, src, false);
   }
   if (!(a->flags & TNF_LINEAR_A_PREQUANTIZED)) {
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
@@ -871,7 +915,7 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
     return TNF_ERR_INVALID_ARGUMENT;
   }
   return run_gemm(ctx, a, static_cast<uint8_t*>(ctx->bufs[ctx->scratch_codes_id].ptr),
-                  static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr));
+                  static_cast<uint8_t*>(ctx->bufs[ctx->scratch_scales_id].ptr), nullptr, false);
 }
 
 int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a, tnf_buf a_codes, tnf_buf a_scales_device) {
@@ -890,7 +934,8 @@ int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a, tnf_buf a_codes, 
   if (!c) return st;
   uint8_t* s = resolve(ctx, a_scales_device, sf_device_bytes(a->m, a->k), "a_scales_device", &st);
   if (!s) return st;
-  return run_gemm(ctx, a, c, s);
+  if (a->flags & TNF_LINEAR_DENSE_ACT) return run_mixed(ctx, a, c, s);
+  return run_gemm(ctx, a, c, s, nullptr, false);
 }
 
 // ---- pinned host arenas and uploads -------------------------------------------------------------------

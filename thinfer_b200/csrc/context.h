@@ -61,6 +61,7 @@ struct tnf_ctx {
   uint64_t scratch_codes_id = 0, scratch_scales_id = 0;
   uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;
   uint32_t scratch_m = 0, scratch_k = 0;  // shape the scratch was last filled for (0 = never)
+  uint64_t wide_id = 0, wide_bytes = 0;   // bf16 image of NVFP4 activations for the mixed arm (workspace category)
   long long wait_limit_cycles = tnf::kDefaultWaitLimitCycles;  // bound of every device-side mbarrier wait
   // small device words: [0] kernel status, [1] amax bits, [2] global scale (f32)
   uint32_t* dwords = nullptr;
@@ -74,6 +75,11 @@ struct tnf_ctx {
   int world = 1, rank = 0;
   void* gather_tmp = nullptr;   // staging of the NCCL gathers: a workspace buffer of the table (gather_tmp_id)
   uint64_t gather_tmp_id = 0, gather_tmp_bytes = 0;
+  // tnf_upload_from_reader: two pinned staging slots (reader -> slot -> device), each guarded by the event of the
+  // copy that last read it
+  void* stage_host[2] = {nullptr, nullptr};
+  cudaEvent_t stage_done[2] = {nullptr, nullptr};
+  uint64_t stage_bytes = 0;
 };
 
 void tnf_comm_teardown(tnf_ctx* ctx);  // comm.cu
