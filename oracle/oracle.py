@@ -64,6 +64,7 @@ def _load():
         "ref_matmul_i8": (None, [vp, vp, vp, vp, vp, i64, i64, i64, vp]),
         "ref_layernorm": (None, [vp, C.c_int, i64, i64, f32, vp]),
         "ref_bcast_modulate": (None, [vp, vp, vp, C.c_int, i64, i64, f32, vp]),
+        "ref_sdpa": (None, [vp, vp, vp, vp, C.c_int, i64, i64, i64, i64, i64, i64, f32, C.c_int, vp]),
         "ref_norm_modulate_bf16": (None, [vp, vp, vp, i64, i64, f32, f32, C.c_int, vp]),
     }
     for name, (res, args) in sig.items():
@@ -336,6 +337,22 @@ def ref_bcast_modulate(x, s, t, bias: float = 1.0):
     x, s, t = _c(x, dt), _c(s, dt), _c(t, dt)
     out = np.empty_like(x)
     _lib.ref_bcast_modulate(_p(x), _p(s), _p(t), int(bf16), x.size, s.size, bias, _p(out))
+    return out
+
+
+def ref_sdpa(q, k, v, scale: float, mask=None, mask_mode: int = 0):
+    """Scaled-dot-product attention as the reference computes it (thinfer-core/src/ops/sdpa.rs: online softmax, keys in
+    order, f32). q [B, Sq, Hq, D], k / v [B, Sk, Hkv, D]; float32 arrays, or uint16 bf16 bit patterns (output then bf16)."""
+    bf16 = q.dtype == np.uint16
+    dt = np.uint16 if bf16 else np.float32
+    q, k, v = _c(q, dt), _c(k, dt), _c(v, dt)
+    b, s_q, h_q, d = q.shape
+    _, s_k, h_kv, _ = k.shape
+    if mask is not None and mask_mode == 0:
+        mask_mode = 2 if mask.ndim == 4 else 1
+    mask = None if mask is None else _c(mask, dt)
+    out = np.empty_like(q)
+    _lib.ref_sdpa(_p(q), _p(k), _p(v), _p(mask), int(bf16), b, s_q, s_k, h_q, h_kv, d, scale, mask_mode if mask is not None else 0, _p(out))
     return out
 
 

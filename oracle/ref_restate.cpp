@@ -264,4 +264,57 @@ void ref_norm_modulate_bf16(const uint16_t* x, const uint16_t* s, const uint16_t
     }
 }
 
+// thinfer-core/src/ops/sdpa.rs:10-47 (shapes, GQA head map, mask modes) and :131-224 (SdpaF32): scaled-dot-product
+// attention with online softmax, one query row at a time, keys in ascending order:
+//   s_j = dot(q, k_j) * scale + bias_j ; m' = max(m, s_j) ; alpha = exp(m - m') ; p = exp(s_j - m')
+//   o = o * alpha + p * v_j ; l = l * alpha + p ; out = o / l
+// with the running maximum started at -3.4e38 (finite, as the reference does for WGSL). Q [B, Sq, Hq, D],
+// K / V [B, Sk, Hkv, D] (head hq reads kv head hq * Hkv / Hq), Out [B, Sq, Hq, D]; f32 arithmetic. mask_mode 0: no
+// bias (mask may be null); 1: mask [B, Sq, Sk]; 2: mask [B, Hq, Sq, Sk]. bf16 != 0: tensors are bf16 bit patterns
+// and the output is rounded to bf16 (the reference's act_store). Rows are independent: OpenMP over them.
+void ref_sdpa(const void* q, const void* k, const void* v, const void* mask, int bf16, int64_t b, int64_t s_q, int64_t s_k,
+              int64_t h_q, int64_t h_kv, int64_t d, float scale, int mask_mode, void* out) {
+    auto ld = [bf16](const void* p, int64_t i) {
+        return bf16 ? rs_bf16_f32(static_cast<const uint16_t*>(p)[i]) : static_cast<const float*>(p)[i];
+    };
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t bb = 0; bb < b; ++bb) {
+        for (int64_t sq = 0; sq < s_q; ++sq) {
+            float* ql = new float[d];
+            float* ol = new float[d];
+            for (int64_t hq = 0; hq < h_q; ++hq) {
+                const int64_t hkv = (hq * h_kv) / h_q;
+                const int64_t q_off = ((bb * s_q + sq) * h_q + hq) * d;
+                const int64_t kv_b0 = (bb * s_k * h_kv + hkv) * d, kv_step = h_kv * d;
+                const int64_t mask_base = (mask_mode == 2 ? (bb * h_q + hq) * s_q + sq : bb * s_q + sq) * s_k;
+                for (int64_t i = 0; i < d; ++i) {
+                    ql[i] = ld(q, q_off + i);
+                    ol[i] = 0.0f;
+                }
+                float m = -3.4e38f, l = 0.0f;
+                for (int64_t j = 0; j < s_k; ++j) {
+                    const int64_t base = kv_b0 + j * kv_step;
+                    float dot = 0.0f;
+                    for (int64_t i = 0; i < d; ++i) dot = dot + ql[i] * ld(k, base + i);
+                    const float bias = mask_mode != 0 ? ld(mask, mask_base + j) : 0.0f;
+                    const float s_j = dot * scale + bias;
+                    const float m_new = std::fmax(m, s_j);
+                    const float alpha = std::exp(m - m_new), p_j = std::exp(s_j - m_new);
+                    for (int64_t i = 0; i < d; ++i) ol[i] = ol[i] * alpha + p_j * ld(v, base + i);
+                    l = l * alpha + p_j;
+                    m = m_new;
+                }
+                const float inv_l = 1.0f / l;
+                for (int64_t i = 0; i < d; ++i) {
+                    const float o = ol[i] * inv_l;
+                    if (bf16) static_cast<uint16_t*>(out)[q_off + i] = rs_bf16_rne(o);
+                    else static_cast<float*>(out)[q_off + i] = o;
+                }
+            }
+            delete[] ql;
+            delete[] ol;
+        }
+    }
+}
+
 }  // extern "C"

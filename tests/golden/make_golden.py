@@ -7,7 +7,8 @@ Part 1 — reference_fixtures.npz: the cases of the reference's committed confor
 fixtures (thinfer-conformance/fixtures/{fp32,bf16w,bf16p}.safetensors, spec in
 fixtures/spec.json) that touch the linear path: matmul_basic, bcast_add (bias),
 bcast_fma (gated residual), gelu_mul_basic (tanh-GELU gate), layernorm_basic and bcast_modulate
-(the two steps in front of every block linear). Copied as data, bit for bit;
+(the two steps in front of every block linear), and the sdpa cases (the attention between the
+linears; the per-case scale is in fixtures/spec.json and repeated in the test). Copied as data, bit for bit;
 bf16 tensors are stored as uint16 bit patterns.
 
 Part 2 — nvfp4_golden.npz: small seeded NVFP4 cases produced by this repo's CPU oracle
@@ -21,7 +22,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 
-CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic", "layernorm_basic", "bcast_modulate"]
+CASES = ["matmul_basic", "bcast_add", "bcast_fma", "gelu_mul_basic", "layernorm_basic", "bcast_modulate",
+         "sdpa_basic", "sdpa_large_d_d128", "sdpa_decode_sq1", "sdpa_decode_multirow"]
 
 
 def part1(reference_root):

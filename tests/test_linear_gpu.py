@@ -85,11 +85,14 @@ def test_epilogue_modes(backend, mode):
         backend.free(rb)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (3, 520, 1056), (8, 264, 4128), (4, 136, 64)])
+@pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (3, 520, 1056), (8, 264, 4128), (4, 136, 64), (16, 1032, 3072), (13, 136, 352),
+                                   (1, 264, 12288), (5, 136, 16384)])
 @pytest.mark.parametrize("mode", ["gelu", "gelu_chain", "gate"])
 def test_skinny_kernel_epilogue_modes(backend, m, n, k, mode):
-    """M <= 8 runs the one-launch skinny kernel (activation quantiser in the prologue, weights streamed on the CUDA
-    cores): same contract, same epilogue variants, K not a multiple of its 1024-element warp step."""
+    """A handful of rows runs a one-launch skinny kernel with the activation quantiser in its prologue: M <= 16 on the
+    tensor cores with the operands swapped (the weight is the 128-row side), and for K too long for that kernel's
+    shared memory (the last two shapes) M <= 8 with the weights streamed on the CUDA cores. Same contract, same
+    epilogue variants; ragged N, K not a multiple of the 256-element tile, more K tiles than ring stages."""
     a, w, b = _inputs(m, n, k, 300 + m)
     wc, ws, gw = O.quantize_weight(w)
     ga = O.global_scale(O.amax_bf16(a))

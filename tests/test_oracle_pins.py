@@ -68,6 +68,31 @@ def test_layernorm_fixture(golden_ref, variant):
         assert np.abs(got - out).max() <= TOL
 
 
+SDPA_SCALES = {"sdpa_basic": 0.35355338, "sdpa_large_d_d128": 0.088388346, "sdpa_decode_sq1": 0.35355338,
+               "sdpa_decode_multirow": 0.35355338}  # thinfer-conformance/fixtures/spec.json
+
+
+@pytest.mark.parametrize("case", sorted(SDPA_SCALES))
+@pytest.mark.parametrize("variant", ["fp32", "bf16w", "bf16p"])
+def test_sdpa_fixture(golden_ref, variant, case):
+    """The reference's attention cases (thinfer-core/src/ops/sdpa.rs test_cases, zero masks, GQA-free): the restated
+    online-softmax SDPA against the committed outputs. sdpa_large_d_d128 has no packed-bf16 variant."""
+    key = f"{variant}/{case}/q"
+    if key not in golden_ref.files:
+        pytest.skip("the reference's fixtures hold no such variant")
+    q, k, v, mask, out = (golden_ref[f"{variant}/{case}/{t}"] for t in "q k v mask out".split())
+    got = O.ref_sdpa(q, k, v, SDPA_SCALES[case], mask=mask)
+    no_mask = O.ref_sdpa(q, k, v, SDPA_SCALES[case])
+    assert np.array_equal(got, no_mask)  # the fixtures' masks are zero: mode 0 and mode 1 agree bit for bit
+    if variant == "bf16p":
+        g, e = O.bf16_to_f32(got), O.bf16_to_f32(out)
+        assert (np.abs(g - e) <= 2.0 ** -7 * np.abs(e) + TOL).all() and (got == out).mean() >= 0.9
+    elif variant == "bf16w":
+        assert (np.abs(got - out) <= 2.0 ** -7 * np.abs(out) + TOL).all()
+    else:
+        assert np.abs(got - out).max() <= 1e-5
+
+
 @pytest.mark.parametrize("variant", ["fp32", "bf16w", "bf16p"])
 def test_bcast_modulate_fixture(golden_ref, variant):
     """bcast_modulate (bias 1.0): out = x * (s + 1) + t."""

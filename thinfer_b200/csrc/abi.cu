@@ -388,6 +388,12 @@ static int32_t run_gemm(tnf_ctx* ctx, const tnf_linear_args* a, const uint8_t* a
   p.wait_limit = ctx->wait_limit_cycles;
   p.trace = reinterpret_cast<unsigned long long*>(ctx->dwords + 64);
   if (a_raw) {
+    if (skinny_tc_applies(a->m, a->n, a->k)) {
+      CUtensorMap mw;
+      if (!get_map(ctx, codes_spec(w_codes, a->n, a->k, 128), &mw)) return TNF_ERR_INVALID_ARGUMENT;
+      TNF_CUDA(launch_skinny_tc(mw, a_raw, a->a_global, p, ctx->compute), "nvfp4 skinny-M tensor-core launch");
+      return TNF_OK;
+    }
     TNF_CUDA(launch_gemv_nvfp4(a_raw, a->a_global, w_codes, p, ctx->compute), "nvfp4 skinny-M launch");
     return TNF_OK;
   }
@@ -890,7 +896,7 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
     if (!src) return st;
     return run_gemm(ctx, a, src, nullptr, nullptr, false);
   }
-  if (a->flags == 0 && gemv_applies(a->m, a->n, a->k)) {
+  if (a->flags == 0 && (skinny_tc_applies(a->m, a->n, a->k) || gemv_applies(a->m, a->n, a->k))) {
     // a handful of rows: one launch that quantises A in its prologue and streams W (no scratch, no quantiser launch)
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
     if (!src) return st;

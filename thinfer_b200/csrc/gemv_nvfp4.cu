@@ -9,18 +9,16 @@
 //     that half's scale bytes in shared memory, row-major; a warp has four rows, two of them in flight at any time
 //     (128 rows per CTA, eight per warp one after the other, was latency-bound: 14 us for a 5 MB weight);
 //   * every thread quantises some 16-element blocks of A exactly as the stand-alone quantiser does (same
-//     operations, same table), and leaves TWICE the E2M1 values in shared memory as int8 (0, +-1, 2, 3, 4, 6, 8,
-//     12: exact) with the decoded block scales beside them;
+//     operations, same table), and leaves the E2M1 values in shared memory as f16 pairs (exact) with the decoded
+//     block scales beside them;
 //   * a warp takes one W row at a time, its lanes covering 512 contiguous bytes of codes per step (32 elements
-//     = two 16-blocks per lane); four codes at a time are widened to int8 by byte permutes -- the eight
-//     magnitudes are one 8-byte table, which is exactly what prmt indexes with a nibble, a second table holds the
-//     negated values, and a permute in sign-replicating mode builds the byte mask that picks between them -- and
-//     multiplied by dp4a; a block's integer sum (at most 16 x 144) is exact, is scaled by a_scale * w_scale / 4 and
-//     accumulated in f32: the block-scaled dot product the tensor-core path computes. (Widening with
-//     cvt.rn.f16x2.e2m1x2 and summing in packed f16 issued 2.2x the instructions and was bound by them.)
+//     = two 16-blocks per lane); the codes are widened by the hardware (cvt.rn.f16x2.e2m1x2), the products of a
+//     half block are summed in packed f16 (at most 8 x 36 in steps of 1/4: exact), the block sum is scaled by
+//     a_scale * w_scale and accumulated in f32: the block-scaled dot product the tensor-core path computes;
 //   * a shuffle reduction per row, then the usual epilogue (alpha, bias, tanh-GELU, gated residual, bf16 RNE).
 // Operands are the buffers the tensor-core kernels read (codes row-major, device-layout scales).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cstdint>
 
 #include "epilogue.cuh"
@@ -37,23 +35,16 @@ constexpr int kThreads = 512;  // 16 warps, 4 W rows each, two of them in flight
                                // of an 18432-column weight are one wave on 148 SMs
 }  // namespace gemv
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-  return d;
-}
-
-// Eight E2M1 codes (nibble i = element i) -> twice their values as int8, elements 0-3 in lo and 4-7 in hi.
-// prmt picks byte (selector nibble & 7) of an 8-byte table, so a code's three magnitude bits index the table
-// directly; with bit 3 of a selector nibble set it replicates the top bit of the picked byte instead, which
-// turns the sign bits (moved to the top of a byte) into 0x00 / 0xFF masks.
-__device__ __forceinline__ void e2m1x8_to_s8x8(uint32_t w, uint32_t& lo, uint32_t& hi) {
-  constexpr uint32_t kPosLo = 0x03020100u, kPosHi = 0x0C080604u;  // 0 1 2 3 | 4 6 8 12
-  constexpr uint32_t kNegLo = 0xFDFEFF00u, kNegHi = 0xF4F8FAFCu;  // 0 -1 -2 -3 | -4 -6 -8 -12
-  const uint32_t sel = w & 0x77777777u, sel_hi = sel >> 16, w4 = w << 4;
-  const uint32_t m_lo = prmt(w4, w, 0xD9C8u), m_hi = prmt(w4, w, 0xFBEAu);  // sign masks of elements 0-3, 4-7
-  lo = (prmt(kPosLo, kPosHi, sel) & ~m_lo) | (prmt(kNegLo, kNegHi, sel) & m_lo);
-  hi = (prmt(kPosLo, kPosHi, sel_hi) & ~m_hi) | (prmt(kNegLo, kNegHi, sel_hi) & m_hi);
+// two E2M1 codes of one byte -> f16x2 (element 2i in the low half), exact
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
 }
 
 struct GemvParams {
@@ -75,10 +66,10 @@ __global__ void __launch_bounds__(gemv::kThreads, M <= 2 ? 2 : 1) nvfp4_gemv_ker
   const uint32_t nb = p.k >> 4;                     // 16-element blocks per row
   const uint32_t kp = (p.k + 1023u) & ~1023u;       // A rows are padded to whole warp steps of 1024 elements
   const uint32_t nbp = p.k_atoms * 4u;              // blocks per row of the scale layout (padded to whole atoms)
-  // [M][kp] twice the E2M1 values of A as int8, permuted so that the 32 lanes of a warp step read consecutive 16-byte
-  // pieces: the piece (one 16-block) of lane l, half j of warp step c sits at ((c*2 + j)*32 + l) * 16 bytes
-  uint4* a_q = reinterpret_cast<uint4*>(smem);
-  float* a_s = reinterpret_cast<float*>(smem + size_t(M) * kp);        // [M][nb] decoded block scales of A
+  // [M][kp/2] E2M1 values of A as f16 pairs, permuted so that the 32 lanes of a warp step read consecutive 16-byte
+  // pieces: the piece of lane l, quarter j of warp step c sits at ((c*4 + j)*32 + l) * 16 bytes
+  __half2* a_h = reinterpret_cast<__half2*>(smem);
+  float* a_s = reinterpret_cast<float*>(smem + size_t(M) * kp * 2);    // [M][nb] decoded block scales of A
   uint8_t* w_sf = reinterpret_cast<uint8_t*>(a_s + size_t(M) * nb);    // this CTA's W scales, row-major [64][nbp]
   __shared__ float inv_d_lut[128];
   __shared__ float e4m3_lut[128];
@@ -126,12 +117,14 @@ __global__ void __launch_bounds__(gemv::kThreads, M <= 2 ? 2 : 1) nvfp4_gemv_ker
       const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
       sc = quant_block16_bf16(w, inv_d_lut, p.inv_t, lo, hi);
     }
-    // block b is half (b & 1) of lane-chunk L = b/2 (warp step c = L/32, lane l = L%32)
-    const uint32_t L = b >> 1;
-    uint4 q;
-    e2m1x8_to_s8x8(lo, q.x, q.y);
-    e2m1x8_to_s8x8(hi, q.z, q.w);
-    a_q[(size_t(row) * kp >> 4) + ((L >> 5) * 2u + (b & 1u)) * 32u + (L & 31u)] = q;
+    uint32_t h[4];
+    // block b is half of lane-chunk L = b/2 (warp step c = L/32, lane l = L%32): quarters j = 2*(b&1), 2*(b&1)+1
+    const uint32_t L = b >> 1, j0 = (b & 1u) * 2u;
+    uint4* dst = reinterpret_cast<uint4*>(a_h + (size_t(row) * kp >> 1)) + ((L >> 5) * 4u + j0) * 32u + (L & 31u);
+    e2m1x8_to_f16x2(lo, h);
+    dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+    e2m1x8_to_f16x2(hi, h);
+    dst[32] = make_uint4(h[0], h[1], h[2], h[3]);
     a_s[i] = e4m3_lut[sc];
   }
   __syncthreads();
@@ -150,22 +143,26 @@ __global__ void __launch_bounds__(gemv::kThreads, M <= 2 ? 2 : 1) nvfp4_gemv_ker
         const uint32_t b0 = e0 >> 4;  // two blocks: b0, b0 + 1 (same scale word of the atom)
         const uint32_t sf2 = *reinterpret_cast<const uint16_t*>(w_sf + rr * nbp + b0);  // consecutive lanes, consecutive pairs
         const float sw[2] = {e4m3_lut[sf2 & 0x7Fu], e4m3_lut[(sf2 >> 8) & 0x7Fu]};
-        uint32_t wq[8];
+        uint32_t wh[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) e2m1x8_to_s8x8(wcw[q], wq[2 * q], wq[2 * q + 1]);
+        for (int q = 0; q < 4; ++q) {
+          uint32_t t4[4];
+          e2m1x8_to_f16x2(wcw[q], t4);
+          wh[q * 4] = t4[0]; wh[q * 4 + 1] = t4[1]; wh[q * 4 + 2] = t4[2]; wh[q * 4 + 3] = t4[3];
+        }
 #pragma unroll
         for (int i = 0; i < M; ++i) {
-          const uint4* ap = a_q + (size_t(i) * kp >> 4) + (ps * 4u + uint32_t(c)) * 64u + lane;
+          const uint4* ap = reinterpret_cast<const uint4*>(a_h + (size_t(i) * kp >> 1)) + (ps * 4u + uint32_t(c)) * 128u + lane;
           const float2 as2 = *reinterpret_cast<const float2*>(a_s + size_t(i) * nb + b0);
 #pragma unroll
           for (int blk = 0; blk < 2; ++blk) {
-            const uint4 av = ap[blk * 32];
-            int sum = __dp4a(int(av.x), int(wq[blk * 4]), 0);
-            sum = __dp4a(int(av.y), int(wq[blk * 4 + 1]), sum);
-            sum = __dp4a(int(av.z), int(wq[blk * 4 + 2]), sum);
-            sum = __dp4a(int(av.w), int(wq[blk * 4 + 3]), sum);
-            // (2a).(2w) summed exactly; the quarter is a power of two, so bs is the exact block sum
-            const float bs = 0.25f * float(sum);
+            const uint4 a0 = ap[blk * 64], a1 = ap[blk * 64 + 32];
+            const uint32_t av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            __half2 sacc = __float2half2_rn(0.0f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              sacc = __hfma2(*reinterpret_cast<const __half2*>(&av[j]), *reinterpret_cast<const __half2*>(&wh[blk * 8 + j]), sacc);
+            const float bs = __low2float(sacc) + __high2float(sacc);  // each half: 8 products <= 36 in steps of 1/4, exact in f16
             acc[i] = fmaf(bs, (blk ? as2.y : as2.x) * sw[blk], acc[i]);
           }
         }
@@ -207,12 +204,12 @@ __global__ void __launch_bounds__(gemv::kThreads, M <= 2 ? 2 : 1) nvfp4_gemv_ker
 
 static uint64_t gemv_smem_bytes(uint32_t m_pad, uint32_t k) {
   const uint64_t kp = (uint64_t(k) + 1023u) & ~uint64_t(1023);
-  return uint64_t(m_pad) * kp + uint64_t(m_pad) * (k >> 4) * 4 + uint64_t(sf_k_atoms(k)) * 256;
+  return uint64_t(m_pad) * kp * 2 + uint64_t(m_pad) * (k >> 4) * 4 + uint64_t(sf_k_atoms(k)) * 256;
 }
 static uint32_t gemv_m_pad(uint32_t m) { return m <= 1 ? 1u : (m <= 2 ? 2u : (m <= 4 ? 4u : 8u)); }
 
 bool gemv_applies(uint32_t m, uint32_t n, uint32_t k) {
-  // the quantised A (int8 + scales) and the CTA's W scales must fit in shared memory with at least two CTAs to an SM
+  // the quantised A (f16 pairs + scales) and the CTA's W scales must fit in shared memory with at least two CTAs to an SM
   return m >= 1 && m <= uint32_t(gemv::kMaxM) && k % 32 == 0 && n % 8 == 0 && gemv_smem_bytes(gemv_m_pad(m), k) <= 96u * 1024u;
 }
 
