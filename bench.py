@@ -21,6 +21,7 @@ reference of the N > 1 lines) and `stream` (configs[3] streamed from pinned host
 
     python bench.py --workload linear --m M --n N --k K [--act 1] [--out-nvfp4] [--iters I] [--flush-l2]
     python bench.py --workload norm-quant --m M --k K
+    python bench.py --workload sdpa --m S --n HEADS*128
 
 time one launch shape (what the ncu captures under profiles/ run).
 
@@ -457,6 +458,43 @@ def time_norm_quant(be, m, k, iters=20, warmup=3):
             "gbs": nbytes / (ms * 1e-3) / 1e9}
 
 
+def time_sdpa(be, s_q, s_k, heads, iters=10, warmup=3, b=1):
+    """Times the attention launch between the linears: bf16 [b, s, heads, 128] tensors, no mask, scale 1/sqrt(128)."""
+    import torch
+
+    d = 128
+    sc = be.scope()
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(777)
+    bufs = []
+    for rows in (s_q, s_k, s_k, s_q):
+        buf = be.allocate(b * rows * heads * d * 2)
+        as_torch(be, buf, torch.bfloat16, (b * rows, heads * d)).copy_(
+            torch.randn(b * rows, heads * d, device=dev, generator=gen).to(torch.bfloat16))
+        bufs.append(buf)
+    q, k, v, out = bufs
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    ts = []
+    for it in range(warmup + iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        sc.sdpa(q, k, v, out, b, s_q, s_k, heads, heads, d ** -0.5)
+        e1.record(stream)
+        be.submit(60000)
+        torch.cuda.synchronize()
+        if it >= warmup:
+            ts.append(e0.elapsed_time(e1))
+    finite = bool(torch.isfinite(as_torch(be, out, torch.bfloat16, (b * s_q, heads * d)).float()).all())
+    for buf in bufs:
+        be.free(buf)
+    ms = float(np.mean(ts))
+    flops = 4.0 * b * heads * s_q * s_k * d
+    return {"op": "sdpa", "b": b, "s_q": s_q, "s_k": s_k, "heads": heads, "d": d, "ms": ms, "ms_min": float(np.min(ts)),
+            "tflops": flops / (ms * 1e-3) / 1e12, "finite": finite}
+
+
 def run_launch_workload(args):
     import torch
     import thinfer_b200 as T
@@ -465,6 +503,8 @@ def run_launch_workload(args):
     be = T.Backend(0)
     if args.workload == "norm-quant":
         res = time_norm_quant(be, args.m, args.k, args.iters, args.warmup)
+    elif args.workload == "sdpa":
+        res = time_sdpa(be, args.m, args.m, args.n // 128, args.iters, args.warmup)
     else:
         res = time_linear(be, args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
                           args.out_nvfp4, dense=args.dense_act)
@@ -545,6 +585,9 @@ def other_shapes(be):
     # sites the reference keeps dense (proj, ffn_down); fraction of the measured sustained bf16 peak
     tensor("c2_out_dense_act_4352x3072x3072", time_linear(be, 4352, 3072, 3072, iters=10, dense=True), peaks["bf16_sustained"])
     tensor("c2_down_dense_act_4352x12288x3072", time_linear(be, 4352, 3072, 12288, iters=10, dense=True), peaks["bf16_sustained"])
+    # the attention between the linears at the configs[1] joint sequence (4352 rows, 24 heads of 128): bf16 tensor cores
+    at = time_sdpa(be, 4352, 4352, HIDDEN // 128, iters=5)
+    out["c2_sdpa_4352x24x128"] = {"us": at["ms"] * 1e3, "tflops": at["tflops"], "bound": "tensor", "frac": at["tflops"] / peaks["bf16_sustained"]}
     pair = time_ffn_pair(be, WAN_M, HIDDEN, WAN_FFN)
     out["c5_ffn_pair_26520_one_gpu"] = {"ms": pair["ms"], "tflops": pair["tflops"], "bound": "tensor", "frac": pair["tflops"] / fp4,
                                         "note": "the N > 1 lines split this work by output columns; this is their same-workload N = 1 time"}
@@ -987,9 +1030,9 @@ def main():
                          "ranks and nvfp4 = the same bytes by NCCL all-gather beyond)")
     ap.add_argument("--bands", type=int, default=2, help="N>1 with --gather push/copy: row bands per linear")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="stack", choices=["stack", "stream", "linear", "norm-quant"],
+    ap.add_argument("--workload", default="stack", choices=["stack", "stream", "linear", "norm-quant", "sdpa"],
                     help="N=1: 'stack' = resident 60-layer block-linear stack (default); 'stream' = streamed variant under 6 GiB; "
-                         "'linear' / 'norm-quant' = one launch shape (--m --n --k)")
+                         "'linear' / 'norm-quant' = one launch shape (--m --n --k); 'sdpa' = the attention launch over --m rows and --n / 128 heads")
     ap.add_argument("--headline-only", action="store_true", help="N=1 stack: skip the `shapes` and `stream` sections")
     ap.add_argument("--m", type=int, default=4352)
     ap.add_argument("--n", type=int, default=3072)
@@ -1011,7 +1054,7 @@ def main():
         run_multi_gpu(args)
     elif args.workload == "stream":
         run_stream_bench(args)
-    elif args.workload in ("linear", "norm-quant"):
+    elif args.workload in ("linear", "norm-quant", "sdpa"):
         run_launch_workload(args)
     else:
         run_single_gpu(args)

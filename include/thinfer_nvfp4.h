@@ -265,6 +265,22 @@ int32_t tnf_quantize_act_shared(tnf_ctx* ctx, tnf_buf a_bf16, uint32_t m, uint32
  * weight side is w_dense instead (mixed arm, see the flag). */
 int32_t tnf_gemm_nvfp4(tnf_ctx* ctx, const tnf_linear_args* args, tnf_buf a_codes, tnf_buf a_scales_device);
 
+/* ---- attention between the linears ------------------------------------------------------ */
+
+/* op_sdpa (thinfer-core/src/ops/sdpa.rs:10-47; the DiT call site thinfer-models/src/qwen_image/dit.rs:618-655 runs it
+ * over the joint [txt ++ img] sequence with has_mask = 0): out = softmax(Q K^T * scale) V per (batch, head).
+ * q, out: bf16 [b, s_q, h_q, d]; k, v: bf16 [b, s_k, h_kv, d] (query head hq reads kv head hq * h_kv / h_q). d must be
+ * 128, scale > 0, mask_mode 0 (no mask: the only mode the DiT blocks use). f32 softmax statistics and accumulation;
+ * the probabilities are rounded to bf16 for the second product (relative Frobenius error <= 4e-3 against the
+ * reference's f32 recurrence). Asynchronous on the compute stream. */
+typedef struct tnf_sdpa_args {
+  uint32_t b, s_q, s_k, h_q, h_kv, d;
+  float scale;
+  uint32_t mask_mode;
+  tnf_buf q, k, v, out;
+} tnf_sdpa_args;
+int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* args);
+
 /* ---- streaming residency (WeightResidency, thinfer-core/src/residency.rs) ------------ */
 
 /* Pinned host arena. host_ptr == NULL allocates `bytes` of pinned memory owned by the

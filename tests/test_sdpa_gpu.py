@@ -1,0 +1,81 @@
+"""Attention between the linears on the device (tnf_sdpa: flash-attention tiling, both products on the tensor
+cores) against the restated reference (oracle.ref_sdpa: thinfer-core/src/ops/sdpa.rs, online softmax in f32, one key
+at a time), which tests/test_oracle_pins.py pins on the reference's own sdpa fixtures.
+
+Tolerance: relative Frobenius error <= 4e-3. The kernel rounds the probabilities to bf16 for the second product and
+evaluates exp as exp2 with the scale folded in; inputs and outputs are bf16 on both sides."""
+import numpy as np
+import pytest
+
+import oracle as O
+from conftest import rel_fro
+
+pytestmark = pytest.mark.gpu
+TOL = 4e-3
+
+
+def _run(be, q, k, v, scale):
+    b, s_q, h_q, d = q.shape
+    _, s_k, h_kv, _ = k.shape
+    qb, kb, vb = be.upload(q), be.upload(k), be.upload(v)
+    out = be.allocate((b * s_q + 1) * h_q * d * 2)
+    be.write_buffer(out, np.full((b * s_q + 1) * h_q * d, 0x7FC0, np.uint16))
+    be.scope().sdpa(qb, kb, vb, out, b, s_q, s_k, h_q, h_kv, scale)
+    be.submit(30000)
+    full = be.read_buffer(out, np.uint16)
+    for buf in (qb, kb, vb, out):
+        be.free(buf)
+    assert (full[b * s_q * h_q * d:] == 0x7FC0).all()  # nothing written past the last row
+    return full[: b * s_q * h_q * d].reshape(b, s_q, h_q, d)
+
+
+def _inputs(b, s_q, s_k, h_q, h_kv, seed, spread=1.0):
+    d = 128
+    q = O.f32_to_bf16(O.gaussian(b * s_q * h_q * d, 0x5100 + seed).reshape(b, s_q, h_q, d) * np.float32(spread))
+    k = O.f32_to_bf16(O.gaussian(b * s_k * h_kv * d, 0x5200 + seed).reshape(b, s_k, h_kv, d))
+    v = O.f32_to_bf16(O.gaussian(b * s_k * h_kv * d, 0x5300 + seed).reshape(b, s_k, h_kv, d))
+    return q, k, v
+
+
+@pytest.mark.parametrize("b,s_q,s_k,h_q,h_kv", [(1, 128, 128, 1, 1), (1, 256, 384, 2, 2), (1, 300, 200, 4, 2), (2, 129, 257, 2, 1),
+                                                 (1, 1, 40, 2, 2), (1, 640, 1100, 3, 3)])
+def test_sdpa_matches_reference_recurrence(backend, b, s_q, s_k, h_q, h_kv):
+    q, k, v = _inputs(b, s_q, s_k, h_q, h_kv, s_q + s_k)
+    scale = 1.0 / np.sqrt(128.0)
+    got = _run(backend, q, k, v, float(scale))
+    want = O.ref_sdpa(q, k, v, float(scale))
+    assert not np.isnan(O.bf16_to_f32(got)).any()
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
+
+
+def test_sdpa_peaked_rows_rescale_the_running_output(backend):
+    """Scores with a large spread: the row maximum keeps growing from tile to tile, so the running output in TMEM is
+    rescaled many times, and most probabilities underflow to zero."""
+    q, k, v = _inputs(1, 256, 1024, 2, 2, 77, spread=6.0)
+    scale = 1.0 / np.sqrt(128.0)
+    got = _run(backend, q, k, v, float(scale))
+    want = O.ref_sdpa(q, k, v, float(scale))
+    assert not np.isnan(O.bf16_to_f32(got)).any()
+    assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
+
+
+def test_sdpa_reference_fixture_d128(backend, golden_ref):
+    """The reference's own D = 128 case (sdpa_large_d_d128: S = 4, one head, scale 0.088388346) through the kernel."""
+    q, k, v, out = (golden_ref[f"fp32/sdpa_large_d_d128/{t}"] for t in "q k v out".split())
+    got = _run(backend, O.f32_to_bf16(q), O.f32_to_bf16(k), O.f32_to_bf16(v), 0.088388346)
+    assert rel_fro(O.bf16_to_f32(got), out) <= 8e-3  # the fixture's inputs are f32: narrowing them to bf16 is part of the error
+
+
+def test_sdpa_argument_errors(backend):
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+
+    buf = backend.allocate(1 << 16)
+    sc = backend.scope()
+    with pytest.raises(T.InvalidArgument, match="d must be 128"):
+        sc.sdpa(buf, buf, buf, buf, 1, 4, 4, 1, 1, 0.1, d=64)
+    with pytest.raises(T.InvalidArgument, match="h_kv must divide"):
+        sc.sdpa(buf, buf, buf, buf, 1, 4, 4, 3, 2, 0.1)
+    with pytest.raises(T.TnfError):
+        sc.sdpa(buf, buf, buf, buf, 1, 4096, 4, 1, 1, 0.1)  # q does not fit its buffer
+    backend.free(buf)

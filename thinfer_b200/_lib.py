@@ -44,6 +44,11 @@ class DenseActSites(C.Structure):
 SITE_QKV, SITE_QKV_SELF, SITE_PROJ, SITE_FFN_UP, SITE_FFN_DOWN = range(5)
 
 
+class SdpaArgs(C.Structure):
+    _fields_ = [("b", C.c_uint32), ("s_q", C.c_uint32), ("s_k", C.c_uint32), ("h_q", C.c_uint32), ("h_kv", C.c_uint32),
+                ("d", C.c_uint32), ("scale", C.c_float), ("mask_mode", C.c_uint32), ("q", Buf), ("k", Buf), ("v", Buf), ("out", Buf)]
+
+
 class NormQuantArgs(C.Structure):
     _fields_ = [
         ("m", C.c_uint32), ("k", C.c_uint32), ("eps", C.c_float), ("mod_bias", C.c_float),
@@ -107,6 +112,7 @@ SIGNATURES = {
     "tnf_prepare_dense": (C.c_int32, [_ctx, Buf, Buf, C.c_uint32, C.c_uint32, Buf]),
     "tnf_site_linear_flags": (C.c_uint32, [C.POINTER(DenseActSites), C.c_int32]),
     "tnf_linear_nvfp4_noalloc": (C.c_int32, [_ctx, C.POINTER(LinearArgs)]),
+    "tnf_sdpa": (C.c_int32, [_ctx, C.POINTER(SdpaArgs)]),
     "tnf_norm_modulate_quantize": (C.c_int32, [_ctx, C.POINTER(NormQuantArgs)]),
     "tnf_noalloc_scratch_bytes": (C.c_uint64, []),
     "tnf_quantize_act_shared": (C.c_int32, [_ctx, Buf, C.c_uint32, C.c_uint32, C.c_float]),

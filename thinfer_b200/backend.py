@@ -365,5 +365,12 @@ class BatchScope:
         args = self._args(m, w, None, a_global, out, act, gate, residual, chain, n_offset, ldo, flags, bias, out_nvfp4)
         _check(self.be.lib.tnf_gemm_nvfp4(self.be._ctx, C.byref(args), a_codes, a_scales_device))
 
+    def sdpa(self, q: Buf, k: Buf, v: Buf, out: Buf, b: int, s_q: int, s_k: int, h_q: int, h_kv: int, scale: float,
+             d: int = 128) -> None:
+        """Joint attention between the linears (``op_sdpa``, thinfer-core/src/ops/sdpa.rs): q / out bf16 [b, s_q, h_q, d],
+        k / v bf16 [b, s_k, h_kv, d], no mask, d = 128."""
+        args = L.SdpaArgs(b, s_q, s_k, h_q, h_kv, d, scale, 0, q, k, v, out)
+        _check(self.be.lib.tnf_sdpa(self.be._ctx, C.byref(args)))
+
     def submit(self, timeout_ms: int = 0) -> None:
         self.be.submit(timeout_ms)

@@ -1,0 +1,379 @@
+// Joint scaled-dot-product attention between the linears of a DiT block (op_sdpa, thinfer-core/src/ops/sdpa.rs:10-47;
+// call site thinfer-models/src/qwen_image/dit.rs:618-655: full attention over [txt ++ img], has_mask = 0, D = 128):
+// out = softmax(Q K^T * scale) V per (batch, head), bf16 in and out, f32 softmax statistics and accumulation.
+//
+// One CTA per (128 query rows, head, batch); flash-attention tiling over 128-key tiles, both products on the tensor
+// cores (tcgen05.mma kind::f16, accumulators in TMEM):
+//   warp 0      TMA: the Q tile once, then K and V tiles into two-stage rings ([128 rows x 64 bf16] boxes with
+//               128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte column window);
+//   warp 1      one elected thread issues S_j = Q K_j^T (both operands K-major, 8 MMAs of K = 16) into one of two
+//               128-column TMEM buffers, one tile AHEAD of the softmax, and O += P_j V_j with V as it lies in
+//               memory (keys x d: an MN-major B operand, no transpose pass);
+//   warps 2-5   online softmax, one query row per thread (TMEM lane = row): pass 1 reads S_j and finds the row
+//               maximum; if it grew, the running output in TMEM is rescaled (tcgen05.ld / mul / tcgen05.st) once
+//               P_{j-1} V_{j-1} has completed; pass 2 reads S_j again, p = exp2(s * scale * log2e - m), sums p in f32
+//               and writes P_j as bf16 into shared memory in the swizzled K-major layout the second product reads.
+//               At the end O / l goes to global memory as bf16.
+// The reference's kernel is the same recurrence one key at a time in f32 (m' = max(m, s); o = o * exp(m - m') +
+// exp(s - m') v; l likewise); here it runs a tile at a time, p is rounded to bf16 for the tensor cores, and exp is
+// exp2 with the scale folded in: the result agrees with the f32 recurrence to bf16 rounding (tests: relative
+// Frobenius error <= 4e-3 against the restated reference).
+// Keys past s_k in the last tile get p = 0; query rows past s_q are computed and not stored. Every mbarrier wait is
+// bounded; a wait that gives up sets the context's status word and the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "../../include/thinfer_nvfp4.h"
+#include "context.h"
+#include "internal.h"
+#include "ptx.cuh"
+
+namespace tnf {
+
+namespace at {
+constexpr int kThreads = 192;
+constexpr uint32_t kD = 128;           // head dimension
+constexpr uint32_t kRows = 128;        // query rows per CTA, keys per tile
+constexpr uint32_t kSub = 128 * 128;   // one [128 rows x 64 bf16] swizzled box: 16 KB
+constexpr uint32_t kTile = 2 * kSub;   // [128 x 128] bf16
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSCol = 0;          // S buffers at columns 0 and 128
+constexpr uint32_t kOCol = 256;        // running output, 128 columns
+constexpr uint32_t kSmemBytes = 1024 + 6 * kTile + 256;  // Q | K x 2 | V x 2 | P | barriers
+}  // namespace at
+
+struct SdpaParams {
+  uint16_t* out;
+  uint32_t* status;
+  long long wait_limit;
+  uint32_t s_q, s_k, h_q, h_kv;
+  float scale_log2;  // scale * log2(e)
+};
+
+// MN-major operand, 128-byte swizzle: rows of 128 bytes hold 64 consecutive MN elements of one K index, 8-row (K)
+// groups are 1024 bytes apart (SBO), the next 64 MN elements start `lbo_bytes` further (LBO).
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+      "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+      "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+__global__ void __launch_bounds__(at::kThreads, 1)
+    sdpa_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const SdpaParams p) {
+  using namespace at;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sP = sV + 2 * kTile, sBar = sP + kTile;
+  const uint32_t q_full = sBar, k_full = sBar + 8, k_empty = sBar + 24, v_full = sBar + 40, v_empty = sBar + 56;
+  const uint32_t s_full = sBar + 72, s_empty = sBar + 88, p_full = sBar + 104, pv_done = sBar + 112;
+  const uint32_t tmem_holder = sBar + 120;
+  volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
+  uint8_t* p_gen = smem_gen + (sP - smem_base);
+
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const uint32_t qt = blockIdx.x, hq = blockIdx.y, bb = blockIdx.z;
+  const uint32_t hkv = (hq * p.h_kv) / p.h_q;
+  const uint32_t q_row0 = bb * p.s_q + qt * kRows, k_row0 = bb * p.s_k;
+  const uint32_t tiles = (p.s_k + kRows - 1u) / kRows;
+  const long long wait_limit = p.wait_limit > 0 ? p.wait_limit : kDefaultWaitLimitCycles;
+
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (uint32_t i = 0; i < 2; ++i) {
+      mbar_init(k_full + 8 * i, 1);
+      mbar_init(k_empty + 8 * i, 1);
+      mbar_init(v_full + 8 * i, 1);
+      mbar_init(v_empty + 8 * i, 1);
+      mbar_init(s_full + 8 * i, 1);
+      mbar_init(s_empty + 8 * i, 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder_gen;
+  pdl_launch_dependents();
+  pdl_wait();  // Q, K and V are the previous kernels' outputs
+
+  if (warp == 0) {
+    // ---------------- loader ----------------
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_full, kTile);
+      tma_load_2d(sQ, &map_q, q_full, int32_t(hq * kD), int32_t(q_row0));
+      tma_load_2d(sQ + kSub, &map_q, q_full, int32_t(hq * kD + 64), int32_t(q_row0));
+    }
+    __syncwarp();
+    for (uint32_t j = 0; j < tiles; ++j) {
+      const uint32_t st = j & 1u, use = j >> 1;
+      if (use > 0 && !mbar_wait_warp(k_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(k_full + 8 * st, kTile);
+        tma_load_2d(sK + st * kTile, &map_k, k_full + 8 * st, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
+        tma_load_2d(sK + st * kTile + kSub, &map_k, k_full + 8 * st, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
+      }
+      __syncwarp();
+      if (use > 0 && !mbar_wait_warp(v_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(v_full + 8 * st, kTile);
+        tma_load_2d(sV + st * kTile, &map_v, v_full + 8 * st, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
+        tma_load_2d(sV + st * kTile + kSub, &map_v, v_full + 8 * st, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc_qk = make_idesc_bf16(kRows, kRows);               // A and B K-major
+    constexpr uint32_t idesc_pv = make_idesc_bf16(kRows, kD) | (1u << 16);     // B (V) MN-major
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag, kStatusMmaTimeout, wait_limit);
+    auto issue_s = [&](uint32_t j) -> bool {  // S_j = Q K_j^T into S buffer j % 2
+      const uint32_t st = j & 1u, use = j >> 1;
+      if (!mbar_wait_warp(k_full + 8 * st, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) return false;
+      if (use > 0 && !mbar_wait_warp(s_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) return false;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (uint32_t kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kSub + (kk & 3u) * 32u;
+          tc_mma_bf16(tmem_base + kSCol + st * 128u, make_desc_sw128(sQ + off), make_desc_sw128(sK + st * kTile + off), idesc_qk, kk != 0u);
+        }
+        tc_commit(s_full + 8 * st);
+        tc_commit(k_empty + 8 * st);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0);
+    for (uint32_t j = 0; j < tiles && ok; ++j) {
+      const uint32_t st = j & 1u, use = j >> 1;
+      if (j + 1 < tiles && !issue_s(j + 1)) break;  // the next tile's scores are computed while the softmax works on this one
+      if (!mbar_wait_warp(p_full, j & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
+      if (!mbar_wait_warp(v_full + 8 * st, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (uint32_t kk = 0; kk < 8; ++kk) {  // 16 keys each: P columns 16kk.., V rows 16kk..
+          const uint32_t poff = (kk >> 2) * kSub + (kk & 3u) * 32u;
+          tc_mma_bf16(tmem_base + kOCol, make_desc_sw128(sP + poff), make_desc_mn_sw128(sV + st * kTile + kk * 2048u, kSub), idesc_pv,
+                      (j | kk) != 0u);
+        }
+        tc_commit(pv_done);
+        tc_commit(v_empty + 8 * st);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------- softmax: one query row per thread ----------------
+    const uint32_t quarter = warp & 3u, row = quarter * 32u + lane;
+    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
+    float m_ref = 0.0f, l = 0.0f;
+    bool ok = true;
+    uint32_t r[32];
+    for (uint32_t j = 0; j < tiles && ok; ++j) {
+      const uint32_t sb = j & 1u;
+      const uint32_t valid = min(kRows, p.s_k - j * kRows);  // keys of this tile that exist
+      if (!mbar_wait_warp(s_full + 8 * sb, (j >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // pass 1: the row maximum of this tile, in the exp2 domain
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (uint32_t c4 = 0; c4 < 4; ++c4) {
+        tmem_ld_32x32b_x32(lane_addr + kSCol + sb * 128u + c4 * 32u, r);
+        tmem_ld_wait();
+        if (valid >= (c4 + 1u) * 32u) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c4 * 32u + uint32_t(i) < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      mx *= p.scale_log2;  // scale > 0: the maximum commutes with it
+      float alpha = 1.0f;
+      if (j == 0) {
+        m_ref = mx;
+      } else if (mx > m_ref) {
+        alpha = ex2(m_ref - mx);
+        m_ref = mx;
+      }
+      if (j > 0) {
+        // P_{j-1} V_{j-1} must have completed before O is rescaled and before P is overwritten
+        if (!mbar_wait_warp(pv_done, (j - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (uint32_t c4 = 0; c4 < 4; ++c4) {
+            tmem_ld_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+          }
+          tmem_st_wait();
+        }
+        l *= alpha;
+      }
+      // pass 2: p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 into the swizzled K-major tile
+      const float neg_m = -m_ref;
+#pragma unroll 1
+      for (uint32_t c4 = 0; c4 < 4; ++c4) {
+        tmem_ld_32x32b_x32(lane_addr + kSCol + sb * 128u + c4 * 32u, r);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          if (valid < kRows && c4 * 32u + uint32_t(i) >= valid) e = 0.0f;
+          pv[i] = e;
+          l += e;
+        }
+        uint8_t* prow = p_gen + (c4 >> 1) * kSub + row * 128u;
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {  // 8 keys = one 16-byte chunk; chunk c of row r sits at position c ^ (r % 8)
+          const uint32_t chunk = (c4 & 1u) * 4u + q;
+          uint4 w;
+          w.x = pack_bf16x2(pv[q * 8 + 0], pv[q * 8 + 1]);
+          w.y = pack_bf16x2(pv[q * 8 + 2], pv[q * 8 + 3]);
+          w.z = pack_bf16x2(pv[q * 8 + 4], pv[q * 8 + 5]);
+          w.w = pack_bf16x2(pv[q * 8 + 6], pv[q * 8 + 7]);
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7u)) << 4)) = w;
+        }
+      }
+      tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrivals below
+      fence_proxy_async();  // P was written by ordinary stores; the MMA reads it through the async proxy
+      mbar_arrive(p_full);
+      mbar_arrive(s_empty + 8 * sb);
+    }
+    // ---------------- O / l -> global ----------------
+    if (ok && mbar_wait_warp(pv_done, (tiles - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+      const bool store = qt * kRows + row < p.s_q;
+      uint16_t* dst = p.out + (uint64_t(q_row0 + row) * p.h_q + hq) * kD;
+#pragma unroll 1
+      for (uint32_t c4 = 0; c4 < 4; ++c4) {
+        tmem_ld_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+        tmem_ld_wait();
+        if (store) {
+#pragma unroll
+          for (uint32_t q = 0; q < 4; ++q) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l);
+            w.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l);
+            w.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l);
+            w.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + c4 * 32u + q * 8u) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (tid == 0 && *abort_flag != 0u) atomicCAS(p.status, 0u, *abort_flag);
+}
+
+}  // namespace tnf
+
+using namespace tnf;
+
+extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
+  if (!ctx || !a) {
+    set_error("tnf_sdpa: null context or args");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (a->b == 0 || a->s_q == 0 || a->s_k == 0 || a->h_q == 0 || a->h_kv == 0 || a->d != at::kD || a->h_q % a->h_kv != 0 ||
+      !(a->scale > 0.0f) || a->mask_mode != 0) {
+    set_error("tnf_sdpa: b=%u s_q=%u s_k=%u h_q=%u h_kv=%u d=%u scale=%g mask_mode=%u (d must be 128, h_kv must divide h_q, "
+              "scale > 0, mask_mode 0)", a->b, a->s_q, a->s_k, a->h_q, a->h_kv, a->d, a->scale, a->mask_mode);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  const uint64_t q_rows = uint64_t(a->b) * a->s_q, k_rows = uint64_t(a->b) * a->s_k;
+  if (q_rows >= (1ull << 31) || k_rows >= (1ull << 31) || uint64_t(a->s_q + 127u) / 128u > 0x7FFFFFFFull || a->h_q > 65535u || a->b > 65535u) {
+    set_error("tnf_sdpa: problem too large for the grid (b*s < 2^31, h_q and b <= 65535)");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  int32_t st = TNF_OK;
+  const uint64_t q_cols = uint64_t(a->h_q) * at::kD, kv_cols = uint64_t(a->h_kv) * at::kD;
+  uint8_t* q = resolve(ctx, a->q, q_rows * q_cols * 2, "q", &st);
+  if (!q) return st;
+  uint8_t* k = resolve(ctx, a->k, k_rows * kv_cols * 2, "k", &st);
+  if (!k) return st;
+  uint8_t* v = resolve(ctx, a->v, k_rows * kv_cols * 2, "v", &st);
+  if (!v) return st;
+  uint8_t* out = resolve(ctx, a->out, q_rows * q_cols * 2, "out", &st);
+  if (!out) return st;
+  if (cudaSetDevice(ctx->device) != cudaSuccess) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  CUtensorMap mq, mk, mv;  // [rows, heads * 128] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
+  if (!get_map(ctx, MapSpec{q, 2, q_cols, q_rows, q_cols * 2, 64, 128, 128}, &mq) ||
+      !get_map(ctx, MapSpec{k, 2, kv_cols, k_rows, kv_cols * 2, 64, 128, 128}, &mk) ||
+      !get_map(ctx, MapSpec{v, 2, kv_cols, k_rows, kv_cols * 2, 64, 128, 128}, &mv))
+    return TNF_ERR_INVALID_ARGUMENT;
+  SdpaParams p{};
+  p.out = reinterpret_cast<uint16_t*>(out);
+  p.status = ctx->dwords;
+  p.wait_limit = ctx->wait_limit_cycles;
+  p.s_q = a->s_q; p.s_k = a->s_k; p.h_q = a->h_q; p.h_kv = a->h_kv;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  static PerDeviceOnce once;
+  if (once.first_use() >= 0) {
+    cudaError_t e = cudaFuncSetAttribute(sdpa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(at::kSmemBytes));
+    if (e != cudaSuccess) return cuda_fail(e, "sdpa kernel attribute");
+  }
+  cudaError_t e = launch_pdl(sdpa_kernel, dim3((a->s_q + 127u) / 128u, a->h_q, a->b), dim3(at::kThreads), at::kSmemBytes, ctx->compute,
+                             mq, mk, mv, p);
+  if (e != cudaSuccess) return cuda_fail(e, "sdpa launch");
+  return TNF_OK;
+}
