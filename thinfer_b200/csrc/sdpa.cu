@@ -3,17 +3,22 @@
 // out = softmax(Q K^T * scale) V per (batch, head), bf16 in and out, f32 softmax statistics and accumulation.
 //
 // One CTA per (128 query rows, head, batch); flash-attention tiling over 128-key tiles, both products on the tensor
-// cores (tcgen05.mma kind::f16, accumulators in TMEM):
+// cores (tcgen05.mma kind::f16, accumulators in TMEM). The key tiles are dealt alternately to two independent
+// softmax groups, each with its own score buffer S_g, probability tile P_g and running output O_g (4 x 128 TMEM
+// columns), so that one group's exponentials run under the other's TMEM traffic and waits; the two partial results
+// are merged at the end by their softmax statistics.
 //   warp 0      TMA: the Q tile once, then K and V tiles into two-stage rings ([128 rows x 64 bf16] boxes with
 //               128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte column window);
-//   warp 1      one elected thread issues S_j = Q K_j^T (both operands K-major, 8 MMAs of K = 16) into one of two
-//               128-column TMEM buffers, one tile AHEAD of the softmax, and O += P_j V_j with V as it lies in
-//               memory (keys x d: an MN-major B operand, no transpose pass);
-//   warps 2-5   online softmax, one query row per thread (TMEM lane = row): pass 1 reads S_j and finds the row
-//               maximum; if it grew, the running output in TMEM is rescaled (tcgen05.ld / mul / tcgen05.st) once
-//               P_{j-1} V_{j-1} has completed; pass 2 reads S_j again, p = exp2(s * scale * log2e - m), sums p in f32
-//               and writes P_j as bf16 into shared memory in the swizzled K-major layout the second product reads.
-//               At the end O / l goes to global memory as bf16.
+//   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) and
+//               O_g += P_g V_j with V as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
+//               after P_g V_j it issues the group's next scores at once, so they are ready when the group returns;
+//   warps 2-9   two groups of four warps, one query row per thread (TMEM lane = row). Pass 1 reads S_g and finds the
+//               row maximum; the reference maximum m only moves when the row maximum exceeds it by more than 8 (in
+//               the exp2 domain: probabilities stay below 256), and only then is O_g rescaled (tcgen05.ld / mul /
+//               tcgen05.st) once the group's previous product has completed; pass 2 reads S_g again,
+//               p = exp2(s * scale * log2e - m), sums p in f32 and writes P_g as bf16 into shared memory in the
+//               swizzled K-major layout the second product reads. At the end the groups exchange (m, l) through
+//               shared memory and each writes half of the columns of (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1).
 // The reference's kernel is the same recurrence one key at a time in f32 (m' = max(m, s); o = o * exp(m - m') +
 // exp(s - m') v; l likewise); here it runs a tile at a time, p is rounded to bf16 for the tensor cores, and exp is
 // exp2 with the scale folded in: the result agrees with the f32 recurrence to bf16 rounding (tests: relative
@@ -33,15 +38,16 @@
 namespace tnf {
 
 namespace at {
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;          // loader, MMA issuer, two softmax groups of four warps
 constexpr uint32_t kD = 128;           // head dimension
 constexpr uint32_t kRows = 128;        // query rows per CTA, keys per tile
 constexpr uint32_t kSub = 128 * 128;   // one [128 rows x 64 bf16] swizzled box: 16 KB
 constexpr uint32_t kTile = 2 * kSub;   // [128 x 128] bf16
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSCol = 0;          // S buffers at columns 0 and 128
-constexpr uint32_t kOCol = 256;        // running output, 128 columns
-constexpr uint32_t kSmemBytes = 1024 + 6 * kTile + 256;  // Q | K x 2 | V x 2 | P | barriers
+constexpr uint32_t kSCol = 0;          // the groups' score buffers at columns 0 and 128
+constexpr uint32_t kOCol = 256;        // the groups' running outputs at columns 256 and 384
+constexpr float kLazy = 8.0f;          // the reference maximum moves only when the row maximum exceeds it by this much
+constexpr uint32_t kSmemBytes = 1024 + 7 * kTile + 256;  // Q | K x 2 | V x 2 | P x 2 | barriers
 }  // namespace at
 
 struct SdpaParams {
@@ -96,13 +102,12 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sP = sV + 2 * kTile, sBar = sP + kTile;
+  const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sP = sV + 2 * kTile, sBar = sP + 2 * kTile;
   const uint32_t q_full = sBar, k_full = sBar + 8, k_empty = sBar + 24, v_full = sBar + 40, v_empty = sBar + 56;
-  const uint32_t s_full = sBar + 72, s_empty = sBar + 88, p_full = sBar + 104, pv_done = sBar + 112;
+  const uint32_t s_full = sBar + 72, p_full = sBar + 88, pv_done = sBar + 104;
   const uint32_t tmem_holder = sBar + 120;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
-  uint8_t* p_gen = smem_gen + (sP - smem_base);
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const uint32_t qt = blockIdx.x, hq = blockIdx.y, bb = blockIdx.z;
@@ -119,10 +124,9 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       mbar_init(v_full + 8 * i, 1);
       mbar_init(v_empty + 8 * i, 1);
       mbar_init(s_full + 8 * i, 1);
-      mbar_init(s_empty + 8 * i, 128);
+      mbar_init(p_full + 8 * i, 128);
+      mbar_init(pv_done + 8 * i, 1);
     }
-    mbar_init(p_full, 128);
-    mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -140,6 +144,8 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   pdl_launch_dependents();
   pdl_wait();  // Q, K and V are the previous kernels' outputs
 
+  // Key tile j belongs to group g = j % 2 and is the group's use = j / 2; it travels through ring stage g, score
+  // buffer g, probability tile g and output g.
   if (warp == 0) {
     // ---------------- loader ----------------
     if (elect_one()) {
@@ -149,19 +155,19 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     }
     __syncwarp();
     for (uint32_t j = 0; j < tiles; ++j) {
-      const uint32_t st = j & 1u, use = j >> 1;
-      if (use > 0 && !mbar_wait_warp(k_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
+      const uint32_t g = j & 1u, use = j >> 1;
+      if (use > 0 && !mbar_wait_warp(k_empty + 8 * g, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
       if (elect_one()) {
-        mbar_arrive_expect_tx(k_full + 8 * st, kTile);
-        tma_load_2d(sK + st * kTile, &map_k, k_full + 8 * st, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
-        tma_load_2d(sK + st * kTile + kSub, &map_k, k_full + 8 * st, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
+        mbar_arrive_expect_tx(k_full + 8 * g, kTile);
+        tma_load_2d(sK + g * kTile, &map_k, k_full + 8 * g, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
+        tma_load_2d(sK + g * kTile + kSub, &map_k, k_full + 8 * g, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
       }
       __syncwarp();
-      if (use > 0 && !mbar_wait_warp(v_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
+      if (use > 0 && !mbar_wait_warp(v_empty + 8 * g, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
       if (elect_one()) {
-        mbar_arrive_expect_tx(v_full + 8 * st, kTile);
-        tma_load_2d(sV + st * kTile, &map_v, v_full + 8 * st, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
-        tma_load_2d(sV + st * kTile + kSub, &map_v, v_full + 8 * st, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
+        mbar_arrive_expect_tx(v_full + 8 * g, kTile);
+        tma_load_2d(sV + g * kTile, &map_v, v_full + 8 * g, int32_t(hkv * kD), int32_t(k_row0 + j * kRows));
+        tma_load_2d(sV + g * kTile + kSub, &map_v, v_full + 8 * g, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
       }
       __syncwarp();
     }
@@ -170,62 +176,65 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     constexpr uint32_t idesc_qk = make_idesc_bf16(kRows, kRows);               // A and B K-major
     constexpr uint32_t idesc_pv = make_idesc_bf16(kRows, kD) | (1u << 16);     // B (V) MN-major
     bool ok = mbar_wait_warp(q_full, 0, abort_flag, kStatusMmaTimeout, wait_limit);
-    auto issue_s = [&](uint32_t j) -> bool {  // S_j = Q K_j^T into S buffer j % 2
-      const uint32_t st = j & 1u, use = j >> 1;
-      if (!mbar_wait_warp(k_full + 8 * st, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) return false;
-      if (use > 0 && !mbar_wait_warp(s_empty + 8 * st, (use - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) return false;
+    // S_g = Q K_j^T. The buffer is free: the group arrived on p_full for its previous tile after its last read of it.
+    auto issue_s = [&](uint32_t j) -> bool {
+      const uint32_t g = j & 1u, use = j >> 1;
+      if (!mbar_wait_warp(k_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) return false;
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
         for (uint32_t kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * kSub + (kk & 3u) * 32u;
-          tc_mma_bf16(tmem_base + kSCol + st * 128u, make_desc_sw128(sQ + off), make_desc_sw128(sK + st * kTile + off), idesc_qk, kk != 0u);
+          tc_mma_bf16(tmem_base + kSCol + g * 128u, make_desc_sw128(sQ + off), make_desc_sw128(sK + g * kTile + off), idesc_qk, kk != 0u);
         }
-        tc_commit(s_full + 8 * st);
-        tc_commit(k_empty + 8 * st);
+        tc_commit(s_full + 8 * g);
+        tc_commit(k_empty + 8 * g);
       }
       __syncwarp();
       return true;
     };
     if (ok) ok = issue_s(0);
+    if (ok && tiles > 1) ok = issue_s(1);
     for (uint32_t j = 0; j < tiles && ok; ++j) {
-      const uint32_t st = j & 1u, use = j >> 1;
-      if (j + 1 < tiles && !issue_s(j + 1)) break;  // the next tile's scores are computed while the softmax works on this one
-      if (!mbar_wait_warp(p_full, j & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
-      if (!mbar_wait_warp(v_full + 8 * st, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
+      const uint32_t g = j & 1u, use = j >> 1;
+      if (!mbar_wait_warp(p_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
+      if (!mbar_wait_warp(v_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
         for (uint32_t kk = 0; kk < 8; ++kk) {  // 16 keys each: P columns 16kk.., V rows 16kk..
           const uint32_t poff = (kk >> 2) * kSub + (kk & 3u) * 32u;
-          tc_mma_bf16(tmem_base + kOCol, make_desc_sw128(sP + poff), make_desc_mn_sw128(sV + st * kTile + kk * 2048u, kSub), idesc_pv,
-                      (j | kk) != 0u);
+          tc_mma_bf16(tmem_base + kOCol + g * 128u, make_desc_sw128(sP + g * kTile + poff),
+                      make_desc_mn_sw128(sV + g * kTile + kk * 2048u, kSub), idesc_pv, (use | kk) != 0u);
         }
-        tc_commit(pv_done);
-        tc_commit(v_empty + 8 * st);
+        tc_commit(pv_done + 8 * g);
+        tc_commit(v_empty + 8 * g);
       }
       __syncwarp();
+      if (j + 2 < tiles && !issue_s(j + 2)) break;  // the group's next scores, ready when it comes back
     }
   } else {
-    // ---------------- softmax: one query row per thread ----------------
-    const uint32_t quarter = warp & 3u, row = quarter * 32u + lane;
+    // ---------------- softmax: two groups, one query row per thread ----------------
+    const uint32_t g = (warp - 2u) >> 2, quarter = warp & 3u, row = quarter * 32u + lane;
     const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    float m_ref = 0.0f, l = 0.0f;
+    const uint32_t s_addr = lane_addr + kSCol + g * 128u, o_addr = lane_addr + kOCol + g * 128u;
+    uint8_t* p_gen = smem_gen + (sP + g * kTile - smem_base);
+    float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
     uint32_t r[32];
-    for (uint32_t j = 0; j < tiles && ok; ++j) {
-      const uint32_t sb = j & 1u;
+    uint32_t use = 0;
+    for (uint32_t j = g; j < tiles && ok; j += 2, ++use) {
       const uint32_t valid = min(kRows, p.s_k - j * kRows);  // keys of this tile that exist
-      if (!mbar_wait_warp(s_full + 8 * sb, (j >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+      if (!mbar_wait_warp(s_full + 8 * g, use & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      // pass 1: the row maximum of this tile, in the exp2 domain
+      // pass 1: the row maximum of this tile
       float mx = -INFINITY;
 #pragma unroll 1
       for (uint32_t c4 = 0; c4 < 4; ++c4) {
-        tmem_ld_32x32b_x32(lane_addr + kSCol + sb * 128u + c4 * 32u, r);
+        tmem_ld_32x32b_x32(s_addr + c4 * 32u, r);
         tmem_ld_wait();
         if (valid >= (c4 + 1u) * 32u) {
 #pragma unroll
@@ -238,15 +247,15 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       }
       mx *= p.scale_log2;  // scale > 0: the maximum commutes with it
       float alpha = 1.0f;
-      if (j == 0) {
+      if (use == 0) {
         m_ref = mx;
-      } else if (mx > m_ref) {
+      } else if (mx > m_ref + kLazy) {
         alpha = ex2(m_ref - mx);
         m_ref = mx;
       }
-      if (j > 0) {
-        // P_{j-1} V_{j-1} must have completed before O is rescaled and before P is overwritten
-        if (!mbar_wait_warp(pv_done, (j - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+      if (use > 0) {
+        // the group's previous product must have completed before O_g is rescaled and before P_g is overwritten
+        if (!mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
           ok = false;
           break;
         }
@@ -254,11 +263,11 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
 #pragma unroll 1
           for (uint32_t c4 = 0; c4 < 4; ++c4) {
-            tmem_ld_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+            tmem_ld_32x32b_x32(o_addr + c4 * 32u, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+            tmem_st_32x32b_x32(o_addr + c4 * 32u, r);
           }
           tmem_st_wait();
         }
@@ -268,7 +277,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       const float neg_m = -m_ref;
 #pragma unroll 1
       for (uint32_t c4 = 0; c4 < 4; ++c4) {
-        tmem_ld_32x32b_x32(lane_addr + kSCol + sb * 128u + c4 * 32u, r);
+        tmem_ld_32x32b_x32(s_addr + c4 * 32u, r);
         tmem_ld_wait();
         float pv[32];
 #pragma unroll
@@ -290,30 +299,47 @@ __global__ void __launch_bounds__(at::kThreads, 1)
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7u)) << 4)) = w;
         }
       }
-      tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrivals below
+      tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrival below
       fence_proxy_async();  // P was written by ordinary stores; the MMA reads it through the async proxy
-      mbar_arrive(p_full);
-      mbar_arrive(s_empty + 8 * sb);
+      mbar_arrive(p_full + 8 * g);
     }
-    // ---------------- O / l -> global ----------------
-    if (ok && mbar_wait_warp(pv_done, (tiles - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
-      tc_fence_after();
-      const float inv_l = 1.0f / l;
+    // ---------------- merge the two groups: (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1) -> global ----------------
+    if (ok && use > 0) ok = mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
+    // the group's probability tile is free now: its first KB carries (m, l) per row to the other group
+    reinterpret_cast<float2*>(p_gen)[row] = make_float2(m_ref, l);
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps; every one of them gets here, whatever happened
+    tc_fence_after();
+    const float2 other = reinterpret_cast<const float2*>(smem_gen + (sP + (g ^ 1u) * kTile - smem_base))[row];
+    const bool other_has = g == 1u || tiles > 1u;  // group 1 has no tile when there is a single one
+    if (ok && __all_sync(0xFFFFFFFFu, *abort_flag == 0u)) {
+      const bool mine_has = use > 0;
+      const float m = fmaxf(mine_has ? m_ref : -INFINITY, other_has ? other.x : -INFINITY);
+      const float w_mine = mine_has ? ex2(m_ref - m) : 0.0f, w_other = other_has ? ex2(other.x - m) : 0.0f;
+      const float inv = 1.0f / (l * w_mine + (other_has ? other.y : 0.0f) * w_other);
+      const float f_mine = w_mine * inv, f_other = w_other * inv;
       const bool store = qt * kRows + row < p.s_q;
-      uint16_t* dst = p.out + (uint64_t(q_row0 + row) * p.h_q + hq) * kD;
+      uint16_t* dst = p.out + (uint64_t(q_row0 + row) * p.h_q + hq) * kD + g * 64u;  // group g writes columns 64g .. 64g+63
+      const uint32_t o_other = lane_addr + kOCol + (g ^ 1u) * 128u;
+      uint32_t r2[32];
 #pragma unroll 1
-      for (uint32_t c4 = 0; c4 < 4; ++c4) {
-        tmem_ld_32x32b_x32(lane_addr + kOCol + c4 * 32u, r);
+      for (uint32_t c2 = 0; c2 < 2; ++c2) {
+        const uint32_t col = g * 64u + c2 * 32u;
+        if (mine_has) tmem_ld_32x32b_x32(o_addr + col, r);
+        if (other_has) tmem_ld_32x32b_x32(o_other + col, r2);
         tmem_ld_wait();
         if (store) {
 #pragma unroll
           for (uint32_t q = 0; q < 4; ++q) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o[i] = (mine_has ? __uint_as_float(r[q * 8 + i]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[q * 8 + i]) * f_other : 0.0f);
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(r[q * 8 + 0]) * inv_l, __uint_as_float(r[q * 8 + 1]) * inv_l);
-            w.y = pack_bf16x2(__uint_as_float(r[q * 8 + 2]) * inv_l, __uint_as_float(r[q * 8 + 3]) * inv_l);
-            w.z = pack_bf16x2(__uint_as_float(r[q * 8 + 4]) * inv_l, __uint_as_float(r[q * 8 + 5]) * inv_l);
-            w.w = pack_bf16x2(__uint_as_float(r[q * 8 + 6]) * inv_l, __uint_as_float(r[q * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(dst + c4 * 32u + q * 8u) = w;
+            w.x = pack_bf16x2(o[0], o[1]);
+            w.y = pack_bf16x2(o[2], o[3]);
+            w.z = pack_bf16x2(o[4], o[5]);
+            w.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(dst + c2 * 32u + q * 8u) = w;
           }
         }
       }
