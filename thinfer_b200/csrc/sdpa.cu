@@ -12,12 +12,12 @@
 //   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) and
 //               O_g += P_g V_j with V as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
 //               after P_g V_j it issues the group's next scores at once, so they are ready when the group returns;
-//   warps 2-9   two groups of four warps, one query row per thread (TMEM lane = row). Pass 1 reads S_g and finds the
-//               row maximum; the reference maximum m only moves when the row maximum exceeds it by more than 8 (in
-//               the exp2 domain: probabilities stay below 256), and only then is O_g rescaled (tcgen05.ld / mul /
-//               tcgen05.st) once the group's previous product has completed; pass 2 reads S_g again,
-//               p = exp2(s * scale * log2e - m), sums p in f32 and writes P_g as bf16 into shared memory in the
-//               swizzled K-major layout the second product reads. At the end the groups exchange (m, l) through
+//   warps 2-9   two groups of four warps, one query row per thread (TMEM lane = row). The thread reads its whole
+//               score row into registers (four loads in flight, one wait) and finds the row maximum; the reference
+//               maximum m only moves when the row maximum exceeds it by more than 8 (in the exp2 domain:
+//               probabilities stay below 256), and only then is O_g rescaled (tcgen05.ld / mul / tcgen05.st) once
+//               the group's previous product has completed; then p = exp2(s * scale * log2e - m), summed in f32,
+//               goes as bf16 into shared memory in the swizzled K-major layout the second product reads. At the end the groups exchange (m, l) through
 //               shared memory and each writes half of the columns of (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1).
 // The reference's kernel is the same recurrence one key at a time in f32 (m' = max(m, s); o = o * exp(m - m') +
 // exp(s - m') v; l likewise); here it runs a tile at a time, p is rounded to bf16 for the tensor cores, and exp is
@@ -82,6 +82,17 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
       "r"(r[31])
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
@@ -221,7 +232,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     uint8_t* p_gen = smem_gen + (sP + g * kTile - smem_base);
     float m_ref = -INFINITY, l = 0.0f;
     bool ok = true;
-    uint32_t r[32];
+    uint32_t r[32], s0[32], s1[32], s2[32], s3[32];
     uint32_t use = 0;
     for (uint32_t j = g; j < tiles && ok; j += 2, ++use) {
       const uint32_t valid = min(kRows, p.s_k - j * kRows);  // keys of this tile that exist
@@ -230,21 +241,34 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         break;
       }
       tc_fence_after();
-      // pass 1: the row maximum of this tile
+      // the whole score row goes to registers in one round trip (four loads in flight, one wait)
+      tmem_ld_32x32b_x32(s_addr, s0);
+      tmem_ld_32x32b_x32(s_addr + 32u, s1);
+      tmem_ld_32x32b_x32(s_addr + 64u, s2);
+      tmem_ld_32x32b_x32(s_addr + 96u, s3);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (uint32_t c4 = 0; c4 < 4; ++c4) {
-        tmem_ld_32x32b_x32(s_addr + c4 * 32u, r);
-        tmem_ld_wait();
+      auto row_max = [&](const uint32_t(&c)[32], uint32_t c4) {
         if (valid >= (c4 + 1u) * 32u) {
+          float a = -INFINITY, b = -INFINITY, d = -INFINITY, e = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 4) {
+            a = fmaxf(a, __uint_as_float(c[i]));
+            b = fmaxf(b, __uint_as_float(c[i + 1]));
+            d = fmaxf(d, __uint_as_float(c[i + 2]));
+            e = fmaxf(e, __uint_as_float(c[i + 3]));
+          }
+          mx = fmaxf(mx, fmaxf(fmaxf(a, b), fmaxf(d, e)));
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c4 * 32u + uint32_t(i) < valid) mx = fmaxf(mx, __uint_as_float(r[i]));
+            if (c4 * 32u + uint32_t(i) < valid) mx = fmaxf(mx, __uint_as_float(c[i]));
         }
-      }
+      };
+      row_max(s0, 0);
+      row_max(s1, 1);
+      row_max(s2, 2);
+      row_max(s3, 3);
       mx *= p.scale_log2;  // scale > 0: the maximum commutes with it
       float alpha = 1.0f;
       if (use == 0) {
@@ -261,44 +285,54 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         }
         tc_fence_after();
         if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+          // rare (the maximum jumped by more than 2^8), and the score row is live in registers: small pieces
+          uint32_t o8[8];
 #pragma unroll 1
-          for (uint32_t c4 = 0; c4 < 4; ++c4) {
-            tmem_ld_32x32b_x32(o_addr + c4 * 32u, r);
+          for (uint32_t c = 0; c < kD; c += 8u) {
+            tmem_ld_32x32b_x8(o_addr + c, o8);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(o_addr + c4 * 32u, r);
+            for (int i = 0; i < 8; ++i) o8[i] = __float_as_uint(__uint_as_float(o8[i]) * alpha);
+            tmem_st_32x32b_x8(o_addr + c, o8);
           }
           tmem_st_wait();
         }
         l *= alpha;
       }
-      // pass 2: p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 into the swizzled K-major tile
+      // p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 into the swizzled K-major tile
       const float neg_m = -m_ref;
-#pragma unroll 1
-      for (uint32_t c4 = 0; c4 < 4; ++c4) {
-        tmem_ld_32x32b_x32(s_addr + c4 * 32u, r);
-        tmem_ld_wait();
-        float pv[32];
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+      auto emit = [&](uint32_t(&c)[32], uint32_t c4) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          float e = ex2(fmaf(__uint_as_float(c[i]), p.scale_log2, neg_m));
           if (valid < kRows && c4 * 32u + uint32_t(i) >= valid) e = 0.0f;
-          pv[i] = e;
-          l += e;
+          c[i] = __float_as_uint(e);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          l0 += __uint_as_float(c[i]);
+          l1 += __uint_as_float(c[i + 1]);
+          l2 += __uint_as_float(c[i + 2]);
+          l3 += __uint_as_float(c[i + 3]);
         }
         uint8_t* prow = p_gen + (c4 >> 1) * kSub + row * 128u;
 #pragma unroll
         for (uint32_t q = 0; q < 4; ++q) {  // 8 keys = one 16-byte chunk; chunk c of row r sits at position c ^ (r % 8)
           const uint32_t chunk = (c4 & 1u) * 4u + q;
           uint4 w;
-          w.x = pack_bf16x2(pv[q * 8 + 0], pv[q * 8 + 1]);
-          w.y = pack_bf16x2(pv[q * 8 + 2], pv[q * 8 + 3]);
-          w.z = pack_bf16x2(pv[q * 8 + 4], pv[q * 8 + 5]);
-          w.w = pack_bf16x2(pv[q * 8 + 6], pv[q * 8 + 7]);
+          w.x = pack_bf16x2(__uint_as_float(c[q * 8 + 0]), __uint_as_float(c[q * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(c[q * 8 + 2]), __uint_as_float(c[q * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(c[q * 8 + 4]), __uint_as_float(c[q * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(c[q * 8 + 6]), __uint_as_float(c[q * 8 + 7]));
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7u)) << 4)) = w;
         }
-      }
+      };
+      emit(s0, 0);
+      emit(s1, 1);
+      emit(s2, 2);
+      emit(s3, 3);
+      l += (l0 + l1) + (l2 + l3);
       tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrival below
       fence_proxy_async();  // P was written by ordinary stores; the MMA reads it through the async proxy
       mbar_arrive(p_full + 8 * g);
