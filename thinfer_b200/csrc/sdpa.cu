@@ -7,11 +7,12 @@
 // softmax groups, each with its own score buffer S_g, probability tile P_g and running output O_g (4 x 128 TMEM
 // columns), so that one group's exponentials run under the other's TMEM traffic and waits; the two partial results
 // are merged at the end by their softmax statistics.
-//   warp 0      TMA: the Q tile once, then K and V tiles into two-stage rings ([128 rows x 64 bf16] boxes with
-//               128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte column window);
+//   warps 0, 10 TMA: the Q tile once, then K tiles (warp 0) and V tiles (warp 10) into two-stage rings ([128 rows x
+//               64 bf16] boxes with 128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte
+//               column window);
 //   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) and
 //               O_g += P_g V_j with V as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
-//               after P_g V_j it issues the group's next scores at once, so they are ready when the group returns;
+//               a group's next scores are issued as soon as it has taken the current score row into registers;
 //   warps 2-9   two groups of four warps, one query row per thread (TMEM lane = row). The thread reads its whole
 //               score row into registers (four loads in flight, one wait) and finds the row maximum; the reference
 //               maximum m only moves when the row maximum exceeds it by more than 8 (in the exp2 domain:
@@ -38,7 +39,7 @@
 namespace tnf {
 
 namespace at {
-constexpr int kThreads = 320;          // loader, MMA issuer, two softmax groups of four warps
+constexpr int kThreads = 352;          // Q/K loader, MMA issuer, two softmax groups of four warps, V loader
 constexpr uint32_t kD = 128;           // head dimension
 constexpr uint32_t kRows = 128;        // query rows per CTA, keys per tile
 constexpr uint32_t kSub = 128 * 128;   // one [128 rows x 64 bf16] swizzled box: 16 KB
@@ -100,6 +101,12 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two non-negative finite f32 -> bf16 pair by integer arithmetic (add half an ulp of bf16, keep the high halves: round
+// to nearest, ties up): the hardware conversion shares the special-function pipe with exp2, which is this kernel's
+// bottleneck, and a tie is one value in 65536.
+__device__ __forceinline__ uint32_t pack_bf16x2_pos(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t d;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
@@ -115,8 +122,8 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sP = sV + 2 * kTile, sBar = sP + 2 * kTile;
   const uint32_t q_full = sBar, k_full = sBar + 8, k_empty = sBar + 24, v_full = sBar + 40, v_empty = sBar + 56;
-  const uint32_t s_full = sBar + 72, p_full = sBar + 88, pv_done = sBar + 104;
-  const uint32_t tmem_holder = sBar + 120;
+  const uint32_t s_full = sBar + 72, p_full = sBar + 88, pv_done = sBar + 104, s_free = sBar + 120;
+  const uint32_t tmem_holder = sBar + 136;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
 
@@ -137,6 +144,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       mbar_init(s_full + 8 * i, 1);
       mbar_init(p_full + 8 * i, 128);
       mbar_init(pv_done + 8 * i, 1);
+      mbar_init(s_free + 8 * i, 128);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -158,7 +166,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   // Key tile j belongs to group g = j % 2 and is the group's use = j / 2; it travels through ring stage g, score
   // buffer g, probability tile g and output g.
   if (warp == 0) {
-    // ---------------- loader ----------------
+    // ---------------- Q and K loader ----------------
     if (elect_one()) {
       mbar_arrive_expect_tx(q_full, kTile);
       tma_load_2d(sQ, &map_q, q_full, int32_t(hq * kD), int32_t(q_row0));
@@ -174,6 +182,11 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         tma_load_2d(sK + g * kTile + kSub, &map_k, k_full + 8 * g, int32_t(hkv * kD + 64), int32_t(k_row0 + j * kRows));
       }
       __syncwarp();
+    }
+  } else if (warp == 10) {
+    // ---------------- V loader (its ring frees later than K's: a warp of its own, so that K never waits behind V) ----------------
+    for (uint32_t j = 0; j < tiles; ++j) {
+      const uint32_t g = j & 1u, use = j >> 1;
       if (use > 0 && !mbar_wait_warp(v_empty + 8 * g, (use - 1u) & 1u, abort_flag, kStatusProducerTimeout, wait_limit)) break;
       if (elect_one()) {
         mbar_arrive_expect_tx(v_full + 8 * g, kTile);
@@ -187,10 +200,12 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     constexpr uint32_t idesc_qk = make_idesc_bf16(kRows, kRows);               // A and B K-major
     constexpr uint32_t idesc_pv = make_idesc_bf16(kRows, kD) | (1u << 16);     // B (V) MN-major
     bool ok = mbar_wait_warp(q_full, 0, abort_flag, kStatusMmaTimeout, wait_limit);
-    // S_g = Q K_j^T. The buffer is free: the group arrived on p_full for its previous tile after its last read of it.
+    // S_g = Q K_j^T, as soon as the group has taken its previous score row into registers (s_free) and K_j has landed:
+    // the scores of the group's next tile are computed while it is still working on the current one.
     auto issue_s = [&](uint32_t j) -> bool {
       const uint32_t g = j & 1u, use = j >> 1;
       if (!mbar_wait_warp(k_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) return false;
+      if (use > 0 && !mbar_wait_warp(s_free + 8 * g, (use - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) return false;
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
@@ -208,6 +223,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     if (ok && tiles > 1) ok = issue_s(1);
     for (uint32_t j = 0; j < tiles && ok; ++j) {
       const uint32_t g = j & 1u, use = j >> 1;
+      if (j + 2 < tiles && !issue_s(j + 2)) break;
       if (!mbar_wait_warp(p_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
       if (!mbar_wait_warp(v_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) break;
       tc_fence_after();
@@ -222,7 +238,6 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         tc_commit(v_empty + 8 * g);
       }
       __syncwarp();
-      if (j + 2 < tiles && !issue_s(j + 2)) break;  // the group's next scores, ready when it comes back
     }
   } else {
     // ---------------- softmax: two groups, one query row per thread ----------------
@@ -247,6 +262,8 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       tmem_ld_32x32b_x32(s_addr + 64u, s2);
       tmem_ld_32x32b_x32(s_addr + 96u, s3);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_free + 8 * g);  // the score buffer can take the group's next tile
       float mx = -INFINITY;
       auto row_max = [&](const uint32_t(&c)[32], uint32_t c4) {
         if (valid >= (c4 + 1u) * 32u) {
@@ -304,10 +321,11 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
       auto emit = [&](uint32_t(&c)[32], uint32_t c4) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = ex2(fmaf(__uint_as_float(c[i]), p.scale_log2, neg_m));
-          if (valid < kRows && c4 * 32u + uint32_t(i) >= valid) e = 0.0f;
-          c[i] = __float_as_uint(e);
+        for (int i = 0; i < 32; ++i) c[i] = __float_as_uint(ex2(fmaf(__uint_as_float(c[i]), p.scale_log2, neg_m)));
+        if (valid < (c4 + 1u) * 32u) {  // only the last tile of a ragged s_k: keys that do not exist weigh nothing
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c4 * 32u + uint32_t(i) >= valid) c[i] = 0u;
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -321,10 +339,10 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         for (uint32_t q = 0; q < 4; ++q) {  // 8 keys = one 16-byte chunk; chunk c of row r sits at position c ^ (r % 8)
           const uint32_t chunk = (c4 & 1u) * 4u + q;
           uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(c[q * 8 + 0]), __uint_as_float(c[q * 8 + 1]));
-          w.y = pack_bf16x2(__uint_as_float(c[q * 8 + 2]), __uint_as_float(c[q * 8 + 3]));
-          w.z = pack_bf16x2(__uint_as_float(c[q * 8 + 4]), __uint_as_float(c[q * 8 + 5]));
-          w.w = pack_bf16x2(__uint_as_float(c[q * 8 + 6]), __uint_as_float(c[q * 8 + 7]));
+          w.x = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 0]), __uint_as_float(c[q * 8 + 1]));
+          w.y = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 2]), __uint_as_float(c[q * 8 + 3]));
+          w.z = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 4]), __uint_as_float(c[q * 8 + 5]));
+          w.w = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 6]), __uint_as_float(c[q * 8 + 7]));
           *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7u)) << 4)) = w;
         }
       };
