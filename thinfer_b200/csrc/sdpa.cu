@@ -33,6 +33,7 @@
 
 #include "../../include/thinfer_nvfp4.h"
 #include "context.h"
+#include "epilogue.cuh"
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -96,6 +97,16 @@ __device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t
                : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -269,11 +280,11 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         if (valid >= (c4 + 1u) * 32u) {
           float a = -INFINITY, b = -INFINITY, d = -INFINITY, e = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            a = fmaxf(a, __uint_as_float(c[i]));
-            b = fmaxf(b, __uint_as_float(c[i + 1]));
-            d = fmaxf(d, __uint_as_float(c[i + 2]));
-            e = fmaxf(e, __uint_as_float(c[i + 3]));
+          for (int i = 0; i < 32; i += 8) {  // three-input maxima: 16 instructions for 32 values
+            a = max3(a, __uint_as_float(c[i]), __uint_as_float(c[i + 1]));
+            b = max3(b, __uint_as_float(c[i + 2]), __uint_as_float(c[i + 3]));
+            d = max3(d, __uint_as_float(c[i + 4]), __uint_as_float(c[i + 5]));
+            e = max3(e, __uint_as_float(c[i + 6]), __uint_as_float(c[i + 7]));
           }
           mx = fmaxf(mx, fmaxf(fmaxf(a, b), fmaxf(d, e)));
         } else {
@@ -318,10 +329,16 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       }
       // p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 into the swizzled K-major tile
       const float neg_m = -m_ref;
-      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+      const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(neg_m, neg_m);
+      uint64_t l01 = pack2(0.0f, 0.0f), l23 = l01;
       auto emit = [&](uint32_t(&c)[32], uint32_t c4) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) c[i] = __float_as_uint(ex2(fmaf(__uint_as_float(c[i]), p.scale_log2, neg_m)));
+        for (int i = 0; i < 32; i += 2) {  // the scale and the shift for two scores in one packed FMA
+          float x0, x1;
+          unpack2(fma2(pack2u(c[i], c[i + 1]), sc2, nm2), x0, x1);
+          c[i] = __float_as_uint(ex2(x0));
+          c[i + 1] = __float_as_uint(ex2(x1));
+        }
         if (valid < (c4 + 1u) * 32u) {  // only the last tile of a ragged s_k: keys that do not exist weigh nothing
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -329,10 +346,8 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         }
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          l0 += __uint_as_float(c[i]);
-          l1 += __uint_as_float(c[i + 1]);
-          l2 += __uint_as_float(c[i + 2]);
-          l3 += __uint_as_float(c[i + 3]);
+          l01 = add2(l01, pack2u(c[i], c[i + 1]));
+          l23 = add2(l23, pack2u(c[i + 2], c[i + 3]));
         }
         uint8_t* prow = p_gen + (c4 >> 1) * kSub + row * 128u;
 #pragma unroll
@@ -350,7 +365,12 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       emit(s1, 1);
       emit(s2, 2);
       emit(s3, 3);
-      l += (l0 + l1) + (l2 + l3);
+      {
+        float l0, l1, l2, l3;
+        unpack2(l01, l0, l1);
+        unpack2(l23, l2, l3);
+        l += (l0 + l1) + (l2 + l3);
+      }
       tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrival below
       fence_proxy_async();  // P was written by ordinary stores; the MMA reads it through the async proxy
       mbar_arrive(p_full + 8 * g);
