@@ -278,7 +278,18 @@ typedef struct tnf_sdpa_args {
   float scale;
   uint32_t mask_mode;
   tnf_buf q, k, v, out;
+  uint32_t flags;       /* TNF_SDPA_* */
+  float out_global;     /* TNF_SDPA_OUT_NVFP4: per-tensor scale of the quantised copy */
+  tnf_buf out_codes;    /* TNF_SDPA_OUT_NVFP4: codes of the output viewed as [b * s_q, h_q * 128] ... */
+  tnf_buf out_scales;   /* ... and its DEVICE-layout scales: the A operand of the out-projection (tnf_gemm_nvfp4) */
 } tnf_sdpa_args;
+enum {
+  /* The epilogue also quantises its bf16-rounded output to NVFP4 (the same bits tnf_quantize_act makes of `out`):
+   * the out-projection that follows (thinfer-models/src/qwen_image/dit.rs:655-670) needs no act_quant dispatch and
+   * never reads the bf16 tensor. */
+  TNF_SDPA_OUT_NVFP4 = 1u,
+  TNF_SDPA_NO_BF16_OUT = 2u /* with OUT_NVFP4: skip the bf16 store (out may have len 0) */
+};
 int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* args);
 
 /* ---- streaming residency (WeightResidency, thinfer-core/src/residency.rs) ------------ */

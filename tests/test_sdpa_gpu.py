@@ -79,3 +79,55 @@ def test_sdpa_argument_errors(backend):
     with pytest.raises(T.TnfError):
         sc.sdpa(buf, buf, buf, buf, 1, 4096, 4, 1, 1, 0.1)  # q does not fit its buffer
     backend.free(buf)
+
+
+@pytest.mark.parametrize("b,s_q,s_k,heads,keep_bf16", [(1, 300, 260, 2, True), (2, 200, 130, 3, True), (1, 257, 128, 4, False)])
+def test_sdpa_fused_output_quantisation(backend, b, s_q, s_k, heads, keep_bf16):
+    """TNF_SDPA_OUT_NVFP4: the attention epilogue also emits its output as the NVFP4 A operand of the out-projection.
+    The codes and scales are bit for bit what the activation quantiser makes of the kernel's own bf16 output (oracle
+    quantiser on those bits), padding of the scale layout is zero, and the operand feeds the GEMM directly."""
+    import thinfer_b200 as T
+    from thinfer_b200.backend import device_scales_bytes
+    from conftest import dev_scales_to_canonical
+
+    be = backend
+    d, rows, cols = 128, b * s_q, heads * 128
+    q, k, v = _inputs(b, s_q, s_k, heads, heads, 900 + s_q)
+    scale = float(1.0 / np.sqrt(128.0))
+    qb, kb, vb = be.upload(q), be.upload(k), be.upload(v)
+    out = be.allocate(rows * cols * 2)
+    codes = be.allocate(rows * cols // 2)
+    nsc = device_scales_bytes(rows, cols)
+    scales = be.allocate(nsc)
+    be.write_buffer(scales, np.full(nsc, 0x7F, np.uint8))  # canary: stale NaN scales must not survive in the padding
+    sc = be.scope()
+    sc.sdpa(qb, kb, vb, out, b, s_q, s_k, heads, heads, scale)  # plain run: the bf16 reference output
+    be.submit(30000)
+    plain = be.read_buffer(out, np.uint16).reshape(rows, cols)
+    g_out = O.global_scale(O.amax_bf16(plain))
+    be.write_buffer(out, np.zeros(rows * cols, np.uint16))
+    sc.sdpa(qb, kb, vb, out if keep_bf16 else None, b, s_q, s_k, heads, heads, scale, out_nvfp4=(codes, scales, g_out))
+    be.submit(30000)
+    if keep_bf16:
+        assert np.array_equal(be.read_buffer(out, np.uint16).reshape(rows, cols), plain)
+    else:
+        assert not be.read_buffer(out, np.uint16).any()  # the bf16 tensor was not touched
+    want_c, want_s = O.quantize_act(plain, g_out)
+    got_c = be.read_buffer(codes).reshape(rows, cols // 2)
+    dev = be.read_buffer(scales)
+    assert np.array_equal(got_c, want_c)
+    assert np.array_equal(dev_scales_to_canonical(dev, rows, cols), want_s)
+    assert np.array_equal(dev, O.scales_to_device_layout(want_s))  # every padding byte is zero
+    # and the out-projection runs on it: same bits as the linear that quantises the bf16 output itself
+    n = 264
+    w = (O.gaussian(n * cols, 0x7700) * np.float32(0.02)).reshape(n, cols)
+    W = T.Nvfp4Weight.from_dense(be, w)
+    y1, y2 = be.allocate(rows * n * 2), be.allocate(rows * n * 2)
+    pb = be.upload(plain)
+    sc.linear(pb, rows, W, g_out, y1)
+    sc.matmul(codes, scales, rows, W, g_out, y2)
+    be.submit(30000)
+    assert np.array_equal(be.read_buffer(y1, np.uint16), be.read_buffer(y2, np.uint16))
+    for buf in (qb, kb, vb, out, codes, scales, y1, y2, pb):
+        be.free(buf)
+    W.free(be)

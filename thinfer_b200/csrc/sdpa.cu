@@ -36,6 +36,7 @@
 #include "epilogue.cuh"
 #include "internal.h"
 #include "ptx.cuh"
+#include "quant_dev.cuh"
 
 namespace tnf {
 
@@ -49,11 +50,15 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSCol = 0;          // the groups' score buffers at columns 0 and 128
 constexpr uint32_t kOCol = 256;        // the groups' running outputs at columns 256 and 384
 constexpr float kLazy = 8.0f;          // the reference maximum moves only when the row maximum exceeds it by this much
-constexpr uint32_t kSmemBytes = 1024 + 7 * kTile + 256;  // Q | K x 2 | V x 2 | P x 2 | barriers
+constexpr uint32_t kSmemBytes = 1024 + 7 * kTile + 256 + 512;  // Q | K x 2 | V x 2 | P x 2 | barriers | quantiser table
 }  // namespace at
 
 struct SdpaParams {
-  uint16_t* out;
+  uint16_t* out;        // bf16 [b, s_q, h_q, 128], or null when only the NVFP4 copy is wanted
+  uint8_t* q_codes;     // NVFP4 copy of the output as an [b * s_q, h_q * 128] operand: codes ...
+  uint8_t* q_scales;    // ... and DEVICE-layout scales; null when not asked for
+  float q_global, q_inv_t;
+  uint32_t q_k_atoms;
   uint32_t* status;
   long long wait_limit;
   uint32_t s_q, s_k, h_q, h_kv;
@@ -137,6 +142,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   const uint32_t tmem_holder = sBar + 136;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
+  float* inv_d_lut = reinterpret_cast<float*>(smem_gen + (sBar + 256u - smem_base));  // the activation quantiser's table
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const uint32_t qt = blockIdx.x, hq = blockIdx.y, bb = blockIdx.z;
@@ -163,6 +169,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     prefetch_tensormap(&map_k);
     prefetch_tensormap(&map_v);
   }
+  if (p.q_codes) fill_inv_scale_lut(inv_d_lut, p.q_global, tid, kThreads);
   if (warp == 1) {
     tmem_alloc(tmem_holder, kTmemCols);
     tmem_relinquish();
@@ -390,9 +397,11 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       const float inv = 1.0f / (l * w_mine + (other_has ? other.y : 0.0f) * w_other);
       const float f_mine = w_mine * inv, f_other = w_other * inv;
       const bool store = qt * kRows + row < p.s_q;
-      uint16_t* dst = p.out + (uint64_t(q_row0 + row) * p.h_q + hq) * kD + g * 64u;  // group g writes columns 64g .. 64g+63
+      const uint64_t grow = uint64_t(q_row0) + row;  // row of the [b * s_q, h_q * 128] matrix
+      uint16_t* dst = p.out ? p.out + (grow * p.h_q + hq) * kD + g * 64u : nullptr;  // group g writes columns 64g .. 64g+63
       const uint32_t o_other = lane_addr + kOCol + (g ^ 1u) * 128u;
       uint32_t r2[32];
+      uint32_t sc4 = 0;  // the four block scales of this thread's 64 columns: one word of the scale layout
 #pragma unroll 1
       for (uint32_t c2 = 0; c2 < 2; ++c2) {
         const uint32_t col = g * 64u + c2 * 32u;
@@ -400,20 +409,37 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         if (other_has) tmem_ld_32x32b_x32(o_other + col, r2);
         tmem_ld_wait();
         if (store) {
+          uint32_t w[16];  // 32 columns as bf16 pairs
 #pragma unroll
-          for (uint32_t q = 0; q < 4; ++q) {
-            float o[8];
+          for (int i = 0; i < 16; ++i) {
+            const float o0 = (mine_has ? __uint_as_float(r[2 * i]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[2 * i]) * f_other : 0.0f);
+            const float o1 = (mine_has ? __uint_as_float(r[2 * i + 1]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[2 * i + 1]) * f_other : 0.0f);
+            w[i] = pack_bf16x2(o0, o1);
+          }
+          if (dst) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              o[i] = (mine_has ? __uint_as_float(r[q * 8 + i]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[q * 8 + i]) * f_other : 0.0f);
-            uint4 w;
-            w.x = pack_bf16x2(o[0], o[1]);
-            w.y = pack_bf16x2(o[2], o[3]);
-            w.z = pack_bf16x2(o[4], o[5]);
-            w.w = pack_bf16x2(o[6], o[7]);
-            *reinterpret_cast<uint4*>(dst + c2 * 32u + q * 8u) = w;
+            for (uint32_t q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(dst + c2 * 32u + q * 8u) = make_uint4(w[q * 4], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
+          }
+          if (p.q_codes) {
+            // the out-projection's activation quantiser, on the bf16-rounded values: two 16-column blocks per 32 columns,
+            // 8 code bytes each; the same bits tnf_quantize_act makes of the bf16 output
+            uint32_t codes[4];
+#pragma unroll
+            for (uint32_t blk = 0; blk < 2; ++blk) {
+              const uint32_t w8[8] = {w[blk * 8], w[blk * 8 + 1], w[blk * 8 + 2], w[blk * 8 + 3], w[blk * 8 + 4], w[blk * 8 + 5], w[blk * 8 + 6], w[blk * 8 + 7]};
+              const uint32_t sc = quant_block16_bf16(w8, inv_d_lut, p.q_inv_t, codes[blk * 2], codes[blk * 2 + 1]);
+              sc4 |= sc << (8u * (c2 * 2u + blk));
+            }
+            *reinterpret_cast<uint4*>(p.q_codes + grow * (uint64_t(p.h_q) * 64u) + hq * 64u + g * 32u + c2 * 16u) =
+                make_uint4(codes[0], codes[1], codes[2], codes[3]);
           }
         }
+      }
+      if (p.q_scales) {
+        // blocks hq*8 + g*4 .. +3 of the row: one 4-byte word of atom hq*2 + g (the launcher has cleared the padding)
+        if (store)
+          *reinterpret_cast<uint32_t*>(p.q_scales + ((grow >> 7) * p.q_k_atoms + hq * 2u + g) * 512u + (grow & 31u) * 16u + ((grow & 127u) >> 5) * 4u) = sc4;
       }
     }
   }
@@ -433,9 +459,11 @@ extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
     return TNF_ERR_INVALID_ARGUMENT;
   }
   if (a->b == 0 || a->s_q == 0 || a->s_k == 0 || a->h_q == 0 || a->h_kv == 0 || a->d != at::kD || a->h_q % a->h_kv != 0 ||
-      !(a->scale > 0.0f) || a->mask_mode != 0) {
+      !(a->scale > 0.0f) || a->mask_mode != 0 || (a->flags & ~uint32_t(TNF_SDPA_OUT_NVFP4 | TNF_SDPA_NO_BF16_OUT)) ||
+      ((a->flags & TNF_SDPA_NO_BF16_OUT) && !(a->flags & TNF_SDPA_OUT_NVFP4)) || ((a->flags & TNF_SDPA_OUT_NVFP4) && !(a->out_global > 0.0f))) {
     set_error("tnf_sdpa: b=%u s_q=%u s_k=%u h_q=%u h_kv=%u d=%u scale=%g mask_mode=%u (d must be 128, h_kv must divide h_q, "
-              "scale > 0, mask_mode 0)", a->b, a->s_q, a->s_k, a->h_q, a->h_kv, a->d, a->scale, a->mask_mode);
+              "scale > 0, mask_mode 0; flags 0x%x: NO_BF16_OUT needs OUT_NVFP4, which needs out_global > 0)", a->b, a->s_q, a->s_k, a->h_q, a->h_kv,
+              a->d, a->scale, a->mask_mode, a->flags);
     return TNF_ERR_INVALID_ARGUMENT;
   }
   const uint64_t q_rows = uint64_t(a->b) * a->s_q, k_rows = uint64_t(a->b) * a->s_k;
@@ -451,8 +479,18 @@ extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
   if (!k) return st;
   uint8_t* v = resolve(ctx, a->v, k_rows * kv_cols * 2, "v", &st);
   if (!v) return st;
-  uint8_t* out = resolve(ctx, a->out, q_rows * q_cols * 2, "out", &st);
-  if (!out) return st;
+  uint8_t* out = nullptr;
+  if (!(a->flags & TNF_SDPA_NO_BF16_OUT)) {
+    out = resolve(ctx, a->out, q_rows * q_cols * 2, "out", &st);
+    if (!out) return st;
+  }
+  uint8_t *q_codes = nullptr, *q_scales = nullptr;
+  if (a->flags & TNF_SDPA_OUT_NVFP4) {  // the out-projection's A operand: [b * s_q, h_q * 128] codes + DEVICE scales
+    q_codes = resolve(ctx, a->out_codes, q_rows * (q_cols / 2), "out_codes", &st);
+    if (!q_codes) return st;
+    q_scales = resolve(ctx, a->out_scales, sf_device_bytes(uint32_t(q_rows), uint32_t(q_cols)), "out_scales", &st);
+    if (!q_scales) return st;
+  }
   if (cudaSetDevice(ctx->device) != cudaSuccess) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   CUtensorMap mq, mk, mv;  // [rows, heads * 128] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
   if (!get_map(ctx, MapSpec{q, 2, q_cols, q_rows, q_cols * 2, 64, 128, 128}, &mq) ||
@@ -461,6 +499,25 @@ extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
     return TNF_ERR_INVALID_ARGUMENT;
   SdpaParams p{};
   p.out = reinterpret_cast<uint16_t*>(out);
+  if (q_codes) {
+    p.q_codes = q_codes;
+    p.q_scales = q_scales;
+    p.q_global = a->out_global;
+    p.q_inv_t = 1.0f / (6.0f * a->out_global);
+    p.q_k_atoms = sf_k_atoms(uint32_t(q_cols));
+    // benign (zero) scales where the kernel writes none: the K-padding atoms of every row block, and the rows of the
+    // last 128-row block past the matrix
+    const uint32_t used_atoms = uint32_t(q_cols / 64), row_blocks = uint32_t((q_rows + 127u) / 128u);
+    if (used_atoms < p.q_k_atoms) {
+      cudaError_t e = cudaMemset2DAsync(q_scales + uint64_t(used_atoms) * 512u, uint64_t(p.q_k_atoms) * 512u, 0,
+                                        uint64_t(p.q_k_atoms - used_atoms) * 512u, row_blocks, ctx->compute);
+      if (e != cudaSuccess) return cuda_fail(e, "out_scales padding clear");
+    }
+    if (q_rows % 128u != 0) {
+      cudaError_t e = cudaMemsetAsync(q_scales + uint64_t(row_blocks - 1u) * p.q_k_atoms * 512u, 0, uint64_t(p.q_k_atoms) * 512u, ctx->compute);
+      if (e != cudaSuccess) return cuda_fail(e, "out_scales last block clear");
+    }
+  }
   p.status = ctx->dwords;
   p.wait_limit = ctx->wait_limit_cycles;
   p.s_q = a->s_q; p.s_k = a->s_k; p.h_q = a->h_q; p.h_kv = a->h_kv;
