@@ -495,6 +495,69 @@ def time_sdpa(be, s_q, s_k, heads, iters=10, warmup=3, b=1):
             "tflops": flops / (ms * 1e-3) / 1e12, "finite": finite}
 
 
+def time_block_with_attention(be, m=4352, hidden=HIDDEN, ffn=12288, layers=8, rounds=3):
+    """The configs[1] block WITH the attention between its linears, every activation hand-over fused: quantise x ->
+    fused-QKV GEMM -> attention on column windows of its output, emitting the out-projection's NVFP4 operand ->
+    out-projection GEMM -> quantise h1 -> up + GELU emitting NVFP4 -> down. `layers` distinct weight sets (> L2) in
+    turn, `rounds` passes, CUDA events around each pass. RoPE and the QK norms of the reference's block (element-wise
+    passes over q and k) are not part of it."""
+    import torch
+    import thinfer_b200 as T
+    from thinfer_b200 import _lib as L
+    from thinfer_b200.backend import device_scales_bytes
+
+    dev = f"cuda:{be.device}"
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+    heads = hidden // 128
+    Ws = [[make_weight(be, T, L, gen, n, k) for n, k in ((3 * hidden, hidden), (hidden, hidden), (ffn, hidden), (hidden, ffn))]
+          for _ in range(layers)]
+    x = be.allocate(m * hidden * 2)
+    as_torch(be, x, torch.bfloat16, (m, hidden)).copy_(torch.randn(m, hidden, device=dev, generator=gen).to(torch.bfloat16))
+    qkv, h1, y = be.allocate(m * 3 * hidden * 2), be.allocate(m * hidden * 2), be.allocate(m * hidden * 2)
+    at_c, at_s = be.allocate(m * hidden // 2), be.allocate(device_scales_bytes(m, hidden))
+    up_c, up_s = be.allocate(m * ffn // 2), be.allocate(device_scales_bytes(m, ffn))
+    win = lambda i: L.Buf(qkv.id, i * hidden * 2, m * 3 * hidden * 2 - i * hidden * 2)
+    sc = be.scope()
+    g_x, g_at, g_up = 4.0 / 2688.0, 1.0 / 2688.0, 2.0 / 2688.0
+
+    def layer(W):
+        sc.linear(x, m, W[0], g_x, qkv)                                                  # quantise x + fused QKV
+        sc.sdpa(win(0), win(1), win(2), None, 1, m, m, heads, heads, 128 ** -0.5,        # attention -> NVFP4 operand
+                out_nvfp4=(at_c, at_s, g_at), q_ld=3 * hidden, kv_ld=3 * hidden)
+        sc.matmul(at_c, at_s, m, W[1], g_at, h1)                                         # out-projection
+        sc.linear(h1, m, W[2], g_x, None, act=1, out_nvfp4=(up_c, up_s, g_up))           # quantise h1 + up + GELU -> NVFP4
+        sc.matmul(up_c, up_s, m, W[3], g_up, y)                                          # down
+
+    stream = torch.cuda.ExternalStream(be.streams()[0], device=dev)
+    for W in Ws[:2]:
+        layer(W)
+    be.submit(60000)
+    ts = []
+    for _ in range(rounds):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for W in Ws:
+            layer(W)
+        e1.record(stream)
+        be.submit(60000)
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / layers)
+    finite = bool(torch.isfinite(as_torch(be, y, torch.bfloat16, (m, hidden)).float()).all())
+    for W4 in Ws:
+        for W in W4:
+            W.free(be)
+    for buf in (x, qkv, h1, y, at_c, at_s, up_c, up_s):
+        be.free(buf)
+    ms = float(np.median(ts))
+    lin_flops = 2.0 * m * hidden * (3 * hidden + hidden + 2 * ffn)
+    at_flops = 4.0 * heads * m * m * 128
+    return {"ms_per_layer": ms, "ms_per_60_layers": ms * 60, "linear_gflop": lin_flops / 1e9, "attention_gflop": at_flops / 1e9,
+            "tflops": (lin_flops + at_flops) / (ms * 1e-3) / 1e12, "launches_per_layer": 7, "finite": finite,
+            "note": "quantise x, fused-QKV GEMM, attention (column windows of the QKV output, NVFP4 out), out-projection, quantise h1, "
+                    "up + GELU (NVFP4 out), down; RoPE / QK norm not included"}
+
+
 def run_launch_workload(args):
     import torch
     import thinfer_b200 as T
@@ -588,6 +651,7 @@ def other_shapes(be):
     # the attention between the linears at the configs[1] joint sequence (4352 rows, 24 heads of 128): bf16 tensor cores
     at = time_sdpa(be, 4352, 4352, HIDDEN // 128, iters=5)
     out["c2_sdpa_4352x24x128"] = {"us": at["ms"] * 1e3, "tflops": at["tflops"], "bound": "tensor", "frac": at["tflops"] / peaks["bf16_sustained"]}
+    out["c2_block_with_attention_4352"] = time_block_with_attention(be)
     pair = time_ffn_pair(be, WAN_M, HIDDEN, WAN_FFN)
     out["c5_ffn_pair_26520_one_gpu"] = {"ms": pair["ms"], "tflops": pair["tflops"], "bound": "tensor", "frac": pair["tflops"] / fp4,
                                         "note": "the N > 1 lines split this work by output columns; this is their same-workload N = 1 time"}

@@ -282,6 +282,10 @@ typedef struct tnf_sdpa_args {
   float out_global;     /* TNF_SDPA_OUT_NVFP4: per-tensor scale of the quantised copy */
   tnf_buf out_codes;    /* TNF_SDPA_OUT_NVFP4: codes of the output viewed as [b * s_q, h_q * 128] ... */
   tnf_buf out_scales;   /* ... and its DEVICE-layout scales: the A operand of the out-projection (tnf_gemm_nvfp4) */
+  uint32_t q_ld, kv_ld; /* elements between consecutive rows of q, and of k and v; 0 = dense (h * d). With the fused-QKV
+                           output [rows, 3 * h * d] as the source, q / k / v are views at column 0, h*d, 2*h*d with
+                           ld = 3 * h * d: no split copies (the reference concatenates and splits with buffer copies,
+                           thinfer-models/src/qwen_image/dit.rs:605-616,648-654) */
 } tnf_sdpa_args;
 enum {
   /* The epilogue also quantises its bf16-rounded output to NVFP4 (the same bits tnf_quantize_act makes of `out`):

@@ -131,3 +131,28 @@ def test_sdpa_fused_output_quantisation(backend, b, s_q, s_k, heads, keep_bf16):
     for buf in (qb, kb, vb, out, codes, scales, y1, y2, pb):
         be.free(buf)
     W.free(be)
+
+
+def test_sdpa_reads_column_windows_of_the_fused_qkv_output(backend):
+    """q, k and v as column windows of one [rows, 3 * h * d] matrix (the fused-QKV linear's output) with a leading
+    dimension: the same bits as on separate dense tensors, without the reference's concatenate / split copies."""
+    from thinfer_b200 import _lib as L
+
+    be = backend
+    b, s, heads = 1, 330, 3
+    hd = heads * 128
+    q, k, v = _inputs(b, s, s, heads, heads, 4242)
+    scale = float(1.0 / np.sqrt(128.0))
+    dense = _run(be, q, k, v, scale)
+    qkv = np.concatenate([q.reshape(s, hd), k.reshape(s, hd), v.reshape(s, hd)], axis=1)  # [s, 3 * hd]
+    buf = be.upload(qkv)
+    out = be.allocate(s * hd * 2)
+    win = lambda i: L.Buf(buf.id, i * hd * 2, s * 3 * hd * 2 - i * hd * 2)
+    be.scope().sdpa(win(0), win(1), win(2), out, b, s, s, heads, heads, scale, q_ld=3 * hd, kv_ld=3 * hd)
+    be.submit(30000)
+    assert np.array_equal(be.read_buffer(out, np.uint16).reshape(b, s, heads, 128), dense)
+    import thinfer_b200 as T
+    with pytest.raises(T.InvalidArgument, match="must cover the heads"):
+        be.scope().sdpa(win(0), win(1), win(2), out, b, s, s, heads, heads, scale, q_ld=hd - 8, kv_ld=3 * hd)
+    be.free(buf)
+    be.free(out)

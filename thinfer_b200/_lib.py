@@ -47,7 +47,8 @@ SITE_QKV, SITE_QKV_SELF, SITE_PROJ, SITE_FFN_UP, SITE_FFN_DOWN = range(5)
 class SdpaArgs(C.Structure):
     _fields_ = [("b", C.c_uint32), ("s_q", C.c_uint32), ("s_k", C.c_uint32), ("h_q", C.c_uint32), ("h_kv", C.c_uint32),
                 ("d", C.c_uint32), ("scale", C.c_float), ("mask_mode", C.c_uint32), ("q", Buf), ("k", Buf), ("v", Buf), ("out", Buf),
-                ("flags", C.c_uint32), ("out_global", C.c_float), ("out_codes", Buf), ("out_scales", Buf)]
+                ("flags", C.c_uint32), ("out_global", C.c_float), ("out_codes", Buf), ("out_scales", Buf),
+                ("q_ld", C.c_uint32), ("kv_ld", C.c_uint32)]
 
 
 SDPA_OUT_NVFP4, SDPA_NO_BF16_OUT = 1, 2

@@ -366,16 +366,18 @@ class BatchScope:
         _check(self.be.lib.tnf_gemm_nvfp4(self.be._ctx, C.byref(args), a_codes, a_scales_device))
 
     def sdpa(self, q: Buf, k: Buf, v: Buf, out: Optional[Buf], b: int, s_q: int, s_k: int, h_q: int, h_kv: int, scale: float,
-             d: int = 128, out_nvfp4=None) -> None:
+             d: int = 128, out_nvfp4=None, q_ld: int = 0, kv_ld: int = 0) -> None:
         """Joint attention between the linears (``op_sdpa``, thinfer-core/src/ops/sdpa.rs): q / out bf16 [b, s_q, h_q, d],
         k / v bf16 [b, s_k, h_kv, d], no mask, d = 128. ``out_nvfp4=(codes, scales_device, g)`` also emits the output
-        quantised to NVFP4 as the [b*s_q, h_q*d] operand of the out-projection; ``out=None`` then skips the bf16 store."""
+        quantised to NVFP4 as the [b*s_q, h_q*d] operand of the out-projection; ``out=None`` then skips the bf16 store.
+        ``q_ld`` / ``kv_ld`` (elements, 0 = dense) let q, k and v be column windows of a wider matrix, e.g. of the fused-QKV
+        linear's output."""
         flags, none = 0, Buf(0, 0, 0)
         oc, os_, og = none, none, 0.0
         if out_nvfp4 is not None:
             oc, os_, og = out_nvfp4
             flags = L.SDPA_OUT_NVFP4 | (L.SDPA_NO_BF16_OUT if out is None else 0)
-        args = L.SdpaArgs(b, s_q, s_k, h_q, h_kv, d, scale, 0, q, k, v, out if out is not None else none, flags, og, oc, os_)
+        args = L.SdpaArgs(b, s_q, s_k, h_q, h_kv, d, scale, 0, q, k, v, out if out is not None else none, flags, og, oc, os_, q_ld, kv_ld)
         _check(self.be.lib.tnf_sdpa(self.be._ctx, C.byref(args)))
 
     def submit(self, timeout_ms: int = 0) -> None:

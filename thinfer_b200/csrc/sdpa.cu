@@ -473,12 +473,23 @@ extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
   }
   int32_t st = TNF_OK;
   const uint64_t q_cols = uint64_t(a->h_q) * at::kD, kv_cols = uint64_t(a->h_kv) * at::kD;
-  uint8_t* q = resolve(ctx, a->q, q_rows * q_cols * 2, "q", &st);
+  // leading dimensions in elements: q, k and v may be column windows of one wider matrix (the fused QKV output)
+  const uint64_t q_ld = a->q_ld ? a->q_ld : q_cols, kv_ld = a->kv_ld ? a->kv_ld : kv_cols;
+  if (q_ld < q_cols || kv_ld < kv_cols || q_ld % 8 != 0 || kv_ld % 8 != 0) {
+    set_error("tnf_sdpa: q_ld %llu / kv_ld %llu must cover the heads (%llu / %llu elements) and be multiples of 8",
+              (unsigned long long)q_ld, (unsigned long long)kv_ld, (unsigned long long)q_cols, (unsigned long long)kv_cols);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  uint8_t* q = resolve(ctx, a->q, ((q_rows - 1) * q_ld + q_cols) * 2, "q", &st);
   if (!q) return st;
-  uint8_t* k = resolve(ctx, a->k, k_rows * kv_cols * 2, "k", &st);
+  uint8_t* k = resolve(ctx, a->k, ((k_rows - 1) * kv_ld + kv_cols) * 2, "k", &st);
   if (!k) return st;
-  uint8_t* v = resolve(ctx, a->v, k_rows * kv_cols * 2, "v", &st);
+  uint8_t* v = resolve(ctx, a->v, ((k_rows - 1) * kv_ld + kv_cols) * 2, "v", &st);
   if (!v) return st;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) {
+    set_error("tnf_sdpa: q, k and v must start on 16-byte boundaries");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
   uint8_t* out = nullptr;
   if (!(a->flags & TNF_SDPA_NO_BF16_OUT)) {
     out = resolve(ctx, a->out, q_rows * q_cols * 2, "out", &st);
@@ -493,9 +504,9 @@ extern "C" int32_t tnf_sdpa(tnf_ctx* ctx, const tnf_sdpa_args* a) {
   }
   if (cudaSetDevice(ctx->device) != cudaSuccess) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   CUtensorMap mq, mk, mv;  // [rows, heads * 128] bf16, boxes of 64 columns x 128 rows, 128-byte swizzle
-  if (!get_map(ctx, MapSpec{q, 2, q_cols, q_rows, q_cols * 2, 64, 128, 128}, &mq) ||
-      !get_map(ctx, MapSpec{k, 2, kv_cols, k_rows, kv_cols * 2, 64, 128, 128}, &mk) ||
-      !get_map(ctx, MapSpec{v, 2, kv_cols, k_rows, kv_cols * 2, 64, 128, 128}, &mv))
+  if (!get_map(ctx, MapSpec{q, 2, q_cols, q_rows, q_ld * 2, 64, 128, 128}, &mq) ||
+      !get_map(ctx, MapSpec{k, 2, kv_cols, k_rows, kv_ld * 2, 64, 128, 128}, &mk) ||
+      !get_map(ctx, MapSpec{v, 2, kv_cols, k_rows, kv_ld * 2, 64, 128, 128}, &mv))
     return TNF_ERR_INVALID_ARGUMENT;
   SdpaParams p{};
   p.out = reinterpret_cast<uint16_t*>(out);
