@@ -3,23 +3,30 @@
 // out = softmax(Q K^T * scale) V per (batch, head), bf16 in and out, f32 softmax statistics and accumulation.
 //
 // One CTA per (128 query rows, head, batch); flash-attention tiling over 128-key tiles, both products on the tensor
-// cores (tcgen05.mma kind::f16, accumulators in TMEM). The key tiles are dealt alternately to two independent
-// softmax groups, each with its own score buffer S_g, probability tile P_g and running output O_g (4 x 128 TMEM
-// columns), so that one group's exponentials run under the other's TMEM traffic and waits; the two partial results
-// are merged at the end by their softmax statistics.
+// cores (tcgen05.mma kind::f16); scores, probabilities and the running output live in TMEM:
+//   columns   0-255  S_0, S_1: score buffers (f32) of the two softmax groups
+//           256-383  P_0, P_1: their probability buffers (bf16 pairs, 64 columns each): the A operand of the second
+//                    product is read from tensor memory, so P never touches shared memory
+//           384-511  O: the one running output (f32) both groups' products accumulate into
 //   warps 0, 10 TMA: the Q tile once, then K tiles (warp 0) and V tiles (warp 10) into two-stage rings ([128 rows x
 //               64 bf16] boxes with 128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte
 //               column window);
-//   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) and
-//               O_g += P_g V_j with V as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
-//               a group's next scores are issued as soon as it has taken the current score row into registers;
-//   warps 2-9   two groups of four warps, one query row per thread (TMEM lane = row). The thread reads its whole
-//               score row into registers (four loads in flight, one wait) and finds the row maximum; the reference
-//               maximum m only moves when the row maximum exceeds it by more than 8 (in the exp2 domain:
-//               probabilities stay below 256), and only then is O_g rescaled (tcgen05.ld / mul / tcgen05.st) once
-//               the group's previous product has completed; then p = exp2(s * scale * log2e - m), summed in f32,
-//               goes as bf16 into shared memory in the swizzled K-major layout the second product reads. At the end the groups exchange (m, l) through
-//               shared memory and each writes half of the columns of (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1).
+//   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) as soon as the group
+//               has taken its previous score row into registers, and O += P_g V_j in tile order, with P from TMEM and V
+//               as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
+//   warps 2-9   two softmax groups of four warps, one query row per thread (TMEM lane = row); the key tiles alternate
+//               between them, so that one group's exponentials run under the other's TMEM traffic and waits. The
+//               reference maximum m of a row is ONE chain through all tiles: the thread of tile j takes m_{j-1} from
+//               the other group's thread of the same row (shared memory, an mbarrier per lane quarter and tile
+//               parity), decides m_j -- it only moves when the tile's row maximum exceeds it by more than 8 in the
+//               exp2 domain, so probabilities stay below 256 -- and publishes it before its expensive part. Only when m
+//               moves is O rescaled (tcgen05.ld / mul / tcgen05.st by the thread that moved it, once the previous
+//               product has completed); both threads of the row scale their partial sums. Then
+//               p = exp2(s * scale * log2e - m), summed in f32, goes as bf16 pairs into P_g with tcgen05.st. At the
+//               end the two partial sums are joined and each group writes half of the columns of O / l.
+// Why this shape: a 128 x 128 x 16 MMA with both operands in shared memory reads 8 KB in its 64 cycles, all of an SM's
+// 128 B/clk, and the TMA's writes of K and V come on top. With P in tensor memory a key tile moves 160 KB through shared
+// memory instead of 224 KB; with one O instead of one per group there are TMEM columns left for P.
 // The reference's kernel is the same recurrence one key at a time in f32 (m' = max(m, s); o = o * exp(m - m') +
 // exp(s - m') v; l likewise); here it runs a tile at a time, p is rounded to bf16 for the tensor cores, and exp is
 // exp2 with the scale folded in: the result agrees with the f32 recurrence to bf16 rounding (tests: relative
@@ -48,9 +55,10 @@ constexpr uint32_t kSub = 128 * 128;   // one [128 rows x 64 bf16] swizzled box:
 constexpr uint32_t kTile = 2 * kSub;   // [128 x 128] bf16
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSCol = 0;          // the groups' score buffers at columns 0 and 128
-constexpr uint32_t kOCol = 256;        // the groups' running outputs at columns 256 and 384
+constexpr uint32_t kPCol = 256;        // the groups' probability buffers (bf16 pairs) at columns 256 and 320
+constexpr uint32_t kOCol = 384;        // the running output
 constexpr float kLazy = 8.0f;          // the reference maximum moves only when the row maximum exceeds it by this much
-constexpr uint32_t kSmemBytes = 1024 + 7 * kTile + 256 + 512;  // Q | K x 2 | V x 2 | P x 2 | barriers | quantiser table
+constexpr uint32_t kSmemBytes = 1024 + 5 * kTile + 512 + 512 + 2048;  // Q | K x 2 | V x 2 | barriers | quantiser table | row statistics
 }  // namespace at
 
 struct SdpaParams {
@@ -101,6 +109,22 @@ __device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t
                "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (bf16, two K elements per 32-bit column, lane = row) comes from tensor memory.
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -136,13 +160,16 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sP = sV + 2 * kTile, sBar = sP + 2 * kTile;
+  const uint32_t sQ = smem_base, sK = sQ + kTile, sV = sK + 2 * kTile, sBar = sV + 2 * kTile;
   const uint32_t q_full = sBar, k_full = sBar + 8, k_empty = sBar + 24, v_full = sBar + 40, v_empty = sBar + 56;
   const uint32_t s_full = sBar + 72, p_full = sBar + 88, pv_done = sBar + 104, s_free = sBar + 120;
-  const uint32_t tmem_holder = sBar + 136;
+  const uint32_t chain_bar = sBar + 136;  // [4 lane quarters][2 tile parities]: "m of tile j is published", 32 arrivals
+  const uint32_t tmem_holder = sBar + 200;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
-  float* inv_d_lut = reinterpret_cast<float*>(smem_gen + (sBar + 256u - smem_base));  // the activation quantiser's table
+  float* inv_d_lut = reinterpret_cast<float*>(smem_gen + (sBar + 512u - smem_base));  // the activation quantiser's table
+  float* m_chain = reinterpret_cast<float*>(smem_gen + (sBar + 1024u - smem_base));   // [2 tile parities][128 rows]
+  float* l_part = m_chain + 256;                                                       // [2 groups][128 rows]
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const uint32_t qt = blockIdx.x, hq = blockIdx.y, bb = blockIdx.z;
@@ -163,6 +190,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       mbar_init(pv_done + 8 * i, 1);
       mbar_init(s_free + 8 * i, 128);
     }
+    for (uint32_t i = 0; i < 8; ++i) mbar_init(chain_bar + 8 * i, 32);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -247,11 +275,9 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
-        for (uint32_t kk = 0; kk < 8; ++kk) {  // 16 keys each: P columns 16kk.., V rows 16kk..
-          const uint32_t poff = (kk >> 2) * kSub + (kk & 3u) * 32u;
-          tc_mma_bf16(tmem_base + kOCol + g * 128u, make_desc_sw128(sP + g * kTile + poff),
-                      make_desc_mn_sw128(sV + g * kTile + kk * 2048u, kSub), idesc_pv, (use | kk) != 0u);
-        }
+        for (uint32_t kk = 0; kk < 8; ++kk)  // 16 keys each: P's packed columns 8kk.. in TMEM, V rows 16kk..
+          tc_mma_bf16_ts(tmem_base + kOCol, tmem_base + kPCol + g * 64u + kk * 8u, make_desc_mn_sw128(sV + g * kTile + kk * 2048u, kSub),
+                         idesc_pv, (j | kk) != 0u);
         tc_commit(pv_done + 8 * g);
         tc_commit(v_empty + 8 * g);
       }
@@ -261,12 +287,21 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     // ---------------- softmax: two groups, one query row per thread ----------------
     const uint32_t g = (warp - 2u) >> 2, quarter = warp & 3u, row = quarter * 32u + lane;
     const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    const uint32_t s_addr = lane_addr + kSCol + g * 128u, o_addr = lane_addr + kOCol + g * 128u;
-    uint8_t* p_gen = smem_gen + (sP + g * kTile - smem_base);
-    float m_ref = -INFINITY, l = 0.0f;
+    const uint32_t s_addr = lane_addr + kSCol + g * 128u, p_addr = lane_addr + kPCol + g * 64u, o_addr = lane_addr + kOCol;
+    float m_known = -INFINITY, l = 0.0f;  // l is this group's partial row sum, relative to m_known
     bool ok = true;
-    uint32_t r[32], s0[32], s1[32], s2[32], s3[32];
+    uint32_t s0[32], s1[32], s2[32], s3[32];
     uint32_t use = 0;
+    // m_{j}: published by the thread of tile j for the thread of tile j + 1 (the same row, the other group)
+    auto chain_wait = [&](uint32_t j) -> bool {
+      return mbar_wait_warp(chain_bar + 8 * (quarter * 2u + (j & 1u)), (j >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
+    };
+    auto adopt = [&](float m_new) {  // bring the partial sum to a new reference maximum
+      if (m_new != m_known) {
+        l *= ex2(m_known - m_new);  // m_known = -inf only while l = 0: ex2(-inf) = 0
+        m_known = m_new;
+      }
+    };
     for (uint32_t j = g; j < tiles && ok; j += 2, ++use) {
       const uint32_t valid = min(kRows, p.s_k - j * kRows);  // keys of this tile that exist
       if (!mbar_wait_warp(s_full + 8 * g, use & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
@@ -305,37 +340,52 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       row_max(s2, 2);
       row_max(s3, 3);
       mx *= p.scale_log2;  // scale > 0: the maximum commutes with it
+      // the chain: take m_{j-1}, decide m_j, publish it at once (the other group's next tile waits for nothing else)
       float alpha = 1.0f;
-      if (use == 0) {
-        m_ref = mx;
-      } else if (mx > m_ref + kLazy) {
-        alpha = ex2(m_ref - mx);
-        m_ref = mx;
+      if (j == 0) {
+        m_known = mx;
+      } else {
+        if (!chain_wait(j - 1u)) {
+          ok = false;
+          break;
+        }
+        adopt(m_chain[((j - 1u) & 1u) * 128u + row]);
+        if (mx > m_known + kLazy) {
+          alpha = ex2(m_known - mx);
+          l *= alpha;
+          m_known = mx;
+        }
       }
-      if (use > 0) {
-        // the group's previous product must have completed before O_g is rescaled and before P_g is overwritten
-        if (!mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+      m_chain[(j & 1u) * 128u + row] = m_known;
+      mbar_arrive(chain_bar + 8 * (quarter * 2u + (j & 1u)));
+      if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+        // rare (the maximum jumped by more than 2^8): O is rescaled once every earlier product has completed (the pipe
+        // runs them in order, so tile j-1's completion covers them all). This tile's product is issued only after this
+        // thread's arrival below, and the next tile's after it.
+        const uint32_t pj = j - 1u;
+        if (!mbar_wait_warp(pv_done + 8 * (pj & 1u), (pj >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (__any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
-          // rare (the maximum jumped by more than 2^8), and the score row is live in registers: small pieces
-          uint32_t o8[8];
+        uint32_t o8[8];
 #pragma unroll 1
-          for (uint32_t c = 0; c < kD; c += 8u) {
-            tmem_ld_32x32b_x8(o_addr + c, o8);
-            tmem_ld_wait();
+        for (uint32_t c = 0; c < kD; c += 8u) {
+          tmem_ld_32x32b_x8(o_addr + c, o8);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o8[i] = __float_as_uint(__uint_as_float(o8[i]) * alpha);
-            tmem_st_32x32b_x8(o_addr + c, o8);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 8; ++i) o8[i] = __float_as_uint(__uint_as_float(o8[i]) * alpha);
+          tmem_st_32x32b_x8(o_addr + c, o8);
         }
-        l *= alpha;
       }
-      // p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 into the swizzled K-major tile
-      const float neg_m = -m_ref;
+      if (use > 0) {  // the group's probability buffer was read by its previous product
+        if (!mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+          ok = false;
+          break;
+        }
+      }
+      // p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 pairs into the group's probability buffer
+      const float neg_m = -m_known;
       const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(neg_m, neg_m);
       uint64_t l01 = pack2(0.0f, 0.0f), l23 = l01;
       auto emit = [&](uint32_t(&c)[32], uint32_t c4) {
@@ -356,17 +406,10 @@ __global__ void __launch_bounds__(at::kThreads, 1)
           l01 = add2(l01, pack2u(c[i], c[i + 1]));
           l23 = add2(l23, pack2u(c[i + 2], c[i + 3]));
         }
-        uint8_t* prow = p_gen + (c4 >> 1) * kSub + row * 128u;
+        uint32_t w[16];  // two probabilities per 32-bit column, key 2i in the low half
 #pragma unroll
-        for (uint32_t q = 0; q < 4; ++q) {  // 8 keys = one 16-byte chunk; chunk c of row r sits at position c ^ (r % 8)
-          const uint32_t chunk = (c4 & 1u) * 4u + q;
-          uint4 w;
-          w.x = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 0]), __uint_as_float(c[q * 8 + 1]));
-          w.y = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 2]), __uint_as_float(c[q * 8 + 3]));
-          w.z = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 4]), __uint_as_float(c[q * 8 + 5]));
-          w.w = pack_bf16x2_pos(__uint_as_float(c[q * 8 + 6]), __uint_as_float(c[q * 8 + 7]));
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7u)) << 4)) = w;
-        }
+        for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2_pos(__uint_as_float(c[2 * i]), __uint_as_float(c[2 * i + 1]));
+        tmem_st_32x32b_x16(p_addr + c4 * 16u, w);
       };
       emit(s0, 0);
       emit(s1, 1);
@@ -378,44 +421,34 @@ __global__ void __launch_bounds__(at::kThreads, 1)
         unpack2(l23, l2, l3);
         l += (l0 + l1) + (l2 + l3);
       }
-      tc_fence_before();    // this thread's TMEM reads and writes are ordered before the arrival below
-      fence_proxy_async();  // P was written by ordinary stores; the MMA reads it through the async proxy
+      tmem_st_wait();
+      tc_fence_before();  // this thread's TMEM reads and writes are ordered before the arrival below
       mbar_arrive(p_full + 8 * g);
     }
-    // ---------------- merge the two groups: (O_0 w_0 + O_1 w_1) / (l_0 w_0 + l_1 w_1) -> global ----------------
-    if (ok && use > 0) ok = mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
-    // the group's probability tile is free now: its first KB carries (m, l) per row to the other group
-    reinterpret_cast<float2*>(p_gen)[row] = make_float2(m_ref, l);
+    // ---------------- O / (l_0 + l_1) -> global: each group half of the columns ----------------
+    const uint32_t last = tiles - 1u;
+    if (ok && (last & 1u) != g) {  // the last tile was the other group's: its m is the final one
+      ok = chain_wait(last);
+      if (ok) adopt(m_chain[(last & 1u) * 128u + row]);
+    }
+    if (ok) ok = mbar_wait_warp(pv_done + 8 * (last & 1u), (last >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
+    l_part[g * 128u + row] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps; every one of them gets here, whatever happened
     tc_fence_after();
-    const float2 other = reinterpret_cast<const float2*>(smem_gen + (sP + (g ^ 1u) * kTile - smem_base))[row];
-    const bool other_has = g == 1u || tiles > 1u;  // group 1 has no tile when there is a single one
     if (ok && __all_sync(0xFFFFFFFFu, *abort_flag == 0u)) {
-      const bool mine_has = use > 0;
-      const float m = fmaxf(mine_has ? m_ref : -INFINITY, other_has ? other.x : -INFINITY);
-      const float w_mine = mine_has ? ex2(m_ref - m) : 0.0f, w_other = other_has ? ex2(other.x - m) : 0.0f;
-      const float inv = 1.0f / (l * w_mine + (other_has ? other.y : 0.0f) * w_other);
-      const float f_mine = w_mine * inv, f_other = w_other * inv;
+      const float inv = 1.0f / (l + l_part[(g ^ 1u) * 128u + row]);
       const bool store = qt * kRows + row < p.s_q;
       const uint64_t grow = uint64_t(q_row0) + row;  // row of the [b * s_q, h_q * 128] matrix
       uint16_t* dst = p.out ? p.out + (grow * p.h_q + hq) * kD + g * 64u : nullptr;  // group g writes columns 64g .. 64g+63
-      const uint32_t o_other = lane_addr + kOCol + (g ^ 1u) * 128u;
-      uint32_t r2[32];
       uint32_t sc4 = 0;  // the four block scales of this thread's 64 columns: one word of the scale layout
 #pragma unroll 1
       for (uint32_t c2 = 0; c2 < 2; ++c2) {
-        const uint32_t col = g * 64u + c2 * 32u;
-        if (mine_has) tmem_ld_32x32b_x32(o_addr + col, r);
-        if (other_has) tmem_ld_32x32b_x32(o_other + col, r2);
+        tmem_ld_32x32b_x32(o_addr + g * 64u + c2 * 32u, s0);
         tmem_ld_wait();
         if (store) {
           uint32_t w[16];  // 32 columns as bf16 pairs
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float o0 = (mine_has ? __uint_as_float(r[2 * i]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[2 * i]) * f_other : 0.0f);
-            const float o1 = (mine_has ? __uint_as_float(r[2 * i + 1]) * f_mine : 0.0f) + (other_has ? __uint_as_float(r2[2 * i + 1]) * f_other : 0.0f);
-            w[i] = pack_bf16x2(o0, o1);
-          }
+          for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(__uint_as_float(s0[2 * i]) * inv, __uint_as_float(s0[2 * i + 1]) * inv);
           if (dst) {
 #pragma unroll
             for (uint32_t q = 0; q < 4; ++q)
@@ -436,10 +469,9 @@ __global__ void __launch_bounds__(at::kThreads, 1)
           }
         }
       }
-      if (p.q_scales) {
+      if (p.q_scales && store) {
         // blocks hq*8 + g*4 .. +3 of the row: one 4-byte word of atom hq*2 + g (the launcher has cleared the padding)
-        if (store)
-          *reinterpret_cast<uint32_t*>(p.q_scales + ((grow >> 7) * p.q_k_atoms + hq * 2u + g) * 512u + (grow & 31u) * 16u + ((grow & 127u) >> 5) * 4u) = sc4;
+        *reinterpret_cast<uint32_t*>(p.q_scales + ((grow >> 7) * p.q_k_atoms + hq * 2u + g) * 512u + (grow & 31u) * 16u + ((grow & 127u) >> 5) * 4u) = sc4;
       }
     }
   }
