@@ -48,10 +48,12 @@ def test_sdpa_matches_reference_recurrence(backend, b, s_q, s_k, h_q, h_kv):
     assert rel_fro(O.bf16_to_f32(got), O.bf16_to_f32(want)) <= TOL
 
 
-def test_sdpa_peaked_rows_rescale_the_running_output(backend):
+@pytest.mark.parametrize("s_q,s_k,heads", [(256, 1024, 2), (128, 2176, 1), (384, 1536, 3)])
+def test_sdpa_peaked_rows_rescale_the_running_output(backend, s_q, s_k, heads):
     """Scores with a large spread: the row maximum keeps growing from tile to tile, so the running output in TMEM is
-    rescaled many times, and most probabilities underflow to zero."""
-    q, k, v = _inputs(1, 256, 1024, 2, 2, 77, spread=6.0)
+    rescaled many times (by threads of both softmax groups, each waiting for the other's product), and most
+    probabilities underflow to zero. Eight and more key tiles: every barrier goes through several phases."""
+    q, k, v = _inputs(1, s_q, s_k, heads, heads, 77, spread=6.0)
     scale = 1.0 / np.sqrt(128.0)
     got = _run(backend, q, k, v, float(scale))
     want = O.ref_sdpa(q, k, v, float(scale))

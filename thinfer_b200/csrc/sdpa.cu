@@ -358,6 +358,15 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       }
       m_chain[(j & 1u) * 128u + row] = m_known;
       mbar_arrive(chain_bar + 8 * (quarter * 2u + (j & 1u)));
+      // A parity wait is only meaningful on a barrier that is at most one phase behind the awaited one. The group's own
+      // previous product (tile j-2) is therefore awaited first -- it also frees the probability buffer --: its completion
+      // implies tile j-3's, which puts the other group's barrier one phase before tile j-1's, awaited below.
+      if (use > 0) {
+        if (!mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
+          ok = false;
+          break;
+        }
+      }
       if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
         // rare (the maximum jumped by more than 2^8): O is rescaled once every earlier product has completed (the pipe
         // runs them in order, so tile j-1's completion covers them all). This tile's product is issued only after this
@@ -376,12 +385,6 @@ __global__ void __launch_bounds__(at::kThreads, 1)
 #pragma unroll
           for (int i = 0; i < 8; ++i) o8[i] = __float_as_uint(__uint_as_float(o8[i]) * alpha);
           tmem_st_32x32b_x8(o_addr + c, o8);
-        }
-      }
-      if (use > 0) {  // the group's probability buffer was read by its previous product
-        if (!mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
-          ok = false;
-          break;
         }
       }
       // p = exp2(s * scale_log2 - m), row sum in f32, P as bf16 pairs into the group's probability buffer
@@ -431,7 +434,10 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       ok = chain_wait(last);
       if (ok) adopt(m_chain[(last & 1u) * 128u + row]);
     }
-    if (ok) ok = mbar_wait_warp(pv_done + 8 * (last & 1u), (last >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
+    // the group's own last product first (one phase ahead of what it has seen), then the very last one if it is the
+    // other group's: the same rule about parity waits
+    if (ok && use > 0) ok = mbar_wait_warp(pv_done + 8 * g, (use - 1u) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
+    if (ok && (last & 1u) != g) ok = mbar_wait_warp(pv_done + 8 * (last & 1u), (last >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
     l_part[g * 128u + row] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps; every one of them gets here, whatever happened
     tc_fence_after();
