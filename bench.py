@@ -900,6 +900,9 @@ def run_single_gpu(args):
         be2 = T.Backend(0)
         line["shapes"] = other_shapes(be2)
         be2.close()
+        # the same 60 layers with the attention between their linears and every hand-over fused (a different, fuller
+        # workload than the headline's, which is the linears alone as the metric defines it)
+        line["ms_per_dit_step_with_attention"] = line["shapes"]["c2_block_with_attention_4352"]["ms_per_60_layers"]
         st_args = argparse.Namespace(**vars(args))
         st_args.steps, st_args.warmup = max(args.steps, 5), 2
         st = run_stream_bench(st_args, as_dict=True)
