@@ -32,6 +32,9 @@ def test_struct_layouts_match_header():
     assert ctypes.sizeof(Buf) == 24
     assert ctypes.sizeof(LinearArgs) == 5 * 4 + 4 + 7 * 24 + 6 * 4 + 3 * 24  # 5 scalars (+pad), 7 views, 6 words, 3 views
     assert ctypes.sizeof(StackLinear) == 24
+    from thinfer_b200._lib import Reader, SdpaArgs
+    assert ctypes.sizeof(SdpaArgs) == 8 * 4 + 4 * 24 + 2 * 4 + 2 * 24 + 2 * 4  # 8 words, 4 views, 2 words, 2 views, 2 words
+    assert ctypes.sizeof(Reader) == 5 * 8
 
 
 def test_no_device_fails_loudly():
@@ -63,10 +66,10 @@ def test_rust_bindings_declare_every_header_symbol():
     text = open(os.path.join(ROOT, "rust", "thinfer-native-cuda", "src", "ffi.rs")).read()
     rust = sorted(set(re.findall(r"pub fn (tnf_[a-z0-9_]+)\s*\(", text)))
     assert rust == declared_symbols()
-    from thinfer_b200._lib import DenseActSites, LinearArgs, NormQuantArgs, StackLinear
+    from thinfer_b200._lib import DenseActSites, LinearArgs, NormQuantArgs, Reader, SdpaArgs, StackLinear
 
     for rust_name, ct in (("TnfLinearArgs", LinearArgs), ("TnfNormQuantArgs", NormQuantArgs), ("TnfStackLinear", StackLinear),
-                          ("TnfDenseActSites", DenseActSites)):
+                          ("TnfDenseActSites", DenseActSites), ("TnfSdpaArgs", SdpaArgs), ("TnfReader", Reader)):
         body = re.search(r"pub struct %s \{(.*?)\n?\}" % rust_name, text, flags=re.S).group(1)
         fields = re.findall(r"pub (\w+):", body)
         assert fields == [f[0] for f in ct._fields_], rust_name
