@@ -54,8 +54,10 @@ constexpr uint32_t kRows = 128;        // query rows per CTA, keys per tile
 constexpr uint32_t kSub = 128 * 128;   // one [128 rows x 64 bf16] swizzled box: 16 KB
 constexpr uint32_t kTile = 2 * kSub;   // [128 x 128] bf16
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSCol = 0;          // the groups' score buffers at columns 0 and 128
-constexpr uint32_t kPCol = 256;        // the groups' probability buffers (bf16 pairs) at columns 256 and 320
+constexpr uint32_t kSCol = 0;          // the score buffer (f32, 128 columns): a thread takes its row to registers at once, so one
+                                       // buffer serves both groups in turn
+constexpr uint32_t kPCol = 128;        // the groups' probability buffers (bf16 pairs) at columns 128 and 192
+constexpr uint32_t kQCol = 256;        // the Q tile (bf16 pairs, 64 columns): the A operand of every score MMA
 constexpr uint32_t kOCol = 384;        // the running output
 constexpr float kLazy = 8.0f;          // the reference maximum moves only when the row maximum exceeds it by this much
 constexpr uint32_t kSmemBytes = 1024 + 5 * kTile + 512 + 512 + 2048;  // Q | K x 2 | V x 2 | barriers | quantiser table | row statistics
@@ -164,7 +166,8 @@ __global__ void __launch_bounds__(at::kThreads, 1)
   const uint32_t q_full = sBar, k_full = sBar + 8, k_empty = sBar + 24, v_full = sBar + 40, v_empty = sBar + 56;
   const uint32_t s_full = sBar + 72, p_full = sBar + 88, pv_done = sBar + 104, s_free = sBar + 120;
   const uint32_t chain_bar = sBar + 136;  // [4 lane quarters][2 tile parities]: "m of tile j is published", 32 arrivals
-  const uint32_t tmem_holder = sBar + 200;
+  const uint32_t q_ready = sBar + 200;    // Q has been copied to tensor memory (128 arrivals)
+  const uint32_t tmem_holder = sBar + 208;
   volatile uint32_t* tmem_holder_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder - smem_base));
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_holder + 8u - smem_base));
   float* inv_d_lut = reinterpret_cast<float*>(smem_gen + (sBar + 512u - smem_base));  // the activation quantiser's table
@@ -191,6 +194,7 @@ __global__ void __launch_bounds__(at::kThreads, 1)
       mbar_init(s_free + 8 * i, 128);
     }
     for (uint32_t i = 0; i < 8; ++i) mbar_init(chain_bar + 8 * i, 32);
+    mbar_init(q_ready, 128);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_q);
@@ -245,19 +249,22 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     // ---------------- MMA issuer ----------------
     constexpr uint32_t idesc_qk = make_idesc_bf16(kRows, kRows);               // A and B K-major
     constexpr uint32_t idesc_pv = make_idesc_bf16(kRows, kD) | (1u << 16);     // B (V) MN-major
-    bool ok = mbar_wait_warp(q_full, 0, abort_flag, kStatusMmaTimeout, wait_limit);
-    // S_g = Q K_j^T, as soon as the group has taken its previous score row into registers (s_free) and K_j has landed:
-    // the scores of the group's next tile are computed while it is still working on the current one.
+    bool ok = mbar_wait_warp(q_ready, 0, abort_flag, kStatusMmaTimeout, wait_limit);
+    // S = Q K_j^T into the ONE score buffer, Q from tensor memory: with Q and K both in shared memory a 128 x 128 x 16
+    // MMA needs 8 KB per 64 cycles, all of the SM's shared-memory bandwidth, and measured 119 cycles. Issued as soon as
+    // the previous tile's scores have been taken into registers (that tile belongs to the other group) and K_j has
+    // landed; the barriers alternate by tile parity although the buffer does not, so that no wait ever looks at a barrier
+    // two phases behind.
     auto issue_s = [&](uint32_t j) -> bool {
       const uint32_t g = j & 1u, use = j >> 1;
       if (!mbar_wait_warp(k_full + 8 * g, use & 1u, abort_flag, kStatusMmaTimeout, wait_limit)) return false;
-      if (use > 0 && !mbar_wait_warp(s_free + 8 * g, (use - 1u) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) return false;
+      if (j > 0 && !mbar_wait_warp(s_free + 8 * ((j - 1u) & 1u), ((j - 1u) >> 1) & 1u, abort_flag, kStatusAccEmptyTimeout, wait_limit)) return false;
       tc_fence_after();
       if (elect_one()) {
 #pragma unroll
         for (uint32_t kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * kSub + (kk & 3u) * 32u;
-          tc_mma_bf16(tmem_base + kSCol + g * 128u, make_desc_sw128(sQ + off), make_desc_sw128(sK + g * kTile + off), idesc_qk, kk != 0u);
+          tc_mma_bf16_ts(tmem_base + kSCol, tmem_base + kQCol + kk * 8u, make_desc_sw128(sK + g * kTile + off), idesc_qk, kk != 0u);
         }
         tc_commit(s_full + 8 * g);
         tc_commit(k_empty + 8 * g);
@@ -287,11 +294,31 @@ __global__ void __launch_bounds__(at::kThreads, 1)
     // ---------------- softmax: two groups, one query row per thread ----------------
     const uint32_t g = (warp - 2u) >> 2, quarter = warp & 3u, row = quarter * 32u + lane;
     const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    const uint32_t s_addr = lane_addr + kSCol + g * 128u, p_addr = lane_addr + kPCol + g * 64u, o_addr = lane_addr + kOCol;
+    const uint32_t s_addr = lane_addr + kSCol, p_addr = lane_addr + kPCol + g * 64u, o_addr = lane_addr + kOCol;
     float m_known = -INFINITY, l = 0.0f;  // l is this group's partial row sum, relative to m_known
     bool ok = true;
     uint32_t s0[32], s1[32], s2[32], s3[32];
     uint32_t use = 0;
+    if (g == 0) {
+      // Q goes from shared to tensor memory once: as the A operand of the score MMAs it then costs no shared-memory
+      // bandwidth. A thread undoes the 128-byte swizzle of its row: chunk c sits at position c ^ (row % 8).
+      ok = mbar_wait_warp(q_full, 0, abort_flag, kStatusEpilogueTimeout, wait_limit);
+      if (ok) {
+        const uint8_t* qrow = smem_gen + (sQ - smem_base) + row * 128u;
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c) {
+          const uint4 a = *reinterpret_cast<const uint4*>(qrow + ((c ^ (row & 7u)) << 4));
+          const uint4 b = *reinterpret_cast<const uint4*>(qrow + kSub + ((c ^ (row & 7u)) << 4));
+          s0[c * 4] = a.x; s0[c * 4 + 1] = a.y; s0[c * 4 + 2] = a.z; s0[c * 4 + 3] = a.w;
+          s1[c * 4] = b.x; s1[c * 4 + 1] = b.y; s1[c * 4 + 2] = b.z; s1[c * 4 + 3] = b.w;
+        }
+        tmem_st_32x32b_x32(lane_addr + kQCol, s0);
+        tmem_st_32x32b_x32(lane_addr + kQCol + 32u, s1);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(q_ready);
+      }
+    }
     // m_{j}: published by the thread of tile j for the thread of tile j + 1 (the same row, the other group)
     auto chain_wait = [&](uint32_t j) -> bool {
       return mbar_wait_warp(chain_bar + 8 * (quarter * 2u + (j & 1u)), (j >> 1) & 1u, abort_flag, kStatusEpilogueTimeout, wait_limit);
