@@ -4,16 +4,18 @@
 //
 // One CTA per (128 query rows, head, batch); flash-attention tiling over 128-key tiles, both products on the tensor
 // cores (tcgen05.mma kind::f16); scores, probabilities and the running output live in TMEM:
-//   columns   0-255  S_0, S_1: score buffers (f32) of the two softmax groups
-//           256-383  P_0, P_1: their probability buffers (bf16 pairs, 64 columns each): the A operand of the second
-//                    product is read from tensor memory, so P never touches shared memory
+//   columns   0-127  S: the score buffer (f32); a thread takes its row into registers at once, so one buffer serves
+//                    both softmax groups in turn
+//           128-255  P_0, P_1: the groups' probability buffers (bf16 pairs, 64 columns each)
+//           256-319  Q (bf16 pairs), copied from shared memory once
 //           384-511  O: the one running output (f32) both groups' products accumulate into
+//   Both products read their A operand (Q, P) from tensor memory: neither costs shared-memory bandwidth in the loop.
 //   warps 0, 10 TMA: the Q tile once, then K tiles (warp 0) and V tiles (warp 10) into two-stage rings ([128 rows x
 //               64 bf16] boxes with 128-byte swizzle straight out of the [B, S, H, D] tensors: a head is a 256-byte
 //               column window);
-//   warp 1      one elected thread issues S_g = Q K_j^T (both operands K-major, 8 MMAs of K = 16) as soon as the group
-//               has taken its previous score row into registers, and O += P_g V_j in tile order, with P from TMEM and V
-//               as it lies in memory (keys x d: an MN-major B operand, no transpose pass);
+//   warp 1      one elected thread issues S = Q K_j^T (K the K-major B operand, 8 MMAs of K = 16) as soon as the previous
+//               tile's score rows have been taken into registers, and O += P_g V_j in tile order, with V as it lies in
+//               memory (keys x d: an MN-major B operand, no transpose pass);
 //   warps 2-9   two softmax groups of four warps, one query row per thread (TMEM lane = row); the key tiles alternate
 //               between them, so that one group's exponentials run under the other's TMEM traffic and waits. The
 //               reference maximum m of a row is ONE chain through all tiles: the thread of tile j takes m_{j-1} from
@@ -25,8 +27,9 @@
 //               p = exp2(s * scale * log2e - m), summed in f32, goes as bf16 pairs into P_g with tcgen05.st. At the
 //               end the two partial sums are joined and each group writes half of the columns of O / l.
 // Why this shape: a 128 x 128 x 16 MMA with both operands in shared memory reads 8 KB in its 64 cycles, all of an SM's
-// 128 B/clk, and the TMA's writes of K and V come on top. With P in tensor memory a key tile moves 160 KB through shared
-// memory instead of 224 KB; with one O instead of one per group there are TMEM columns left for P.
+// 128 B/clk (measured: 119 cycles), and the TMA's writes of K and V come on top. With Q and P in tensor memory a key
+// tile moves 128 KB through shared memory instead of 224 KB; with one O and one S instead of one per group there are
+// TMEM columns for them.
 // The reference's kernel is the same recurrence one key at a time in f32 (m' = max(m, s); o = o * exp(m - m') +
 // exp(s - m') v; l likewise); here it runs a tile at a time, p is rounded to bf16 for the tensor cores, and exp is
 // exp2 with the scale folded in: the result agrees with the f32 recurrence to bf16 rounding (tests: relative
