@@ -99,6 +99,27 @@ int32_t tnf_mem_snapshot(tnf_ctx* ctx, uint64_t out[8]);
  * is given back is streamed through its ring from the next step on -- and is refused with
  * TNF_ERR_BUDGET_EXCEEDED only if that was not enough. *bytes = total given back so far. */
 int32_t tnf_reclaimed_bytes(tnf_ctx* ctx, uint64_t* bytes);
+/* Workspace pool (Workspace::alloc / WsBuf::drop / drain_pool / pool_bytes / free_count,
+ * thinfer-core/src/workspace.rs:131-316,318-420): scratch buffers rented by size class
+ * (bytes rounded up to 256, at least 256), charged to the workspace category.
+ *   tnf_ws_alloc    hands out the newest idle buffer of the class without a device call (a hit), else
+ *                   allocates one (a miss) under the same budget rule as tnf_alloc. The buffer is at
+ *                   least `bytes` long; views over it carry the requested length.
+ *   tnf_ws_release  puts a rented buffer back as idle. Its bytes stay allocated and stay in the
+ *                   workspace category of the snapshot; work already enqueued on the compute stream
+ *                   that uses it is ordered before whatever the next renter enqueues there.
+ *   tnf_ws_drain    frees every idle buffer (the phase boundary call); buffers out on rent stay.
+ *   tnf_ws_stats    out = {idle bytes, idle buffers, buffers out on rent, hits, misses, bytes freed
+ *                   under memory pressure}.
+ * The idle pool is the first holder asked when an allocation does not fit the budget
+ * (RECLAIM_IDLE_POOL before RECLAIM_EVICTABLE_WEIGHTS, thinfer-core/src/arbiter.rs:37-38): smallest
+ * class first, until enough is back (spill_pool_locked, workspace.rs:52-85); only then are weights
+ * given back. tnf_free on a pool buffer also takes it out of the pool's books. Releasing an id
+ * that is not out on rent fails with TNF_ERR_UNKNOWN_BUFFER. */
+int32_t tnf_ws_alloc(tnf_ctx* ctx, uint64_t bytes, uint64_t* id);
+int32_t tnf_ws_release(tnf_ctx* ctx, uint64_t id);
+int32_t tnf_ws_drain(tnf_ctx* ctx, uint64_t* freed_bytes);
+int32_t tnf_ws_stats(tnf_ctx* ctx, uint64_t out[6]);
 /* set_transient_reserve (thinfer-core/src/residency.rs:535-537): bytes of the budget that weight plans
  * (tnf_stack_create with a context budget, tnf_stack_restore) leave free for transient workspace. */
 int32_t tnf_set_transient_reserve(tnf_ctx* ctx, uint64_t bytes);

@@ -6,7 +6,7 @@ C ABI in ``include/thinfer_nvfp4.h``. Everything computes on the GPU through
 """
 from . import _lib  # noqa: F401
 from .backend import (  # noqa: F401
-    Backend, BatchScope, BudgetExceeded, DenseActSites, DeviceTimeout, InvalidArgument, Nvfp4Weight, TnfError, UnknownBuffer,
+    Backend, BatchScope, BudgetExceeded, DenseActSites, DeviceTimeout, InvalidArgument, Nvfp4Weight, TnfError, UnknownBuffer, WsBuf,
     interleave_swiglu,
 )
 from .reader import CallbackReader, MmapReader, Reader, ReaderError, ReaderView  # noqa: F401

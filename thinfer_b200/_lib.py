@@ -141,6 +141,10 @@ SIGNATURES = {
     "tnf_stack_restore": (C.c_int32, [C.c_void_p, C.c_uint64]),
     "tnf_reclaimed_bytes": (C.c_int32, [_ctx, _u64p]),
     "tnf_set_transient_reserve": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_ws_alloc": (C.c_int32, [_ctx, C.c_uint64, _u64p]),
+    "tnf_ws_release": (C.c_int32, [_ctx, C.c_uint64]),
+    "tnf_ws_drain": (C.c_int32, [_ctx, _u64p]),
+    "tnf_ws_stats": (C.c_int32, [_ctx, _u64p]),
     "tnf_mmap_open": (C.c_int32, [C.c_char_p, C.POINTER(Reader)]),
     "tnf_mmap_stats": (C.c_int32, [C.POINTER(Reader), _u64p]),
     "tnf_reader_view": (C.c_int32, [C.POINTER(Reader), C.c_uint64, C.c_uint64, C.POINTER(Reader)]),

@@ -169,8 +169,53 @@ class Backend:
         _check(self.lib.tnf_streams(self._ctx, C.byref(a), C.byref(b)))
         return int(a.value), int(b.value)
 
+    # -- workspace pool (Workspace in the reference) ---------------------------------------
+    def ws_alloc(self, nbytes: int) -> "WsBuf":
+        """Rents a scratch buffer of at least ``nbytes`` from the pool (Workspace::alloc,
+        thinfer-core/src/workspace.rs:196-260). Release it (or leave its ``with`` block) to make it idle."""
+        bid = C.c_uint64()
+        _check(self.lib.tnf_ws_alloc(self._ctx, nbytes, C.byref(bid)))
+        return WsBuf(self, Buf(bid.value, 0, nbytes))
+
+    def drain_pool(self) -> int:
+        """Frees every idle pool buffer (Workspace::drain_pool); returns the bytes freed."""
+        freed = C.c_uint64()
+        _check(self.lib.tnf_ws_drain(self._ctx, C.byref(freed)))
+        return int(freed.value)
+
+    def pool_stats(self) -> dict:
+        out = (C.c_uint64 * 6)()
+        _check(self.lib.tnf_ws_stats(self._ctx, out))
+        return dict(zip(["pool_bytes", "free_count", "rented", "hits", "misses", "spilled_bytes"], [int(v) for v in out]))
+
     def scope(self) -> "BatchScope":
         return BatchScope(self)
+
+
+class WsBuf:
+    """A rented pool buffer (WsBuf, thinfer-core/src/workspace.rs:318-420): ``buf`` is the view of the requested
+    length; releasing returns the buffer to the pool, once."""
+
+    def __init__(self, be: Backend, buf: Buf):
+        self.be, self.buf = be, buf
+
+    @property
+    def id(self) -> int:
+        return self.buf.id
+
+    def __len__(self) -> int:
+        return self.buf.len
+
+    def release(self) -> None:
+        if self.be is not None:
+            be, self.be = self.be, None
+            _check(be.lib.tnf_ws_release(be._ctx, self.buf.id))
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.release()
 
 
 def device_scales_bytes(rows: int, k: int) -> int:
@@ -279,6 +324,14 @@ class BatchScope:
 
     def __init__(self, backend: Backend):
         self.be = backend
+        self._guards = []  # pool buffers rented through the scope: none returns to the pool before submit
+
+    def alloc(self, nbytes: int) -> Buf:
+        """Scratch for the launches of this scope (BatchScope::alloc, thinfer-core/src/workspace.rs:452-467): rented
+        from the pool and held until ``submit``, so no launch of the scope sees a buffer recycled under it."""
+        g = self.be.ws_alloc(nbytes)
+        self._guards.append(g)
+        return g.buf
 
     def act_quant(self, a_bf16: Buf, m: int, k: int, global_scale: float = 0.0, device_layout: bool = False):
         """Per-row per-16 NVFP4 activation quantiser. Returns (codes, scales, global_scale_used)."""
@@ -381,4 +434,9 @@ class BatchScope:
         _check(self.be.lib.tnf_sdpa(self.be._ctx, C.byref(args)))
 
     def submit(self, timeout_ms: int = 0) -> None:
-        self.be.submit(timeout_ms)
+        try:
+            self.be.submit(timeout_ms)
+        finally:
+            guards, self._guards = self._guards, []
+            for g in guards:
+                g.release()

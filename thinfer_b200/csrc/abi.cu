@@ -1,5 +1,6 @@
 // C ABI of the NVFP4 linear path: context, buffers, quantisers, the linear, uploads.
 // See include/thinfer_nvfp4.h for the reference interface each entry point replaces.
+#include <algorithm>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -84,6 +85,8 @@ int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id) {
     // reclaim_until_fits (thinfer-core/src/arbiter.rs:129-160): ask the registered holders, in order, to give
     // memory back before refusing; a holder frees whole weight sets and streams them from then on
     ctx->in_reclaim = true;
+    // the idle workspace pool is first in the chain (RECLAIM_IDLE_POOL, thinfer-core/src/arbiter.rs:37-38)
+    ws_spill_locked(ctx, total + bytes - ctx->budget);
     for (auto& r : ctx->reclaimers) {
       total = ctx->live[0] + ctx->live[1] + ctx->live[2];
       if (total + bytes <= ctx->budget) break;
@@ -130,8 +133,38 @@ int32_t free_locked(tnf_ctx* ctx, uint64_t id) {
     else ++m;
   }
   ctx->bufs.erase(it);
+  // a pool buffer freed directly leaves the pool's books too
+  auto rented = ctx->ws_rented.find(id);
+  if (rented != ctx->ws_rented.end()) {
+    ctx->ws_rented.erase(rented);
+  } else {
+    for (auto c = ctx->ws_free.begin(); c != ctx->ws_free.end(); ++c) {
+      auto pos = std::find(c->second.begin(), c->second.end(), id);
+      if (pos == c->second.end()) continue;
+      c->second.erase(pos);
+      ctx->ws_pool_bytes -= c->first;
+      if (c->second.empty()) ctx->ws_free.erase(c);
+      break;
+    }
+  }
   if (e != cudaSuccess) return cuda_fail(e, "cudaFree");
   return TNF_OK;
+}
+
+// spill_pool_locked (thinfer-core/src/workspace.rs:52-85): classes in ascending size, newest buffer of a class first.
+uint64_t ws_spill_locked(tnf_ctx* ctx, uint64_t at_least) {
+  uint64_t freed = 0;
+  while (freed < at_least && !ctx->ws_free.empty()) {
+    auto c = ctx->ws_free.begin();
+    const uint64_t cls = c->first, id = c->second.back();
+    c->second.pop_back();
+    if (c->second.empty()) ctx->ws_free.erase(c);
+    ctx->ws_pool_bytes -= cls;
+    free_locked(ctx, id);
+    freed += cls;
+  }
+  ctx->ws_spilled += freed;
+  return freed;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -662,6 +695,74 @@ int32_t tnf_reclaimed_bytes(tnf_ctx* ctx, uint64_t* bytes) {
   }
   std::lock_guard<std::mutex> lk(ctx->mu);
   *bytes = ctx->reclaimed;
+  return TNF_OK;
+}
+
+int32_t tnf_ws_alloc(tnf_ctx* ctx, uint64_t bytes, uint64_t* id) {
+  if (!ctx || !id) {
+    set_error("tnf_ws_alloc: null argument");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  if (bytes > UINT64_MAX - 255) {
+    set_error("tnf_ws_alloc: size %llu overflows its class", (unsigned long long)bytes);
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  const uint64_t cls = std::max<uint64_t>(256, (bytes + 255) / 256 * 256);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto c = ctx->ws_free.find(cls);
+  if (c != ctx->ws_free.end()) {  // pool hit: the newest idle buffer of the class, no device call
+    *id = c->second.back();
+    c->second.pop_back();
+    if (c->second.empty()) ctx->ws_free.erase(c);
+    ctx->ws_pool_bytes -= cls;
+    ctx->ws_hits++;
+  } else {
+    int32_t st = alloc_locked(ctx, cls, TNF_CAT_WORKSPACE, id);
+    if (st != TNF_OK) return st;
+    ctx->ws_misses++;
+  }
+  ctx->ws_rented[*id] = cls;
+  return TNF_OK;
+}
+
+int32_t tnf_ws_release(tnf_ctx* ctx, uint64_t id) {
+  TNF_CHECK_CTX(ctx);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  auto r = ctx->ws_rented.find(id);
+  if (r == ctx->ws_rented.end()) {
+    set_error("tnf_ws_release: buffer id %llu is not out on rent", (unsigned long long)id);
+    return TNF_ERR_UNKNOWN_BUFFER;
+  }
+  ctx->ws_free[r->second].push_back(id);
+  ctx->ws_pool_bytes += r->second;
+  ctx->ws_rented.erase(r);
+  return TNF_OK;
+}
+
+int32_t tnf_ws_drain(tnf_ctx* ctx, uint64_t* freed_bytes) {
+  TNF_CHECK_CTX(ctx);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const uint64_t spilled = ctx->ws_spilled;
+  const uint64_t freed = ws_spill_locked(ctx, UINT64_MAX);
+  ctx->ws_spilled = spilled;  // a drain is a phase boundary, not memory pressure
+  if (freed_bytes) *freed_bytes = freed;
+  return TNF_OK;
+}
+
+int32_t tnf_ws_stats(tnf_ctx* ctx, uint64_t out[6]) {
+  if (!ctx || !out) {
+    set_error("tnf_ws_stats: null argument");
+    return TNF_ERR_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  uint64_t idle = 0;
+  for (auto& c : ctx->ws_free) idle += c.second.size();
+  out[0] = ctx->ws_pool_bytes;
+  out[1] = idle;
+  out[2] = ctx->ws_rented.size();
+  out[3] = ctx->ws_hits;
+  out[4] = ctx->ws_misses;
+  out[5] = ctx->ws_spilled;
   return TNF_OK;
 }
 

@@ -57,6 +57,11 @@ struct tnf_ctx {
   bool in_reclaim = false;
   uint64_t reclaimed = 0;                 // bytes given back by reclaimers so far
   uint64_t transient_reserve = 0;         // bytes of the budget a weight plan leaves free for transient workspace
+  // Workspace pool (thinfer-core/src/workspace.rs:131-316): idle scratch buffers by 256-byte size class, last in
+  // first out within a class. Idle buffers stay in `bufs` and in `live[workspace]`; `ws_pool_bytes` is their sum.
+  std::map<uint64_t, std::vector<uint64_t>> ws_free;  // class bytes -> ids of idle buffers
+  std::unordered_map<uint64_t, uint64_t> ws_rented;   // id -> class of every buffer out on rent
+  uint64_t ws_pool_bytes = 0, ws_hits = 0, ws_misses = 0, ws_spilled = 0;
   // scratch for on-the-fly activation quantisation (workspace category)
   uint64_t scratch_codes_id = 0, scratch_scales_id = 0;
   uint64_t scratch_codes_bytes = 0, scratch_scales_bytes = 0;
@@ -93,5 +98,7 @@ uint8_t* resolve(tnf_ctx* ctx, const tnf_buf& b, uint64_t need_bytes, const char
 uint8_t* resolve_multicast(tnf_ctx* ctx, const tnf_buf& b, const char* name, int32_t* status);
 int32_t alloc_locked(tnf_ctx* ctx, uint64_t bytes, int category, uint64_t* id);
 int32_t free_locked(tnf_ctx* ctx, uint64_t id);
+// Frees idle pool buffers, smallest class first, until `at_least` bytes are back; returns the bytes freed.
+uint64_t ws_spill_locked(tnf_ctx* ctx, uint64_t at_least);
 bool get_map(tnf_ctx* ctx, const MapSpec& spec, CUtensorMap* out);  // copies the (cached) map out under the lock
 }  // namespace tnf

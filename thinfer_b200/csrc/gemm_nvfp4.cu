@@ -44,7 +44,8 @@ struct TileCfg {
   static constexpr int kSfbBytes = 2048 * kSfbAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kStages = (BN >= 224) ? 4 : (BN >= 192 ? 5 : 6);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kEpiVecBytes = 4 * 1536;  // per epilogue warp: the tile's bias as f32 (1 KB) and gate as bf16 (512 B)
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kEpiVecBytes;
   static constexpr uint32_t kAccCol0 = 0;
   static constexpr uint32_t kSfaCol = kAccStages * BN;
   static constexpr uint32_t kSfbCol = kSfaCol + 16;
@@ -53,6 +54,46 @@ struct TileCfg {
 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// One warp's 32 rows x 32 columns of a tile: r holds this lane's row. The arithmetic is the pair kernel's
+// (epilogue8), chosen once per chunk instead of per element. Each lane then trades half of its four 16-byte
+// vectors with its neighbour so that a lane pair stores whole 32-byte sectors of one row per instruction:
+// half-sector stores from 32 different rows per instruction ran at a fraction of that.
+template <bool kGelu, bool kChain, bool kGate>
+__device__ __forceinline__ void epilogue_chunk32(const uint32_t (&r)[32], const GemmParams& p, float alpha, const float* bias32,
+                                                 const uint4* gate4, const uint4 (&res)[4], uint32_t ncols, uint32_t row,
+                                                 uint32_t col, int lane, bool skip_stores) {
+  uint4 v[4];
+#pragma unroll
+  for (int v8 = 0; v8 < 4; ++v8)
+    v[v8] = epilogue8<kGelu, kChain, kGate>(r + v8 * 8, alpha, bias32 + v8 * 8, kGate ? gate4[v8] : make_uint4(0, 0, 0, 0), res[v8]);
+  const bool odd = (lane & 1) != 0;
+  uint4 mine[2], theirs[2];  // vectors of this lane's row it still stores / of the neighbour's row it stores for it
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const uint4 give = odd ? v[2 * j] : v[2 * j + 1];
+    mine[j] = odd ? v[2 * j + 1] : v[2 * j];
+    theirs[j].x = __shfl_xor_sync(0xFFFFFFFFu, give.x, 1);
+    theirs[j].y = __shfl_xor_sync(0xFFFFFFFFu, give.y, 1);
+    theirs[j].z = __shfl_xor_sync(0xFFFFFFFFu, give.z, 1);
+    theirs[j].w = __shfl_xor_sync(0xFFFFFFFFu, give.w, 1);
+  }
+  if (skip_stores) return;
+  // even lane: columns [0,8) and [16,24) of both rows of the pair; odd lane: columns [8,16) and [24,32)
+  const uint32_t row_even = row & ~1u, c8 = odd ? 8u : 0u;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    if (c8 + 16u * j >= ncols) break;  // ncols is a multiple of 8
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const uint32_t orow = row_even + rr;
+      if (orow >= p.m) continue;
+      const uint4 o4 = (uint32_t(rr) == (row & 1u)) ? mine[j] : theirs[j];
+      const uint64_t off = uint64_t(orow) * p.ldo + p.n_offset + col + c8 + 16u * j;
+      for (uint32_t d = 0; d < p.n_out; ++d) *reinterpret_cast<uint4*>(p.out[d] + off) = o4;
+    }
+  }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -202,12 +243,34 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
     const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    // this warp's copy of the tile's bias (as f32, halved for the fused GELU) and gate columns: fetched while the
+    // main loop runs, so that their latency is not paid after the accumulator is ready (with few tiles per SM
+    // nothing else would hide it)
+    float* bias_smem = reinterpret_cast<float*>(smem_gen + (sBar + 256 - smem_base)) + quarter * 384;
+    uint4* gate_smem = reinterpret_cast<uint4*>(bias_smem + 256);
+    const float bias_mul = (p.act == 1u && !p.chain) ? 0.5f : 1.0f;  // the fused GELU works on x/2
+    const float alpha = p.alpha * bias_mul;
+    const uint32_t mode = (p.act == 1u ? 1u : 0u) | (p.chain ? 2u : 0u) | (p.gate ? 4u : 0u);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       const uint32_t row = tm * kBlockM + quarter * 32 + lane;
       const uint32_t n0 = tn * BN;
+      {
+        const uint32_t col = n0 + lane * 8;
+        const bool live = lane * 8 < uint32_t(BN) && col < p.n;  // n is a multiple of 8
+        uint4 b4 = make_uint4(0, 0, 0, 0);
+        if (p.bias && live) b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+        if (lane * 8 < uint32_t(BN)) {
+          *reinterpret_cast<float4*>(bias_smem + lane * 8) =
+              make_float4(bf16_lo(b4.x) * bias_mul, bf16_hi(b4.x) * bias_mul, bf16_lo(b4.y) * bias_mul, bf16_hi(b4.y) * bias_mul);
+          *reinterpret_cast<float4*>(bias_smem + lane * 8 + 4) =
+              make_float4(bf16_lo(b4.z) * bias_mul, bf16_hi(b4.z) * bias_mul, bf16_lo(b4.w) * bias_mul, bf16_hi(b4.w) * bias_mul);
+        }
+        if (p.gate) gate_smem[lane] = live ? __ldg(reinterpret_cast<const uint4*>(p.gate + col)) : make_uint4(0, 0, 0, 0);
+        __syncwarp();
+      }
       if (!mbar_wait_bounded(bar_acc_full + 8 * acc, acc_phase, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
         ok = false;
         break;
@@ -221,55 +284,33 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (nc >= p.n) break;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        const uint32_t ncols = min(32u, p.n - nc);  // multiple of 8
+        // the residual row's four vectors are requested together, before the accumulator read is waited for
+        uint4 res[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (p.gate && row < p.m) {
+          const uint16_t* res_row = p.residual + uint64_t(row) * p.n + nc;
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8)
+            if (uint32_t(v8 * 8) < ncols) res[v8] = __ldg(reinterpret_cast<const uint4*>(res_row + v8 * 8));
+        }
         tmem_ld_wait();
-        if (row < p.m) {
-          const uint32_t ncols = min(32u, p.n - nc);  // multiple of 8
-          const uint64_t out_off = uint64_t(row) * p.ldo + p.n_offset + nc;
-          const uint16_t* res_row = p.residual ? p.residual + uint64_t(row) * p.n + nc : nullptr;
-#pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
-            if (uint32_t(v8 * 8) >= ncols) break;
-            uint4 bias4 = make_uint4(0, 0, 0, 0), gate4 = make_uint4(0, 0, 0, 0), res4 = make_uint4(0, 0, 0, 0);
-            if (p.bias) bias4 = __ldg(reinterpret_cast<const uint4*>(p.bias + nc + v8 * 8));
-            if (p.gate) {
-              gate4 = __ldg(reinterpret_cast<const uint4*>(p.gate + nc + v8 * 8));
-              res4 = __ldg(reinterpret_cast<const uint4*>(res_row + v8 * 8));
-            }
-            const uint32_t bw[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
-            const uint32_t gw[4] = {gate4.x, gate4.y, gate4.z, gate4.w};
-            const uint32_t rw[4] = {res4.x, res4.y, res4.z, res4.w};
-            uint32_t ow[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              float v[2];
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                float x = __uint_as_float(r[v8 * 8 + h * 2 + e]) * p.alpha;
-                if (p.chain) x = bf16r(x);
-                if (p.bias) {
-                  x += bf16_bits_to_f32(e ? (bw[h] >> 16) : (bw[h] & 0xFFFFu));
-                  if (p.chain) x = bf16r(x);
-                }
-                if (p.act == 1u) {
-                  x = p.chain ? gelu_tanh_exact(x) : gelu_tanh_fast(x);  // same two forms as the pair kernel
-                  if (p.chain) x = bf16r(x);
-                }
-                if (p.gate) {
-                  float g = bf16_bits_to_f32(e ? (gw[h] >> 16) : (gw[h] & 0xFFFFu));
-                  float rs = bf16_bits_to_f32(e ? (rw[h] >> 16) : (rw[h] & 0xFFFFu));
-                  x = rs + g * x;
-                }
-                v[e] = x;
-              }
-              __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
-              ow[h] = *reinterpret_cast<uint32_t*>(&pk);
-            }
-            const uint4 o4 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-            if (!(kDiag && (p.diag & 1u)) || o4.x == 0x12345678u)
-              for (uint32_t d = 0; d < p.n_out; ++d)
-                *reinterpret_cast<uint4*>(p.out[d] + out_off + v8 * 8) = o4;
+        if (ktr && warp == 2 && lane == 0) p.trace[1210 + 2 * c] = clock64();
+        {
+          const bool skip = kDiag && (p.diag & 1u);
+          const float* b32 = bias_smem + c * 32;
+          const uint4* g4 = gate_smem + c * 4;
+          switch (mode) {  // warp-uniform
+            case 0: epilogue_chunk32<false, false, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 1: epilogue_chunk32<true, false, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 2: epilogue_chunk32<false, true, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 3: epilogue_chunk32<true, true, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 4: epilogue_chunk32<false, false, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 5: epilogue_chunk32<true, false, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            case 6: epilogue_chunk32<false, true, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
+            default: epilogue_chunk32<true, true, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
           }
         }
+        if (ktr && warp == 2 && lane == 0) p.trace[1211 + 2 * c] = clock64();
       }
       tc_fence_before();
       __syncwarp();

@@ -79,44 +79,6 @@ struct PairOutMaps {
   CUtensorMap m[kMaxPeers];
 };
 
-// 8 accumulator columns -> 8 bf16 (one 16-byte chunk of the staging row). `b8` points at the 8 bias values
-// in shared memory as f32 (zero without a bias); in the fused GELU variant alpha and the bias arrive halved.
-// The fused variants work on packed pairs (fma.rn.f32x2): one FMA applies alpha and the bias to two columns.
-template <bool kGelu, bool kChain, bool kGate>
-__device__ __forceinline__ uint4 epilogue8(const uint32_t* r, float alpha, const float* b8, uint4 g4, uint4 s4) {
-  const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, sw[4] = {s4.x, s4.y, s4.z, s4.w};
-  const float4 bl = *reinterpret_cast<const float4*>(b8), bh = *reinterpret_cast<const float4*>(b8 + 4);
-  const float bv[8] = {bl.x, bl.y, bl.z, bl.w, bh.x, bh.y, bh.z, bh.w};
-  uint32_t o[4];
-#pragma unroll
-  for (int h = 0; h < 4; ++h) {
-    float v0, v1;
-    if (kChain) {  // the reference's op chain: every step rounded to bf16, accurate tanh
-      float v[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float x = bf16r(__uint_as_float(r[2 * h + e]) * alpha);
-        x = bf16r(x + bv[2 * h + e]);  // adding the zero of "no bias" changes nothing
-        if (kGelu) x = bf16r(gelu_tanh_exact(x));
-        v[e] = x;
-      }
-      v0 = v[0];
-      v1 = v[1];
-    } else {
-      uint64_t y2 = fma2(pack2u(r[2 * h], r[2 * h + 1]), pack2(alpha, alpha), pack2(bv[2 * h], bv[2 * h + 1]));
-      if (kGelu) y2 = gelu_tanh_fast2_half(y2);
-      unpack2(y2, v0, v1);
-    }
-    if (kGate) {
-      v0 = fmaf(bf16_lo(gw[h]), v0, bf16_lo(sw[h]));
-      v1 = fmaf(bf16_hi(gw[h]), v1, bf16_hi(sw[h]));
-    }
-    __nv_bfloat162 pk = __floats2bfloat162_rn(v0, v1);
-    o[h] = *reinterpret_cast<uint32_t*>(&pk);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
 // One warp's 32 rows x 64 columns: accumulator registers -> bf16 rows in the swizzled staging
 // buffer (128 bytes per row; 16-byte chunk j of row `lane` lands at chunk j ^ (lane & 7)).
 template <bool kGelu, bool kChain, bool kGate, bool kQuant>

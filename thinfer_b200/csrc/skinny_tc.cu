@@ -212,15 +212,16 @@ __global__ void __launch_bounds__(sk::kThreads, 1)
   } else if (warp >= 4) {
     // ---------------- epilogue: lane = W row = output column; register i = activation row i ----------------
     const uint32_t quarter = warp & 3u;
+    const uint32_t n = row0 + quarter * 32u + lane;
+    // the column's bias and gate are requested before the wait: their latency runs under the main loop
+    const float bias = (p.bias && n < p.n) ? bf16_lo(uint32_t(__ldg(p.bias + n))) : 0.0f;
+    const float gate = (p.gate && n < p.n) ? bf16_lo(uint32_t(__ldg(p.gate + n))) : 0.0f;
     if (mbar_wait_bounded(bar_acc, 0, abort_flag, kStatusEpilogueTimeout, wait_limit)) {
       tc_fence_after();
       uint32_t r[16];
       tmem_ld_32x32b_x16(tmem_base + ((quarter * 32u) << 16) + kAccCol, r);
       tmem_ld_wait();
-      const uint32_t n = row0 + quarter * 32u + lane;
       if (n < p.n) {
-        const float bias = p.bias ? bf16_lo(uint32_t(p.bias[n])) : 0.0f;
-        const float gate = p.gate ? bf16_lo(uint32_t(p.gate[n])) : 0.0f;
 #pragma unroll
         for (uint32_t i = 0; i < kMaxM; ++i) {
           if (i < p.m) {
