@@ -43,7 +43,9 @@ def _run(be, a, w, b, **kw):
 # shapes: reference conformance geometries (q4_0_matmul.rs:178-223 small / ragged / rectangular),
 # tile-edge cases of this kernel (128x256 tiles, 256-element K tiles) and BASELINE config 1
 SHAPES = [(16, 16, 32), (10, 16, 32), (8, 8, 128), (24, 48, 96), (128, 256, 256), (129, 264, 288),
-          (200, 520, 1024), (256, 3072, 3072), (1, 3072, 3072), (2, 264, 96), (3, 18432, 3072), (8, 1000, 320), (5, 136, 12288)]
+          (200, 520, 1024), (256, 3072, 3072), (1, 3072, 3072), (2, 264, 96), (3, 18432, 3072), (8, 1000, 320), (5, 136, 12288),
+          # the 1-CTA kernel's three tile widths: 64 (few tiles, above), 128 (76 tiles of 128) and 256 (148 of 256), ragged in n
+          (100, 9608, 64), (40, 37896, 96)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)

@@ -36,61 +36,87 @@ constexpr uint32_t kTmemCols = 512;
 
 template <int BN>
 struct TileCfg {
-  static constexpr int kSfbAtoms = (BN % 128 == 0) ? BN / 128 : (BN + 96 + 127) / 128;  // 128-row scale blocks touched
-  static constexpr int kAccStages = (2 * BN + 16 + 4 * kSfbAtoms * 4 <= 512) ? 2 : 1;
+  // 128-row scale blocks a tile touches: tiles that divide 128 never straddle a block
+  static constexpr int kSfbAtoms = (BN % 128 == 0) ? BN / 128 : (128 % BN == 0 ? 1 : (BN + 96 + 127) / 128);
+  // scale factors in TMEM: two slots used by alternate K tiles, so that a tile's copies do not wait for the
+  // previous tile's MMAs to finish reading theirs
+  static constexpr int kSfSlotCols = 16 + 16 * kSfbAtoms;
+  static constexpr int kAccStages = (2 * BN + 2 * kSfSlotCols <= 512) ? 2 : 1;
   static constexpr int kABytes = kBlockM * kBlockKBytes;
   static constexpr int kBBytes = BN * kBlockKBytes;
   static constexpr int kSfaBytes = 2048;
   static constexpr int kSfbBytes = 2048 * kSfbAtoms;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kStages = (BN >= 224) ? 4 : (BN >= 192 ? 5 : 6);
+  static constexpr int kStages = (BN >= 224) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 7));
   static constexpr int kEpiVecBytes = 4 * 1536;  // per epilogue warp: the tile's bias as f32 (1 KB) and gate as bf16 (512 B)
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kEpiVecBytes;
   static constexpr uint32_t kAccCol0 = 0;
   static constexpr uint32_t kSfaCol = kAccStages * BN;
-  static constexpr uint32_t kSfbCol = kSfaCol + 16;
-  static_assert(kSfbCol + 4 * kSfbAtoms * 4 <= 512, "TMEM overflow");
+  static constexpr uint32_t kSfbCol = kSfaCol + 16;  // within a slot: 16 columns of A scales, then W's
+  static_assert(kSfaCol + 2 * kSfSlotCols <= 512, "TMEM overflow");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory overflow");
 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
 
-// One warp's 32 rows x 32 columns of a tile: r holds this lane's row. The arithmetic is the pair kernel's
-// (epilogue8), chosen once per chunk instead of per element. Each lane then trades half of its four 16-byte
-// vectors with its neighbour so that a lane pair stores whole 32-byte sectors of one row per instruction:
-// half-sector stores from 32 different rows per instruction ran at a fraction of that.
-template <bool kGelu, bool kChain, bool kGate>
-__device__ __forceinline__ void epilogue_chunk32(const uint32_t (&r)[32], const GemmParams& p, float alpha, const float* bias32,
-                                                 const uint4* gate4, const uint4 (&res)[4], uint32_t ncols, uint32_t row,
-                                                 uint32_t col, int lane, bool skip_stores) {
-  uint4 v[4];
-#pragma unroll
-  for (int v8 = 0; v8 < 4; ++v8)
-    v[v8] = epilogue8<kGelu, kChain, kGate>(r + v8 * 8, alpha, bias32 + v8 * 8, kGate ? gate4[v8] : make_uint4(0, 0, 0, 0), res[v8]);
+// One epilogue warp's 32 rows of a tile, 32 columns at a time; each lane holds its own row. The arithmetic is the
+// pair kernel's (epilogue8), chosen once per tile instead of per element: with one warp per scheduler every
+// branch and every dependent instruction is paid in full. Each lane then trades half of its four 16-byte vectors with its
+// neighbour so that a lane pair stores whole 32-byte sectors of one row per instruction.
+template <int BN, bool kGelu, bool kChain, bool kGate>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_addr, uint32_t row, uint32_t n0, int lane,
+                                              float alpha, const float* bias_smem, const uint4* gate_smem, bool skip_stores) {
+  constexpr int NC = BN / 32;
   const bool odd = (lane & 1) != 0;
-  uint4 mine[2], theirs[2];  // vectors of this lane's row it still stores / of the neighbour's row it stores for it
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const uint4 give = odd ? v[2 * j] : v[2 * j + 1];
-    mine[j] = odd ? v[2 * j + 1] : v[2 * j];
-    theirs[j].x = __shfl_xor_sync(0xFFFFFFFFu, give.x, 1);
-    theirs[j].y = __shfl_xor_sync(0xFFFFFFFFu, give.y, 1);
-    theirs[j].z = __shfl_xor_sync(0xFFFFFFFFu, give.z, 1);
-    theirs[j].w = __shfl_xor_sync(0xFFFFFFFFu, give.w, 1);
-  }
-  if (skip_stores) return;
-  // even lane: columns [0,8) and [16,24) of both rows of the pair; odd lane: columns [8,16) and [24,32)
   const uint32_t row_even = row & ~1u, c8 = odd ? 8u : 0u;
+  // even lane: columns [0,8) and [16,24) of both rows of the pair; odd lane: columns [8,16) and [24,32)
+  const uint64_t base_off = uint64_t(row_even) * p.ldo + p.n_offset + n0 + c8;
+  uint16_t* const out0 = p.out[0] + base_off;
+  const bool row_ok[2] = {row_even < p.m, row_even + 1u < p.m};
+  // one 32-column chunk out of `rc`; the read of the next chunk goes into `rn` meanwhile
+#pragma unroll 1
+  for (int c = 0; c < NC; ++c) {
+    const uint32_t nc = n0 + c * 32;
+    if (nc >= p.n) break;                       // warp-uniform
+    const uint32_t ncols = min(32u, p.n - nc);  // multiple of 8
+    uint32_t rc[32];
+    tmem_ld_32x32b_x32(t_addr + c * 32, rc);
+    // the residual row's four vectors are requested together, before the accumulator read is waited for
+    uint4 res[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (kGate && row < p.m) {
+      const uint16_t* res_row = p.residual + uint64_t(row) * p.n + nc;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    if (c8 + 16u * j >= ncols) break;  // ncols is a multiple of 8
+      for (int v8 = 0; v8 < 4; ++v8)
+        if (uint32_t(v8 * 8) < ncols) res[v8] = __ldg(reinterpret_cast<const uint4*>(res_row + v8 * 8));
+    }
+    tmem_ld_wait();
+    uint4 v[4];
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const uint32_t orow = row_even + rr;
-      if (orow >= p.m) continue;
-      const uint4 o4 = (uint32_t(rr) == (row & 1u)) ? mine[j] : theirs[j];
-      const uint64_t off = uint64_t(orow) * p.ldo + p.n_offset + col + c8 + 16u * j;
-      for (uint32_t d = 0; d < p.n_out; ++d) *reinterpret_cast<uint4*>(p.out[d] + off) = o4;
+    for (int v8 = 0; v8 < 4; ++v8)
+      v[v8] = epilogue8<kGelu, kChain, kGate>(rc + v8 * 8, alpha, bias_smem + c * 32 + v8 * 8,
+                                             kGate ? gate_smem[c * 4 + v8] : make_uint4(0, 0, 0, 0), res[v8]);
+    uint4 mine[2], theirs[2];  // vectors of this lane's row it still stores / of the neighbour's row it stores for it
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 give = odd ? v[2 * j] : v[2 * j + 1];
+      mine[j] = odd ? v[2 * j + 1] : v[2 * j];
+      theirs[j].x = __shfl_xor_sync(0xFFFFFFFFu, give.x, 1);
+      theirs[j].y = __shfl_xor_sync(0xFFFFFFFFu, give.y, 1);
+      theirs[j].z = __shfl_xor_sync(0xFFFFFFFFu, give.z, 1);
+      theirs[j].w = __shfl_xor_sync(0xFFFFFFFFu, give.w, 1);
+    }
+    if (skip_stores) continue;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (c8 + 16u * j >= ncols) break;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        if (!row_ok[rr]) continue;
+        const uint4 o4 = (odd == (rr == 1)) ? mine[j] : theirs[j];
+        const uint64_t off = uint64_t(rr) * p.ldo + uint32_t(c * 32 + 16 * j);
+        *reinterpret_cast<uint4*>(out0 + off) = o4;
+        for (uint32_t d = 1; d < p.n_out; ++d) *reinterpret_cast<uint4*>(p.out[d] + base_off + off) = o4;
+      }
     }
   }
 }
@@ -169,6 +195,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
+          if (ktr && kt < 16 && lane == 0) p.trace[1240 + kt] = clock64();
           if (elect_one()) {
           if (kDiag && (p.diag & 8u)) {
             mbar_arrive_expect_tx(full, Cfg::kSfaBytes + Cfg::kSfbBytes);
@@ -192,8 +219,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- MMA issuer: whole warp runs the loop, one elected lane issues ----------------
     {
       constexpr uint32_t idesc = make_idesc_nvfp4(kBlockM, BN);
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      bool ok = true;
+      // descriptor words of stage 0, K block 0; the loop only moves the 14-bit start-address field of the low
+      // word (shared addresses are below 256 KB, so the add never carries out of it)
+      const uint64_t op0 = make_desc_sw128(sA), sf0 = make_desc_sf(sSfa);
+      const uint32_t op_hi = uint32_t(op0 >> 32), sf_hi = uint32_t(sf0 >> 32);
+      const uint32_t a_lo0 = uint32_t(op0), b_lo0 = uint32_t(make_desc_sw128(sB));
+      const uint32_t sfa_lo0 = uint32_t(sf0), sfb_lo0 = uint32_t(make_desc_sf(sSfb));
+      auto d64 = [](uint32_t lo, uint32_t hi) { return (uint64_t(hi) << 32) | lo; };
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, titer = 0;
+      bool ok = true, ready = false;
       for (uint32_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const uint32_t n0 = (tile / p.tiles_m) * BN;
         const uint32_t sfb_shift = (n0 & 127u) >> 5;  // TMEM column shift when the tile starts inside a 128-row scale block
@@ -203,35 +237,40 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + Cfg::kAccCol0 + acc * BN;
-        for (uint32_t kt = 0; kt < num_k_tiles; ++kt) {
-          if (!mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
+        for (uint32_t kt = 0; kt < num_k_tiles; ++kt, ++titer) {
+          // `ready`: the probe issued one stage ago already saw this stage loaded; otherwise the warp waits here
+          if (!ready && !mbar_wait_warp(bar_full + 8 * stage, phase, abort_flag, kStatusMmaTimeout, wait_limit)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          // probe the next stage now: the answer arrives while this stage's instructions are being issued
+          const uint32_t nstage = stage + 1u == uint32_t(S) ? 0u : stage + 1u;
+          const bool probe = mbar_test_wait(bar_full + 8 * nstage, nstage == 0u ? phase ^ 1u : phase);
           if (ktr && kt == 0 && lane == 0) p.trace[1204] = clock64();
+          if (ktr && kt < 16 && lane == 0) p.trace[1220 + kt] = clock64();
           if (elect_one()) {
-          const uint32_t a_addr = sA + stage * Cfg::kABytes, b_addr = sB + stage * Cfg::kBBytes;
-          const uint32_t sfa_addr = sSfa + stage * Cfg::kSfaBytes, sfb_addr = sSfb + stage * Cfg::kSfbBytes;
+          const uint32_t a_lo = a_lo0 + stage * uint32_t(Cfg::kABytes >> 4), b_lo = b_lo0 + stage * uint32_t(Cfg::kBBytes >> 4);
+          const uint32_t sfa_lo = sfa_lo0 + stage * uint32_t(Cfg::kSfaBytes >> 4), sfb_lo = sfb_lo0 + stage * uint32_t(Cfg::kSfbBytes >> 4);
+          const uint32_t slot = tmem_base + (titer & 1u) * uint32_t(Cfg::kSfSlotCols);
+          const uint32_t t_sfa = slot + Cfg::kSfaCol, t_sfb = slot + Cfg::kSfbCol;
           if (!(kDiag && (p.diag & 2u)) || kt == 0)
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
-            tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfaCol + kb * 4, make_desc_sf(sfa_addr + kb * 512));
+            tc_cp_32x128b_warpx4(t_sfa + kb * 4, d64(sfa_lo + kb * 32, sf_hi));
 #pragma unroll
             for (int j = 0; j < Cfg::kSfbAtoms; ++j)
-              tc_cp_32x128b_warpx4(tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + j * 4,
-                                   make_desc_sf(sfb_addr + j * 2048 + kb * 512));
+              tc_cp_32x128b_warpx4(t_sfb + kb * (4 * Cfg::kSfbAtoms) + j * 4, d64(sfb_lo + j * 128 + kb * 32, sf_hi));
           }
           if (!(kDiag && (p.diag & 4u)))
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
-            tc_mma_nvfp4(d_tmem, make_desc_sw128(a_addr + kb * 32), make_desc_sw128(b_addr + kb * 32), idesc,
-                         tmem_base + Cfg::kSfaCol + kb * 4,
-                         tmem_base + Cfg::kSfbCol + kb * (4 * Cfg::kSfbAtoms) + sfb_shift, (kt | kb) != 0u);
+            tc_mma_nvfp4(d_tmem, d64(a_lo + kb * 2, op_hi), d64(b_lo + kb * 2, op_hi), idesc, t_sfa + kb * 4,
+                         t_sfb + kb * (4 * Cfg::kSfbAtoms) + sfb_shift, (kt | kb) != 0u);
           }
           tc_commit(bar_empty + 8 * stage);
           }
-          __syncwarp();
+          ready = __all_sync(0xFFFFFFFFu, probe) != 0;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (ktr && lane == 0) p.trace[1205] = clock64();
@@ -278,39 +317,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       if (ktr && warp == 2 && lane == 0) p.trace[1206] = clock64();
       const uint32_t t_addr = tmem_base + Cfg::kAccCol0 + acc * BN + ((quarter * 32u) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const uint32_t nc = n0 + c * 32;
-        if (nc >= p.n) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_addr + c * 32, r);
-        const uint32_t ncols = min(32u, p.n - nc);  // multiple of 8
-        // the residual row's four vectors are requested together, before the accumulator read is waited for
-        uint4 res[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-        if (p.gate && row < p.m) {
-          const uint16_t* res_row = p.residual + uint64_t(row) * p.n + nc;
-#pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8)
-            if (uint32_t(v8 * 8) < ncols) res[v8] = __ldg(reinterpret_cast<const uint4*>(res_row + v8 * 8));
+      {
+        const bool skip = kDiag && (p.diag & 1u);
+        switch (mode) {  // warp-uniform
+          case 0: epilogue_tile<BN, false, false, false>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 1: epilogue_tile<BN, true, false, false>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 2: epilogue_tile<BN, false, true, false>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 3: epilogue_tile<BN, true, true, false>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 4: epilogue_tile<BN, false, false, true>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 5: epilogue_tile<BN, true, false, true>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          case 6: epilogue_tile<BN, false, true, true>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
+          default: epilogue_tile<BN, true, true, true>(p, t_addr, row, n0, lane, alpha, bias_smem, gate_smem, skip); break;
         }
-        tmem_ld_wait();
-        if (ktr && warp == 2 && lane == 0) p.trace[1210 + 2 * c] = clock64();
-        {
-          const bool skip = kDiag && (p.diag & 1u);
-          const float* b32 = bias_smem + c * 32;
-          const uint4* g4 = gate_smem + c * 4;
-          switch (mode) {  // warp-uniform
-            case 0: epilogue_chunk32<false, false, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 1: epilogue_chunk32<true, false, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 2: epilogue_chunk32<false, true, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 3: epilogue_chunk32<true, true, false>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 4: epilogue_chunk32<false, false, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 5: epilogue_chunk32<true, false, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            case 6: epilogue_chunk32<false, true, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-            default: epilogue_chunk32<true, true, true>(r, p, alpha, b32, g4, res, ncols, row, nc, lane, skip); break;
-          }
-        }
-        if (ktr && warp == 2 && lane == 0) p.trace[1211 + 2 * c] = clock64();
       }
       tc_fence_before();
       __syncwarp();
@@ -338,10 +356,14 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
 }
 
 uint32_t gemm_tile_n(uint32_t m, uint32_t n) {
-  static uint32_t forced = env_u32("TNF_GEMM_TILE_N", 0);  // tuning knob: 128 or 256
-  if (forced == 128 || forced == 256) return forced;
-  // 256-wide tiles only when they still fill the SMs; 128-wide tiles also double-buffer the accumulator
-  return uint64_t((m + 127u) / 128u) * ((n + 255u) / 256u) >= 148u ? 256u : 128u;
+  static uint32_t forced = env_u32("TNF_GEMM_TILE_N", 0);  // tuning knob: 64, 128 or 256
+  if (forced == 64 || forced == 128 || forced == 256) return forced;
+  // 256-wide tiles only when they still fill the SMs; 128-wide tiles also double-buffer the accumulator; with so
+  // few tiles that half the SMs would idle, 64-wide ones: a CTA's time is what it has to pull in (its A tile
+  // and its share of W) and what it writes out, and both shrink with the tile
+  const uint64_t tm = (m + 127u) / 128u;
+  if (tm * ((n + 255u) / 256u) >= 148u) return 256u;
+  return tm * ((n + 127u) / 128u) * 2u <= 148u ? 64u : 128u;
 }
 
 template <int BN>
@@ -366,6 +388,7 @@ static cudaError_t launch_bn(const CUtensorMap& map_a, const CUtensorMap& map_w,
 cudaError_t launch_gemm_nvfp4(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmParams& p, int sm_count,
                               cudaStream_t s) {
   switch (gemm_tile_n(p.m, p.n)) {
+    case 64: return launch_bn<64>(map_a, map_w, p, sm_count, s);
     case 128: return launch_bn<128>(map_a, map_w, p, sm_count, s);
     default: return launch_bn<256>(map_a, map_w, p, sm_count, s);
   }
