@@ -87,8 +87,10 @@ def test_epilogue_modes(backend, mode):
         backend.free(rb)
 
 
+# one-launch kernels where they are the chosen path (m * k <= 12288, or 24576 from n = 12288 on; K beyond the
+# tensor-core kernel's reach goes to the CUDA-core one) and shapes just outside it, which take quantiser + GEMM
 @pytest.mark.parametrize("m,n,k", [(1, 18432, 3072), (3, 520, 1056), (8, 264, 4128), (4, 136, 64), (16, 1032, 3072), (13, 136, 352),
-                                   (1, 264, 12288), (5, 136, 16384)])
+                                   (1, 264, 12288), (5, 136, 16384), (16, 264, 768), (8, 12296, 3072)])
 @pytest.mark.parametrize("mode", ["gelu", "gelu_chain", "gate"])
 def test_skinny_kernel_epilogue_modes(backend, m, n, k, mode):
     """A handful of rows runs a one-launch skinny kernel with the activation quantiser in its prologue: M <= 16 on the

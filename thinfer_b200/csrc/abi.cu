@@ -997,7 +997,10 @@ int32_t tnf_linear_nvfp4(tnf_ctx* ctx, const tnf_linear_args* a) {
     if (!src) return st;
     return run_gemm(ctx, a, src, nullptr, nullptr, false);
   }
-  if (a->flags == 0 && (skinny_tc_applies(a->m, a->n, a->k) || gemv_applies(a->m, a->n, a->k))) {
+  // one launch for skinny M: the tensor-core kernel where it is the faster path, the CUDA-core one only for K too
+  // long for it; everything else is quantiser + GEMM
+  if (a->flags == 0 && (skinny_tc_applies(a->m, a->n, a->k) ||
+                        (!skinny_tc_capable(a->m, a->n, a->k) && gemv_applies(a->m, a->n, a->k)))) {
     // a handful of rows: one launch that quantises A in its prologue and streams W (no scratch, no quantiser launch)
     uint8_t* src = resolve(ctx, a->a_bf16, uint64_t(a->m) * a->k * 2, "a_bf16", &st);
     if (!src) return st;

@@ -126,7 +126,8 @@ cudaError_t launch_gemm_nvfp4_pair(const CUtensorMap& map_a, const CUtensorMap& 
 // Skinny-M kernel (M <= 8): activation quantiser + weight streaming on the CUDA cores in one launch.
 // Skinny-M on the tensor cores with the operands swapped (M <= 16, one launch, quantiser in the prologue); map_w is the
 // weight's codes as [n, k/2] bytes with a {128 B, 128 rows} box and 128-byte swizzle.
-bool skinny_tc_applies(uint32_t m, uint32_t n, uint32_t k);
+bool skinny_tc_capable(uint32_t m, uint32_t n, uint32_t k);  // the tensor-core skinny kernel can run this shape
+bool skinny_tc_applies(uint32_t m, uint32_t n, uint32_t k);  // ... and is the faster path for it
 cudaError_t launch_skinny_tc(const CUtensorMap& map_w, const void* a_bf16, float a_global, const GemmParams& p, cudaStream_t s);
 bool gemv_applies(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_gemv_nvfp4(const void* a_bf16, float a_global, const uint8_t* w_codes, const GemmParams& p, cudaStream_t s);

@@ -256,8 +256,16 @@ static uint32_t skinny_stages(uint32_t k) {
   return uint32_t(std::min<uint64_t>((sk::kSmemMax - fixed) / sk::kStageBytes, nkt));
 }
 
-bool skinny_tc_applies(uint32_t m, uint32_t n, uint32_t k) {
+bool skinny_tc_capable(uint32_t m, uint32_t n, uint32_t k) {
   return m >= 1 && m <= sk::kMaxM && k % 32 == 0 && n % 8 == 0 && skinny_stages(k) >= std::min(4u, (k + 255u) / 256u);
+}
+
+// Every CTA quantises all of A in its prologue, so the kernel's time grows with m * k (0.4 us per row at K = 3072,
+// 0.9 at K = 9216) while quantiser + GEMM does not depend on m at these sizes. Measured back to back on rotating
+// weights, the one launch wins up to m * k = 12288 (m = 4 at K = 3072: 7.5 against 7.8 us at N = 3072) and, where the
+// other path has many tiles to get through, up to 24576 (m = 8 at N = 18432: 11.8 against 12.9 us).
+bool skinny_tc_applies(uint32_t m, uint32_t n, uint32_t k) {
+  return skinny_tc_capable(m, n, k) && uint64_t(m) * k <= (n >= 12288u ? 24576u : 12288u);
 }
 
 cudaError_t launch_skinny_tc(const CUtensorMap& map_w, const void* a_bf16, float a_global, const GemmParams& g, cudaStream_t s) {
