@@ -369,11 +369,13 @@ def time_linear(be, m, n, k, act=0, iters=20, warmup=3, quant=True, flush_l2=Fal
     return res
 
 
-def time_linear_rotating(be, m, n, k, act=0, rounds=5):
+def time_linear_rotating(be, m, n, k, act=0, rounds=5, two_launches=False):
     """A skinny (HBM-bound) linear measured the way it runs inside a step: launches back to back on the stream,
     no host synchronisation between them, each one on a DIFFERENT weight of the same shape, enough copies that
     their bytes exceed twice the L2 (so every launch reads its weight from HBM). One event pair around the whole
-    train, replayed from a CUDA graph; the time per linear is the device time of its launches in the dependent chain."""
+    train, replayed from a CUDA graph; the time per linear is the device time of its launches in the dependent chain.
+    two_launches: always the stand-alone quantiser followed by the GEMM on its output (the path every shape but the
+    skinniest takes), whatever the library would choose for a plain call of this shape."""
     import torch
     import thinfer_b200 as T
     from thinfer_b200 import _lib as L
@@ -394,7 +396,11 @@ def time_linear_rotating(be, m, n, k, act=0, rounds=5):
 
     def train():
         for w in ws:
-            sc.linear(a, m, w, ga, out, act=act)
+            if two_launches:
+                sc.act_quant_shared(a, m, k, ga)
+                sc.linear(None, m, w, ga, out, act=act, flags=L.LINEAR_A_PREQUANTIZED)
+            else:
+                sc.linear(a, m, w, ga, out, act=act)
 
     train()
     be.submit()
@@ -568,6 +574,9 @@ def run_launch_workload(args):
         res = time_norm_quant(be, args.m, args.k, args.iters, args.warmup)
     elif args.workload == "sdpa":
         res = time_sdpa(be, args.m, args.m, args.n // 128, args.iters, args.warmup)
+    elif args.rotating:
+        res = time_linear_rotating(be, args.m, args.n, args.k, args.act, two_launches=args.two_launches)
+        res.update(m=args.m, n=args.n, k=args.k, two_launches=bool(args.two_launches))
     else:
         res = time_linear(be, args.m, args.n, args.k, args.act, args.iters, args.warmup, not args.no_quant, args.flush_l2,
                           args.out_nvfp4, dense=args.dense_act)
@@ -1109,6 +1118,10 @@ def main():
     ap.add_argument("--no-quant", action="store_true", help="linear: quantise the activations once, time the GEMM alone afterwards")
     ap.add_argument("--flush-l2", action="store_true", help="linear: overwrite a 256 MB buffer between iterations")
     ap.add_argument("--out-nvfp4", action="store_true", help="linear: the epilogue also emits the NVFP4 copy of the output")
+    ap.add_argument("--rotating", action="store_true",
+                    help="linear: the in-step view instead: launches back to back on rotating weights (> 2 x L2), CUDA-graph replay")
+    ap.add_argument("--two-launches", action="store_true",
+                    help="linear --rotating: quantiser + GEMM even where a plain call would take the one-launch skinny kernel")
     ap.add_argument("--dense-act", action="store_true", help="linear: the dense-activation arm (bf16 activations, no quantiser)")
     ap.add_argument("--ring-slots", type=int, default=0)
     args = ap.parse_args()
